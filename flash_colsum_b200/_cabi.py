@@ -1,0 +1,68 @@
+"""ctypes binding of the C ABI declared in ``include/flash_colsum_b200.h``."""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+from . import build as _build
+
+# every symbol the header declares
+EXPORTED_SYMBOLS = (
+    "fcs_version", "fcs_last_error", "fcs_workspace_bytes",
+    "fcs_colsum_batched", "fcs_colsum_non_batched", "fcs_colsum_causal",
+)
+
+FCS_OK = 0
+FCS_DTYPE_FP16 = 0
+FCS_DTYPE_BF16 = 1
+
+_lib: Optional[ctypes.CDLL] = None
+
+_i, _i64, _f, _p, _sz = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
+
+
+class LibraryMissing(RuntimeError):
+    """The CUDA library is not built; there is no other implementation to fall back to."""
+
+
+def load() -> ctypes.CDLL:
+    """Load the library, building it when sources are newer and nvcc is present.
+
+    Fails loudly if the library can neither be found nor built.
+    """
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if _build.is_stale():
+        try:
+            path = _build.build()
+        except Exception as exc:  # no nvcc on this machine
+            if not os.path.exists(path):
+                raise LibraryMissing(
+                    f"{path} is missing and could not be built ({exc}); "
+                    "run `python -m flash_colsum_b200.build` where nvcc is available") from exc
+    lib = ctypes.CDLL(path)
+    lib.fcs_version.restype = _i
+    lib.fcs_version.argtypes = []
+    lib.fcs_last_error.restype = ctypes.c_char_p
+    lib.fcs_last_error.argtypes = []
+    lib.fcs_workspace_bytes.restype = _sz
+    lib.fcs_workspace_bytes.argtypes = [_i] * 6
+    lib.fcs_colsum_batched.restype = _i
+    lib.fcs_colsum_batched.argtypes = [_p, _p, _p, _i64, _i, _i, _i, _i, _i] + [_i64] * 6 + \
+        [_f, _i, _i, _p, _sz, _p, _p]
+    lib.fcs_colsum_non_batched.restype = _i
+    lib.fcs_colsum_non_batched.argtypes = [_p, _p, _p, _i, _i, _i, _i] + [_i64] * 4 + \
+        [_f, _i, _i, _p, _sz, _p, _p]
+    lib.fcs_colsum_causal.restype = _i
+    lib.fcs_colsum_causal.argtypes = [_p, _p, _p, _i, _i, _i, _i, _i] + [_i64] * 4 + \
+        [_f, _i, _i, _p, _sz, _p, _p]
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().fcs_last_error().decode("utf-8", "replace")

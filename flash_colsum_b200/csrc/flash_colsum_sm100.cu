@@ -1,0 +1,584 @@
+// Attention column mean for B200 (sm_100a): kernels and their C ABI.
+//
+// out[b, k] = 1/(H * R) * sum_h sum_{q < R} softmax_k(scale * Q[b,h,q,:] . K[b,h,k,:])
+//
+// Two streaming kernels share one warp-specialised skeleton (TMA -> shared
+// memory -> tcgen05 MMA -> tensor memory -> consumer warps):
+//
+//   statistics pass  S  = Q K^T : tensor-memory lane = query row, so the running
+//                    row maximum and sum of exp2 stay inside one thread.  It
+//                    writes -(log2-sum-exp + log2(H*R)) per query row.
+//   column pass      S^T = K Q^T: tensor-memory lane = key, so the reduction
+//                    down the query axis stays inside one thread as well.  It
+//                    adds exp2(c*s - lse) into a per-key fp32 accumulator and
+//                    flushes that with one atomic add per (key tile, CTA range).
+//
+// Both operands are [128 x D] row tiles with the head dimension contiguous, so
+// the same shared-memory tile layout serves as A or B of the MMA.
+#include "sm100_ptx.cuh"
+#include "schedule.h"
+
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/flash_colsum_b200.h"
+
+namespace fcs {
+
+constexpr int NUM_TBUF = 4;        // accumulator buffers of 128 tensor-memory columns
+constexpr int TMEM_COLS = 512;
+constexpr int CONSUMER_WARPS = 8;  // two groups of four warps; a group owns lanes 0..127
+constexpr int PRODUCER_WARP = 8;
+constexpr int MMA_WARP = 9;
+constexpr int THREADS = 320;
+
+template <int D>
+struct Layout {
+    static constexpr int SLABS = D / 64;              // 64-element (128-byte) column slabs
+    static constexpr int SLAB_BYTES = TILE * 128;
+    static constexpr int TILE_BYTES = SLABS * SLAB_BYTES;
+    static constexpr int NS = (D == 64) ? 6 : 4;      // streamed-operand stages
+    static constexpr int A_OFF = 0;
+    static constexpr int B_OFF = 2 * TILE_BYTES;
+    static constexpr int BAR_OFF = B_OFF + NS * TILE_BYTES;
+    // barriers: a_full[2] a_empty[2] b_full[NS] b_empty[NS] t_full[4] t_empty[4] merge[2]
+    static constexpr int NUM_BARS = 4 + 2 * NS + 2 * NUM_TBUF + 2;
+    static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;        // tmem address, abort flag
+    static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // float2[2][128]
+    static constexpr int TOTAL = MERGE_OFF + 2 * TILE * 8;
+    static constexpr int DYN_BYTES = TOTAL + 1024;    // slack to align the base to 1024
+};
+
+// ---------------------------------------------------------------------------
+// Consumer math
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// Online (max, sum) update of one query row with 32 more scores.
+// `last_valid`: columns 0..last_valid of this chunk are visible (>= 31: all).
+template <bool MASKED>
+__device__ __forceinline__ void stats_chunk(const uint32_t (&r)[32], int last_valid, float c,
+                                            float& m, float& l) {
+    float s[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        s[j] = __uint_as_float(r[j]);
+        if (MASKED) s[j] = (j <= last_valid) ? s[j] : -INFINITY;
+    }
+    float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
+#pragma unroll
+    for (int j = 6; j < 30; j += 4) {
+        m0 = max3(m0, s[j], s[j + 1]);
+        m1 = max3(m1, s[j + 2], s[j + 3]);
+    }
+    float cm = max3(m0, m1, fmaxf(s[30], s[31]));
+    float scaled = (cm == -INFINITY) ? -INFINITY : cm * c;
+    const float m_new = fmaxf(m, scaled);
+    const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+    l *= ex2_approx(m - m_safe);
+    m = m_new;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        float t0 = fmaf(s[j], c, -m_safe), t1 = fmaf(s[j + 1], c, -m_safe);
+        float t2 = fmaf(s[j + 2], c, -m_safe), t3 = fmaf(s[j + 3], c, -m_safe);
+        if (MASKED) {
+            t0 = (j <= last_valid) ? t0 : -INFINITY;
+            t1 = (j + 1 <= last_valid) ? t1 : -INFINITY;
+            t2 = (j + 2 <= last_valid) ? t2 : -INFINITY;
+            t3 = (j + 3 <= last_valid) ? t3 : -INFINITY;
+        }
+        a0 += ex2_approx(t0); a1 += ex2_approx(t1);
+        a2 += ex2_approx(t2); a3 += ex2_approx(t3);
+    }
+    l += (a0 + a1) + (a2 + a3);
+}
+
+// Add exp2(c*s - lse[q]) of 32 query columns into a key's accumulators.
+// `first_valid`: columns >= first_valid of this chunk are visible (<= 0: all).
+template <bool MASKED>
+__device__ __forceinline__ void colsum_chunk(const uint32_t (&r)[32], const float4 (&nl)[8],
+                                             int first_valid, float c, float (&acc)[4]) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const float4 n = nl[j >> 2];
+        float t0 = fmaf(__uint_as_float(r[j]), c, n.x);
+        float t1 = fmaf(__uint_as_float(r[j + 1]), c, n.y);
+        float t2 = fmaf(__uint_as_float(r[j + 2]), c, n.z);
+        float t3 = fmaf(__uint_as_float(r[j + 3]), c, n.w);
+        if (MASKED) {
+            t0 = (j >= first_valid) ? t0 : -INFINITY;
+            t1 = (j + 1 >= first_valid) ? t1 : -INFINITY;
+            t2 = (j + 2 >= first_valid) ? t2 : -INFINITY;
+            t3 = (j + 3 >= first_valid) ? t3 : -INFINITY;
+        }
+        acc[0] += ex2_approx(t0); acc[1] += ex2_approx(t1);
+        acc[2] += ex2_approx(t2); acc[3] += ex2_approx(t3);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The streaming kernel
+// ---------------------------------------------------------------------------
+template <int D, int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
+                     const __grid_constant__ CUtensorMap tm_k, const Problem p) {
+    using L = Layout<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t a_smem = smem_base + L::A_OFF;
+    const uint32_t b_smem = smem_base + L::B_OFF;
+    const uint32_t bars = smem_base + L::BAR_OFF;
+    auto a_full = [&](int i) { return bars + 8u * i; };
+    auto a_empty = [&](int i) { return bars + 8u * (2 + i); };
+    auto b_full = [&](int i) { return bars + 8u * (4 + i); };
+    auto b_empty = [&](int i) { return bars + 8u * (4 + L::NS + i); };
+    auto t_full = [&](int i) { return bars + 8u * (4 + 2 * L::NS + i); };
+    auto t_empty = [&](int i) { return bars + 8u * (4 + 2 * L::NS + NUM_TBUF + i); };
+    auto merge_bar = [&](int i) { return bars + 8u * (4 + 2 * L::NS + 2 * NUM_TBUF + i); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFF + 4);
+    float2* merge_buf = reinterpret_cast<float2*>(smem + L::MERGE_OFF);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const CUtensorMap* tm_a = (MODE == MODE_STATS) ? &tm_q : &tm_k;   // resident operand
+    const CUtensorMap* tm_b = (MODE == MODE_STATS) ? &tm_k : &tm_q;   // streamed operand
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), 1); }
+        for (int i = 0; i < L::NS; ++i) { mbar_init(b_full(i), 1); mbar_init(b_empty(i), 1); }
+        for (int i = 0; i < NUM_TBUF; ++i) { mbar_init(t_full(i), 1); mbar_init(t_empty(i), 128); }
+        for (int i = 0; i < 2; ++i) mbar_init(merge_bar(i), 128);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == PRODUCER_WARP && lane == 0) {
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == PRODUCER_WARP) {
+        // ------------------------------------------------ TMA producer (one thread)
+        if (lane == 0) {
+            WorkIter<MODE> it;
+            it.init(p, blockIdx.x, gridDim.x);
+            int a_cnt = 0, stage = 0;
+            uint32_t phase = 0;
+            for (; !it.done; it.next(p)) {
+                if (it.first) {
+                    const int ab = a_cnt & 1;
+                    if (!mbar_wait(a_empty(ab), ((a_cnt >> 1) & 1) ^ 1, abort_flag, p.status,
+                                   FCS_STATUS_WAIT_PRODUCER)) break;
+                    mbar_arrive_expect_tx(a_full(ab), L::TILE_BYTES);
+#pragma unroll
+                    for (int sl = 0; sl < L::SLABS; ++sl)
+                        tma_load_4d(a_smem + ab * L::TILE_BYTES + sl * L::SLAB_BYTES, tm_a,
+                                    a_full(ab), sl * 64, it.a_row(), it.h, it.b);
+                }
+                if (!mbar_wait(b_empty(stage), phase ^ 1, abort_flag, p.status,
+                               FCS_STATUS_WAIT_PRODUCER)) break;
+                mbar_arrive_expect_tx(b_full(stage), L::TILE_BYTES);
+#pragma unroll
+                for (int sl = 0; sl < L::SLABS; ++sl)
+                    tma_load_4d(b_smem + stage * L::TILE_BYTES + sl * L::SLAB_BYTES, tm_b,
+                                b_full(stage), sl * 64, it.b_row(), it.h, it.b);
+                if (it.last) ++a_cnt;
+                if (++stage == L::NS) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        // ------------------------------------------------ MMA issuer (one thread)
+        if (lane == 0) {
+            WorkIter<MODE> it;
+            it.init(p, blockIdx.x, gridDim.x);
+            int a_cnt = 0, stage = 0, i = 0;
+            uint32_t phase = 0;
+            for (; !it.done; it.next(p), ++i) {
+                const int ab = a_cnt & 1;
+                if (it.first) {
+                    if (!mbar_wait(a_full(ab), (a_cnt >> 1) & 1, abort_flag, p.status,
+                                   FCS_STATUS_WAIT_MMA)) break;
+                }
+                if (!mbar_wait(b_full(stage), phase, abort_flag, p.status, FCS_STATUS_WAIT_MMA)) break;
+                const int buf = i & (NUM_TBUF - 1);
+                if (!mbar_wait(t_empty(buf), ((i >> 2) & 1) ^ 1, abort_flag, p.status,
+                               FCS_STATUS_WAIT_MMA)) break;
+                tc_fence_after();
+                const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::TILE_BYTES);
+                const uint64_t db = umma_desc_k_sw128(b_smem + stage * L::TILE_BYTES);
+                const uint32_t d_tmem = tmem_base + buf * TILE;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    // 32 bytes per 16-element step inside a slab, 16 KB per slab
+                    const uint64_t off = (uint64_t)(((ks >> 2) * L::SLAB_BYTES + (ks & 3) * 32) >> 4);
+                    umma_f16(d_tmem, da + off, db + off, p.idesc, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(b_empty(stage));
+                umma_commit(t_full(buf));
+                if (it.last) { umma_commit(a_empty(ab)); ++a_cnt; }
+                if (++stage == L::NS) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------ consumers (8 warps)
+        const int wg = warp >> 2;                 // 0 or 1: takes every other tile
+        const int row = ((warp & 3) << 5) | lane; // tensor-memory lane of this thread
+        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16);
+        const float c = p.c;
+        bool ok = true;
+
+        if constexpr (MODE == MODE_STATS) {
+            // the output is accumulated by the column pass: clear it here
+            const long long n_out = (long long)p.B * p.Sk;
+            for (long long idx = (long long)blockIdx.x * (CONSUMER_WARPS * 32) + threadIdx.x; idx < n_out;
+                 idx += (long long)gridDim.x * (CONSUMER_WARPS * 32)) {
+                const long long bb = idx / p.Sk;
+                p.out[bb * p.out_ld + (idx - bb * p.Sk)] = 0.f;
+            }
+        }
+
+        WorkIter<MODE> it;
+        it.init(p, blockIdx.x, gridDim.x);
+        float m_run = -INFINITY, l_run = 0.f;      // statistics pass state
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};       // column pass state
+        int item_cnt = 0;
+        for (int i = 0; !it.done; it.next(p), ++i) {
+            if ((i & 1) == wg) {
+                const int buf = i & (NUM_TBUF - 1);
+                ok = mbar_wait(t_full(buf), (i >> 2) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = lane_addr + buf * TILE;
+                uint32_t r[32];
+                if constexpr (MODE == MODE_STATS) {
+                    const int lim = stats_last_visible(p, it.qt, it.kt, row);
+                    const bool full = stats_tile_full(p, it.qt, it.kt);
+#pragma unroll 1
+                    for (int ch = 0; ch < 4; ++ch) {
+                        tmem_ld_x32(taddr + ch * 32, r);
+                        tmem_ld_wait(r);
+                        if (full) stats_chunk<false>(r, 31, c, m_run, l_run);
+                        else stats_chunk<true>(r, lim - ch * 32, c, m_run, l_run);
+                    }
+                } else {
+                    const float4* nl4 = reinterpret_cast<const float4*>(
+                        p.neg_lse + (((long long)it.b * p.H + it.h) * p.NQ + it.qt) * TILE);
+                    const int thr = colsum_first_visible(p, it.kt, it.qt, row);
+                    const bool full = colsum_tile_full(p, it.kt, it.qt);
+#pragma unroll 1
+                    for (int ch = 0; ch < 4; ++ch) {
+                        tmem_ld_x32(taddr + ch * 32, r);
+                        float4 nl[8];
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) nl[v] = __ldg(nl4 + ch * 8 + v);
+                        tmem_ld_wait(r);
+                        if (full) colsum_chunk<false>(r, nl, 0, c, acc);
+                        else colsum_chunk<true>(r, nl, thr - ch * 32, c, acc);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(t_empty(buf));
+            }
+            if constexpr (MODE == MODE_STATS) {
+                if (it.last) {
+                    // combine the two consumer groups' partial (max, sum) and store
+                    const int slot = item_cnt & 1;
+                    if (wg == 1) {
+                        merge_buf[slot * TILE + row] = make_float2(m_run, l_run);
+                        mbar_arrive(merge_bar(slot));
+                    } else {
+                        ok = mbar_wait(merge_bar(slot), (item_cnt >> 1) & 1, abort_flag, p.status,
+                                       FCS_STATUS_WAIT_CONSUMER);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        const float2 o = merge_buf[slot * TILE + row];
+                        const float mm = fmaxf(m_run, o.x);
+                        const float ms = (mm == -INFINITY) ? 0.f : mm;
+                        const float ll = l_run * exp2f(m_run - ms) + o.y * exp2f(o.x - ms);
+                        const long long bh = (long long)it.b * p.H + it.h;
+                        const long long ridx = (bh * p.NQ + it.qt) * TILE + row;
+                        if (p.nsplit == 1) {
+                            const bool real = (it.qt * TILE + row) < p.Sq;
+                            p.neg_lse[ridx] = real ? -(mm + log2f(ll) + p.log2_norm) : -INFINITY;
+                        } else {
+                            reinterpret_cast<float2*>(p.part)[(long long)it.sp * ((long long)p.B * p.H * p.NQ * TILE) + ridx] =
+                                make_float2(mm, ll);
+                        }
+                    }
+                    m_run = -INFINITY; l_run = 0.f;
+                    ++item_cnt;
+                }
+            } else {
+                if (it.flush) {
+                    const int k_abs = it.kt * TILE + row;
+                    if (k_abs < p.Sk)
+                        atomicAdd(p.out + (long long)it.b * p.out_ld + k_abs,
+                                  (acc[0] + acc[1]) + (acc[2] + acc[3]));
+                    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        if (*abort_flag) __nanosleep(1000000);   // let copies and MMAs in flight land
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// Combine the key-range partials of the statistics pass into the per-row value
+// the column pass subtracts.
+__global__ void merge_stats_kernel(const Problem p) {
+    const long long rows_per_bh = (long long)p.NQ * TILE;
+    const long long n = (long long)p.B * p.H * rows_per_bh;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int q_abs = (int)(idx % rows_per_bh);
+        float v = -INFINITY;
+        if (q_abs < p.Sq) {
+            float mm = -INFINITY;
+            const float2* part = reinterpret_cast<const float2*>(p.part);
+            for (int s = 0; s < p.nsplit; ++s) mm = fmaxf(mm, part[s * n + idx].x);
+            float ll = 0.f;
+            for (int s = 0; s < p.nsplit; ++s) {
+                const float2 t = part[s * n + idx];
+                ll += t.y * exp2f(t.x - mm);
+            }
+            v = -(mm + log2f(ll) + p.log2_norm);
+        }
+        p.neg_lse[idx] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+static int num_sms() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// (D, S, H, B) view of a [B, H, S, D] tensor, boxes of 128 rows x 64 elements,
+// 128-byte swizzle, out-of-range rows read as zero.
+static int make_tensor_map(CUtensorMap* m, const void* base, int dtype, int B, int H, int S, int D,
+                           int64_t sb, int64_t sh, int64_t ss) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(FCS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)TILE, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(m, dtype == FCS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                     4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FCS_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return FCS_OK;
+}
+
+template <int D, int MODE>
+static cudaError_t launch_stream(const CUtensorMap& tq, const CUtensorMap& tk, const Problem& p, int grid,
+                                 cudaStream_t stream) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kern = colsum_stream_kernel<D, MODE>;
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Layout<D>::DYN_BYTES);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    kern<<<grid, THREADS, Layout<D>::DYN_BYTES, stream>>>(tq, tk, p);
+    return cudaGetLastError();
+}
+
+static int check_operand(const char* name, const void* ptr, int64_t sb, int64_t sh, int64_t ss) {
+    if (!ptr) return fail(FCS_ERR_INVALID_ARGUMENT, "%s is NULL", name);
+    if (reinterpret_cast<uintptr_t>(ptr) % 16)
+        return fail(FCS_ERR_INVALID_ARGUMENT, "%s must be 16-byte aligned", name);
+    if (sb <= 0 || sh <= 0 || ss <= 0 || sb % 8 || sh % 8 || ss % 8)
+        return fail(FCS_ERR_INVALID_ARGUMENT,
+                    "%s strides must be positive multiples of 8 elements (got b=%lld h=%lld s=%lld)", name,
+                    (long long)sb, (long long)sh, (long long)ss);
+    return FCS_OK;
+}
+
+// The one implementation behind the three entry points.
+static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int Sq_full,
+                       int Sk, int D, int dtype, int64_t qsb, int64_t qsh, int64_t qss, int64_t ksb,
+                       int64_t ksh, int64_t kss, float scale, int causal, int k_past, int cls_n, int h_norm,
+                       void* workspace, size_t workspace_bytes, int* status, void* stream_v) {
+    g_err[0] = 0;
+    if (B <= 0 || H <= 0 || Sq_full <= 0 || Sk <= 0)
+        return fail(FCS_ERR_INVALID_ARGUMENT, "sizes must be positive (B=%d H=%d Sq=%d Sk=%d)", B, H, Sq_full, Sk);
+    if (D != 64 && D != 128) return fail(FCS_ERR_UNSUPPORTED, "head dimension must be 64 or 128, got %d", D);
+    if (dtype != FCS_DTYPE_FP16 && dtype != FCS_DTYPE_BF16)
+        return fail(FCS_ERR_UNSUPPORTED, "dtype must be FCS_DTYPE_FP16 or FCS_DTYPE_BF16, got %d", dtype);
+    if (!out) return fail(FCS_ERR_INVALID_ARGUMENT, "out is NULL");
+    if (out_ld < Sk) return fail(FCS_ERR_INVALID_ARGUMENT, "out_ld (%lld) is smaller than the key length", (long long)out_ld);
+    if (!isfinite(scale)) return fail(FCS_ERR_INVALID_ARGUMENT, "scale must be finite");
+    if (!causal && cls_n != -1 && cls_n <= 0)
+        return fail(FCS_ERR_INVALID_ARGUMENT, "cls_n must be -1 or positive, got %d", cls_n);
+    int rc;
+    if ((rc = check_operand("q", q, qsb, qsh, qss)) != FCS_OK) return rc;
+    if ((rc = check_operand("k", k, ksb, ksh, kss)) != FCS_OK) return rc;
+    if (h_norm <= 0) h_norm = H;
+
+    int Sq = Sq_full;                       // rows that enter the mean
+    if (!causal && cls_n > 0 && cls_n < Sq_full) Sq = cls_n;
+    if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
+
+    const int sms = num_sms();
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    plan(p, B, H, Sq, Sk, causal, k_past, sms);
+    size_t part_off = 0;
+    const size_t need = workspace_layout(p, &part_off);
+    if (!workspace || workspace_bytes < need)
+        return fail(FCS_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256)
+        return fail(FCS_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    p.neg_lse = reinterpret_cast<float*>(workspace);
+    p.part = reinterpret_cast<uint8_t*>(workspace) + part_off;
+    p.out = out;
+    p.out_ld = out_ld;
+    p.status = status;
+    p.c = fabsf(scale) * 1.4426950408889634f;
+    p.log2_norm = log2f((float)h_norm * (float)Sq);
+    const uint32_t fmt = dtype == FCS_DTYPE_BF16 ? 1u : 0u;
+    // fp32 accumulate, K-major A and B, M = N = 128; a negative scale negates A
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((scale < 0.f ? 1u : 0u) << 13) |
+              ((uint32_t)(TILE >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
+
+    CUtensorMap tq, tk;
+    if ((rc = make_tensor_map(&tq, q, dtype, B, H, Sq, D, qsb, qsh, qss)) != FCS_OK) return rc;
+    if ((rc = make_tensor_map(&tk, k, dtype, B, H, Sk, D, ksb, ksh, kss)) != FCS_OK) return rc;
+
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+    const int grid1 = (int)(p.stats_items < sms ? p.stats_items : sms);
+    const int grid2 = (int)(p.steps_total < sms ? p.steps_total : sms);
+    cudaError_t e;
+    e = (D == 64) ? launch_stream<64, MODE_STATS>(tq, tk, p, grid1, stream)
+                  : launch_stream<128, MODE_STATS>(tq, tk, p, grid1, stream);
+    if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics pass launch failed: %s", cudaGetErrorString(e));
+    if (p.nsplit > 1) {
+        const long long n = (long long)B * H * p.NQ * TILE;
+        int blocks = (int)((n + 255) / 256);
+        if (blocks > sms * 8) blocks = sms * 8;
+        merge_stats_kernel<<<blocks, 256, 0, stream>>>(p);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics merge launch failed: %s", cudaGetErrorString(e));
+    }
+    e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tq, tk, p, grid2, stream)
+                  : launch_stream<128, MODE_COLSUM>(tq, tk, p, grid2, stream);
+    if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "column pass launch failed: %s", cudaGetErrorString(e));
+    return FCS_OK;
+}
+
+}  // namespace fcs
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+extern "C" {
+
+int fcs_version(void) { return 100; }
+
+const char* fcs_last_error(void) { return fcs::g_err; }
+
+size_t fcs_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_causal) {
+    if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0 || (D != 64 && D != 128)) return 0;
+    fcs::Problem p;
+    memset(&p, 0, sizeof(p));
+    const int k_past = Sk > sq_rows ? Sk - sq_rows : 0;
+    fcs::plan(p, B, H, sq_rows, Sk, is_causal ? 1 : 0, k_past, fcs::num_sms());
+    return fcs::workspace_layout(p, nullptr);
+}
+
+int fcs_colsum_batched(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int S, int D,
+                       int dtype, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                       int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s, float scale, int cls_n,
+                       int h_norm, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+    return fcs::colsum_impl(q, k, out, out_ld, B, H, S, S, D, dtype, q_stride_b, q_stride_h, q_stride_s,
+                            k_stride_b, k_stride_h, k_stride_s, scale, 0, 0, cls_n, h_norm, workspace,
+                            workspace_bytes, status, stream);
+}
+
+int fcs_colsum_non_batched(const void* q, const void* k, float* out, int H, int S, int D, int dtype,
+                           int64_t q_stride_h, int64_t q_stride_s, int64_t k_stride_h, int64_t k_stride_s,
+                           float scale, int cls_n, int h_norm, void* workspace, size_t workspace_bytes,
+                           int* status, void* stream) {
+    return fcs::colsum_impl(q, k, out, S, 1, H, S, S, D, dtype, q_stride_h * H, q_stride_h, q_stride_s,
+                            k_stride_h * H, k_stride_h, k_stride_s, scale, 0, 0, cls_n, h_norm, workspace,
+                            workspace_bytes, status, stream);
+}
+
+int fcs_colsum_causal(const void* q, const void* k, float* out, int H, int q_len, int k_len, int D, int dtype,
+                      int64_t q_stride_h, int64_t q_stride_s, int64_t k_stride_h, int64_t k_stride_s,
+                      float scale, int k_past, int h_norm, void* workspace, size_t workspace_bytes,
+                      int* status, void* stream) {
+    return fcs::colsum_impl(q, k, out, k_len, 1, H, q_len, k_len, D, dtype, q_stride_h * H, q_stride_h,
+                            q_stride_s, k_stride_h * H, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm,
+                            workspace, workspace_bytes, status, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,199 @@
+"""The operator: column means of softmax attention without forming the matrix.
+
+Same call as the reference's ``flash_colsum`` (flash_colsum/ops.py:13-105): same
+arguments, same validation order and messages, same three-way dispatch (causal /
+single-sample / batched) -- each branch calls one C-ABI entry point of the CUDA
+library instead of a Triton launcher.  There is no CPU path and no fallback: if
+the library is missing the call raises.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _cabi
+
+_DTYPE_CODE = {torch.float16: _cabi.FCS_DTYPE_FP16, torch.bfloat16: _cabi.FCS_DTYPE_BF16}
+
+# one sticky device-status word per device, zeroed once
+_status: Dict[int, torch.Tensor] = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def device_status(device=None) -> int:
+    """Synchronise and return the device status word (0 = no kernel gave up a wait)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    return int(_status_word(dev).item())
+
+
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """Unit inner stride, outer strides multiples of 16 bytes, 16-byte aligned base."""
+    ok = (t.stride(3) == 1 and all(s > 0 and s % 8 == 0 for s in t.stride()[:3])
+          and t.data_ptr() % 16 == 0)
+    return t if ok else t.contiguous()
+
+
+def _rows(cls_n: int, S: int) -> int:
+    return S if cls_n == -1 else min(cls_n, S)
+
+
+def _check(rc: int) -> None:
+    if rc != _cabi.FCS_OK:
+        raise RuntimeError(f"flash_colsum_b200: {_cabi.last_error()} (code {rc})")
+
+
+def _prepare(query: torch.Tensor, key: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, int]:
+    if query.dtype not in _DTYPE_CODE:
+        raise ValueError(f"flash_colsum supports float16 and bfloat16 inputs, got {query.dtype}")
+    if key.dtype != query.dtype:
+        raise ValueError(f"query and key must have the same dtype, got {query.dtype} and {key.dtype}")
+    if key.device != query.device:
+        raise ValueError(f"query and key must be on the same device, got {query.device} and {key.device}")
+    if query.shape[3] not in (64, 128):
+        raise ValueError(f"head_dim must be 64 or 128, got {query.shape[3]}")
+    return _tma_ready(query), _tma_ready(key), _DTYPE_CODE[query.dtype]
+
+
+def _workspace(lib, device, B, H, rows, Sk, D, causal) -> torch.Tensor:
+    n = lib.fcs_workspace_bytes(B, H, rows, Sk, D, int(causal))
+    if n == 0:
+        raise RuntimeError("flash_colsum_b200: fcs_workspace_bytes rejected the sizes")
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+def _flash_colsum_batched(Q: torch.Tensor, K: torch.Tensor, scale: float, CLS_N: int = -1,
+                          h_norm: int = 0) -> torch.Tensor:
+    """(B, S) fp32.  Counterpart of kernel_noncausal_batched.py:102."""
+    lib = _cabi.load()
+    Q, K, code = _prepare(Q, K)
+    B, H, S, D = Q.shape
+    with torch.cuda.device(Q.device):
+        out = torch.empty((B, S), device=Q.device, dtype=torch.float32)
+        ws = _workspace(lib, Q.device, B, H, _rows(CLS_N, S), S, D, False)
+        _check(lib.fcs_colsum_batched(
+            Q.data_ptr(), K.data_ptr(), out.data_ptr(), S, B, H, S, D, code,
+            Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
+            float(scale), int(CLS_N), int(h_norm), ws.data_ptr(), ws.numel(),
+            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+    return out
+
+
+def _flash_colsum_non_batched(Q: torch.Tensor, K: torch.Tensor, scale: float, CLS_N: int = -1,
+                              h_norm: int = 0) -> torch.Tensor:
+    """(1, S) fp32.  Counterpart of kernel_noncausal.py:95."""
+    lib = _cabi.load()
+    Q, K, code = _prepare(Q, K)
+    _, H, S, D = Q.shape
+    with torch.cuda.device(Q.device):
+        out = torch.empty((1, S), device=Q.device, dtype=torch.float32)
+        ws = _workspace(lib, Q.device, 1, H, _rows(CLS_N, S), S, D, False)
+        _check(lib.fcs_colsum_non_batched(
+            Q.data_ptr(), K.data_ptr(), out.data_ptr(), H, S, D, code,
+            Q.stride(1), Q.stride(2), K.stride(1), K.stride(2),
+            float(scale), int(CLS_N), int(h_norm), ws.data_ptr(), ws.numel(),
+            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+    return out
+
+
+def _flash_colsum_causal(Q: torch.Tensor, K: torch.Tensor, scale: float, K_past: Optional[int] = None,
+                         h_norm: int = 0) -> torch.Tensor:
+    """(1, K_len) fp32.  Counterpart of kernel_causal.py:94."""
+    lib = _cabi.load()
+    Q, K, code = _prepare(Q, K)
+    _, H, Q_len, D = Q.shape
+    K_len = K.shape[2]
+    with torch.cuda.device(Q.device):
+        out = torch.empty((1, K_len), device=Q.device, dtype=torch.float32)
+        ws = _workspace(lib, Q.device, 1, H, Q_len, K_len, D, True)
+        _check(lib.fcs_colsum_causal(
+            Q.data_ptr(), K.data_ptr(), out.data_ptr(), H, Q_len, K_len, D, code,
+            Q.stride(1), Q.stride(2), K.stride(1), K.stride(2),
+            float(scale), -1 if K_past is None else int(K_past), int(h_norm),
+            ws.data_ptr(), ws.numel(),
+            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+    return out
+
+
+def flash_colsum(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    scale: Optional[float] = None,
+    is_causal: bool = False,
+    cls_len: Optional[int] = None,
+    *,
+    out_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """Column means of the attention matrix.
+
+    Args:
+        query: (B, H, S, D) for non-causal or (1, H, Q_len, D) for causal; fp16 or bf16.
+        key: same shape as query (non-causal) or (1, H, K_len, D) (causal).
+        scale: score scale, default 1/sqrt(D).
+        is_causal: queries are aligned to the end of the keys and key j is visible
+            to query i iff j <= max(0, K_len - Q_len) + i.
+        cls_len: non-causal only; average over the first ``min(cls_len, S)`` query
+            rows instead of all of them.
+        out_dtype: dtype of the result.  Default fp32, the precision the kernels
+            accumulate in (column means of long sequences are fp16 subnormals);
+            pass ``torch.float16`` for the dtype the reference's kernels return.
+
+    Returns:
+        (B, S) for non-causal, (1, K_len) for causal.
+
+    Raises:
+        ValueError: invalid shapes/arguments, with the reference's messages
+        (flash_colsum/ops.py:59-97).
+    """
+    if query.ndim != 4 or key.ndim != 4:
+        raise ValueError(f"Expected 4D tensors, got query.ndim={query.ndim}, key.ndim={key.ndim}")
+
+    if query.device.type != 'cuda':
+        raise ValueError(f"Flash attention only supports CUDA tensors, got {query.device}")
+
+    if cls_len is not None and is_causal:
+        raise ValueError("cls_len is only supported for non-causal attention")
+    if cls_len is not None and cls_len <= 0:
+        raise ValueError(f"cls_len must be positive, got {cls_len}")
+
+    B_q, H_q, S_q, D_q = query.shape
+    B_k, H_k, S_k, D_k = key.shape
+
+    if scale is None:
+        scale = 1.0 / (D_q ** 0.5)
+
+    if is_causal:
+        if B_q != 1 or B_k != 1:
+            raise ValueError(
+                f"Causal attention currently only supports batch size 1, got B_q={B_q}, B_k={B_k}")
+        if H_q != H_k or D_q != D_k:
+            raise ValueError(
+                f"Query and key must have same heads and head_dim, got "
+                f"H_q={H_q}, H_k={H_k}, D_q={D_q}, D_k={D_k}")
+        out = _flash_colsum_causal(query, key, scale)
+    else:
+        if B_q != B_k or H_q != H_k or S_q != S_k or D_q != D_k:
+            raise ValueError(
+                f"For non-causal attention, query and key must have same shape, got "
+                f"query: {query.shape}, key: {key.shape}")
+        cls_n = -1 if cls_len is None else int(cls_len)
+        if B_q == 1:
+            out = _flash_colsum_non_batched(query, key, scale, CLS_N=cls_n)
+        else:
+            out = _flash_colsum_batched(query, key, scale, CLS_N=cls_n)
+
+    if out_dtype is not None and out_dtype != out.dtype:
+        out = out.to(out_dtype)
+    return out
+
+
+__all__ = ["flash_colsum", "device_status"]

@@ -1,0 +1,112 @@
+/*
+ * flash_colsum_b200 -- C ABI of the B200 (sm_100a) attention column-mean library.
+ *
+ * For attention A = softmax(scale * Q K^T [+ causal mask]) the library returns,
+ * per key position, the mean of A over heads and query rows without forming A.
+ * The entry points are what a binding of the reference's three kernel
+ * launchers would call; the Python operator `flash_colsum` binds them with
+ * ctypes.  Plain pointers and sizes only: device pointers are raw addresses,
+ * the stream is a cudaStream_t passed as void*.
+ *
+ * Common conventions
+ *   - q, k: device pointers to 16-bit elements (dtype: FCS_DTYPE_*), innermost
+ *     (head-dim) stride 1; the other strides are given in elements and must be
+ *     multiples of 8 (16 bytes); base addresses 16-byte aligned.  D is 64 or 128.
+ *   - out: device pointer to fp32, row stride `out_ld` elements.  It is
+ *     overwritten (zeroed by the library, then accumulated).
+ *   - h_norm: number of heads the mean is taken over.  Pass H, or the global
+ *     head count when this call sees only a shard of the heads and the partial
+ *     results are summed afterwards.
+ *   - workspace: device scratch of at least fcs_workspace_bytes(...) bytes,
+ *     256-byte aligned, owned by the caller, not preserved between calls.
+ *   - status: optional device int (may be NULL), zeroed by the caller once.  A
+ *     device-side wait that ran out of time stores a non-zero code there; the
+ *     caller reads it after synchronising the stream.
+ *   - All calls are asynchronous on `stream`, never synchronise and never
+ *     allocate.  Return value: FCS_OK or a negative FCS_ERR_* code;
+ *     fcs_last_error() gives the message for the calling thread.
+ */
+#ifndef FLASH_COLSUM_B200_H_
+#define FLASH_COLSUM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FCS_OK 0
+#define FCS_ERR_INVALID_ARGUMENT (-1)
+#define FCS_ERR_UNSUPPORTED (-2)
+#define FCS_ERR_WORKSPACE (-3)
+#define FCS_ERR_CUDA (-4)
+
+#define FCS_DTYPE_FP16 0
+#define FCS_DTYPE_BF16 1
+
+/* Device status codes (written to *status by a kernel whose bounded wait expired). */
+#define FCS_STATUS_WAIT_PRODUCER 1
+#define FCS_STATUS_WAIT_MMA 2
+#define FCS_STATUS_WAIT_CONSUMER 3
+
+/* Library version, as major * 10000 + minor * 100 + patch. */
+int fcs_version(void);
+
+/* Message of the last failing call made by this thread ("" if none). */
+const char *fcs_last_error(void);
+
+/*
+ * Scratch bytes a call with these sizes needs on the current device.
+ * `sq_rows` is the number of query rows that enter the mean (S, or
+ * min(cls_len, S)).  Returns 0 on invalid sizes.
+ */
+size_t fcs_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_causal);
+
+/*
+ * Batched non-causal column mean: out[b, k] = mean over h and over the first
+ * `rows` query positions of softmax_k(scale * q[b,h,s,:] . k[b,h,k,:]), where
+ * rows = S if cls_n == -1, else min(cls_n, S).
+ * Replaces _flash_colsum_batched(Q, K, scale, CLS_N=-1)
+ * (reference flash_colsum/kernel_noncausal_batched.py:102-125 and its kernel
+ * :9-97); unlike that launcher it writes fp32 and normalises by min(cls_n, S).
+ */
+int fcs_colsum_batched(const void *q, const void *k, float *out, int64_t out_ld,
+                       int B, int H, int S, int D, int dtype,
+                       int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                       int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                       float scale, int cls_n, int h_norm,
+                       void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+/*
+ * Single-sample non-causal column mean (B == 1), out has S elements.
+ * Replaces _flash_colsum_non_batched(Q, K, scale, CLS_N=-1)
+ * (reference flash_colsum/kernel_noncausal.py:95-117 and its kernel :9-93).
+ */
+int fcs_colsum_non_batched(const void *q, const void *k, float *out,
+                           int H, int S, int D, int dtype,
+                           int64_t q_stride_h, int64_t q_stride_s,
+                           int64_t k_stride_h, int64_t k_stride_s,
+                           float scale, int cls_n, int h_norm,
+                           void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+/*
+ * Causal suffix-query column mean (B == 1): q_len queries aligned to the end of
+ * k_len keys; key j is visible to query i iff j <= k_past + i.  k_past < 0
+ * means "infer": max(0, k_len - q_len).  out has k_len elements.
+ * Replaces _flash_colsum_causal(Q, K, scale, K_past=None)
+ * (reference flash_colsum/kernel_causal.py:94-125 and its kernel :7-92); unlike
+ * that kernel it contracts the full head dimension and accepts any q_len.
+ */
+int fcs_colsum_causal(const void *q, const void *k, float *out,
+                      int H, int q_len, int k_len, int D, int dtype,
+                      int64_t q_stride_h, int64_t q_stride_s,
+                      int64_t k_stride_h, int64_t k_stride_s,
+                      float scale, int k_past, int h_norm,
+                      void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FLASH_COLSUM_B200_H_ */

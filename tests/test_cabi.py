@@ -1,0 +1,65 @@
+"""The C-ABI library loads and exports what the header declares; the operator's
+host-side validation behaves like the reference's.  No GPU needed."""
+
+import os
+import re
+
+import pytest
+import torch
+
+import flash_colsum_b200
+from flash_colsum_b200 import _cabi, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_builds_and_exports_every_declared_symbol():
+    lib = _cabi.load()
+    header = open(os.path.join(ROOT, "include", "flash_colsum_b200.h")).read()
+    declared = set(re.findall(r"\b(fcs_[a-z_0-9]+)\s*\(", header))
+    assert declared == set(_cabi.EXPORTED_SYMBOLS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.fcs_version() >= 100
+    assert os.path.samefile(os.path.dirname(build.LIB_PATH), os.path.join(ROOT, "flash_colsum_b200", "_lib"))
+
+
+def test_workspace_query_is_pure_host_arithmetic():
+    lib = _cabi.load()
+    # B*H*ceil(S/128)*128 fp32 rows, no key split for the batched headline shape
+    assert lib.fcs_workspace_bytes(8, 16, 2048, 2048, 64, 0) == 8 * 16 * 2048 * 4
+    assert lib.fcs_workspace_bytes(32, 16, 1, 577, 64, 0) >= 32 * 16 * 128 * 4   # one padded query tile
+    assert lib.fcs_workspace_bytes(1, 32, 512, 131072, 128, 1) > 32 * 512 * 4   # key ranges split
+    assert lib.fcs_workspace_bytes(1, 1, 1, 1, 96, 0) == 0
+    assert lib.fcs_workspace_bytes(0, 1, 1, 1, 64, 0) == 0
+
+
+def test_argument_errors_come_back_as_codes_not_crashes():
+    lib = _cabi.load()
+    rc = lib.fcs_colsum_batched(None, None, None, 0, 1, 1, 1, 64, 0, 64, 64, 64, 64, 64, 64,
+                                1.0, -1, 0, None, 0, None, None)
+    assert rc < 0 and _cabi.last_error()
+    rc = lib.fcs_colsum_causal(None, None, None, 1, 1, 1, 96, 0, 96, 96, 96, 96, 1.0, -1, 0,
+                               None, 0, None, None)
+    assert rc == -2 and "head dimension" in _cabi.last_error()
+
+
+def test_validation_order_and_messages_without_a_gpu():
+    f = flash_colsum_b200.flash_colsum
+    with pytest.raises(ValueError, match="4D"):
+        f(torch.randn(2, 3, 4), torch.randn(2, 3, 4))
+    with pytest.raises(ValueError, match="CUDA"):
+        f(torch.randn(1, 8, 128, 64), torch.randn(1, 8, 128, 64))
+    # the device check comes before the cls_len checks, as in the reference
+    with pytest.raises(ValueError, match="CUDA"):
+        f(torch.randn(1, 8, 128, 64), torch.randn(1, 8, 128, 64), cls_len=0)
+
+
+def test_no_cpu_fallback_in_the_product_package():
+    """The package never imports the CPU checkers."""
+    pkg = os.path.join(ROOT, "flash_colsum_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for fn in files:
+            if fn.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, fn)).read()
+                assert "oracle" not in text, os.path.join(dirpath, fn)

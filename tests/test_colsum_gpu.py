@@ -1,0 +1,231 @@
+"""Parity of the CUDA path with the CPU checker, through the public operator
+(which calls the C ABI).  Bar: rel-L2 <= 1e-3 and max-abs <= 1e-3 of the largest
+column mean, on fp32 outputs, against the checker fed the same inputs."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import MAX_ABS_TOL, REL_L2_TOL
+from flash_colsum_b200.inputs import WORKLOADS, Workload, make_inputs
+from oracle import c_oracle
+from oracle.naive_colsum import naive_colsum_torch, parity_errors
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def fc():
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu-marked tests need a CUDA device")
+    import flash_colsum_b200
+    return flash_colsum_b200
+
+
+def run_gpu(fc, w: Workload, q, k, **kw):
+    out = fc.flash_colsum(q.cuda(), k.cuda(), is_causal=w.is_causal, cls_len=w.cls_len, **kw)
+    torch.cuda.synchronize()
+    assert fc.device_status() == 0, "a device-side wait expired"
+    assert out.dtype == torch.float32
+    return out.cpu().numpy()
+
+
+def assert_parity(got, want, what):
+    rel, mx = parity_errors(got, want)
+    assert np.isfinite(got).all(), what
+    assert rel <= REL_L2_TOL and mx <= MAX_ABS_TOL, (what, rel, mx)
+
+
+def test_golden_cases_match_reference_outputs(fc, golden):
+    """Every stored output of the reference's naive_colsum (fp32 run), 16-bit cases."""
+    cases, arrays = golden
+    ran = 0
+    for w, _ in cases:
+        if w.dtype == "fp32":
+            continue
+        q, k = make_inputs(w)
+        got = run_gpu(fc, w, q, k)
+        assert got.shape == arrays[w.name].shape
+        assert_parity(got, arrays[w.name], w.name)
+        ran += 1
+    assert ran >= 14
+
+
+def test_c1_shape_in_fp16_matches_checker(fc):
+    """The CPU reference config (B2 H4 S256 D64) with inputs rounded to fp16."""
+    w = Workload("c1_fp16", 2, 4, 256, 256, 64, "fp16", seed=0)
+    q, k = make_inputs(w)
+    assert_parity(run_gpu(fc, w, q, k), c_oracle.colsum_c(q, k), "c1")
+
+
+SHAPES = [
+    # B, H, Sq, Sk, D, dtype, causal, cls
+    (4, 8, 512, 512, 64, "fp16", False, None),       # reference test_core.py:21-35
+    (4, 8, 512, 512, 64, "fp16", False, 1),          # reference test_core.py:57-72
+    (1, 4, 1024, 1024, 64, "fp16", False, 2),        # single-sample + cls (test_core.py:76-91, shortened)
+    (1, 4, 2048, 2048, 64, "fp16", False, None),     # single-sample (test_core.py:39-53, shortened)
+    (1, 8, 128, 4096, 128, "fp16", True, None),      # causal (test_core.py:95-109, shortened)
+    (2, 3, 1, 1, 64, "fp16", False, None),           # one key: every mean is 1
+    (1, 2, 7, 7, 128, "bf16", False, None),
+    (1, 2, 129, 129, 64, "bf16", False, None),
+    (3, 5, 383, 383, 128, "fp16", False, None),
+    (1, 2, 1, 300, 64, "fp16", True, None),          # one decode query
+    (1, 2, 257, 257, 128, "bf16", True, None),
+    (1, 3, 200, 1000, 64, "fp16", True, None),
+    (1, 2, 513, 3000, 128, "bf16", True, None),
+    (1, 2, 300, 100, 64, "fp16", True, None),        # keys shorter than queries
+    (2, 2, 640, 640, 64, "fp16", False, 130),        # cls prefix spanning two query tiles
+]
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk,D,dtype,causal,cls", SHAPES)
+def test_shapes_match_checker(fc, B, H, Sq, Sk, D, dtype, causal, cls):
+    w = Workload("t", B, H, Sq, Sk, D, dtype, is_causal=causal, cls_len=cls, seed=Sq + Sk + D)
+    q, k = make_inputs(w)
+    got = run_gpu(fc, w, q, k)
+    want = c_oracle.colsum_c(q, k, is_causal=causal, cls_len=cls)
+    assert_parity(got, want, (B, H, Sq, Sk, D, dtype, causal, cls))
+    np.testing.assert_allclose(got.sum(axis=1), 1.0, atol=2e-3)
+
+
+def test_key_equal_to_query_and_outlier_keys(fc):
+    w = Workload("kq", 2, 4, 512, 512, 64, "fp16", key_is_query=True, seed=21)
+    q, k = make_inputs(w)
+    assert_parity(run_gpu(fc, w, q, k), c_oracle.colsum_c(q, k), "key=query")
+    w = Workload("outl", 1, 4, 256, 4096, 128, "bf16", is_causal=True, key_outliers=True, seed=22)
+    q, k = make_inputs(w)
+    assert_parity(run_gpu(fc, w, q, k), c_oracle.colsum_c(q, k, is_causal=True), "outlier keys")
+
+
+def test_scale_argument_and_large_scores(fc):
+    w = Workload("s", 2, 2, 256, 256, 64, "fp16", seed=31)
+    q, k = make_inputs(w)
+    for scale in (0.5, 0.01, -0.2, 0.0):
+        got = fc.flash_colsum(q.cuda(), k.cuda(), scale=scale).cpu().numpy()
+        assert_parity(got, c_oracle.colsum_c(q, k, scale=scale), f"scale={scale}")
+    assert fc.device_status() == 0
+
+
+def test_zero_queries_give_closed_form(fc):
+    H, Sq, Sk, D = 2, 70, 300, 64
+    q = torch.zeros(1, H, Sq, D, dtype=torch.float16)
+    k = torch.randn(1, H, Sk, D).half()
+    got = fc.flash_colsum(q.cuda(), k.cuda(), is_causal=True).cpu().numpy()[0]
+    k_past = Sk - Sq
+    want = np.zeros(Sk)
+    for r in range(Sq):
+        want[: k_past + r + 1] += 1.0 / (k_past + r + 1)
+    want /= Sq
+    np.testing.assert_allclose(got, want, rtol=2e-5, atol=1e-9)
+    flat = fc.flash_colsum(q[:, :, :, :].cuda(), torch.randn(1, H, Sq, D).half().cuda()).cpu().numpy()
+    np.testing.assert_allclose(flat, 1.0 / Sq, rtol=2e-5)
+
+
+def test_non_contiguous_views_and_out_dtype(fc):
+    g = torch.Generator().manual_seed(41)
+    big_q = torch.randn(2, 3, 200, 128, generator=g).half().cuda()
+    big_k = torch.randn(2, 3, 200, 128, generator=g).half().cuda()
+    q, k = big_q[..., :64], big_k[..., 64:]          # strided rows, offset base
+    want = c_oracle.colsum_c(q.cpu(), k.cpu())
+    assert_parity(fc.flash_colsum(q, k).cpu().numpy(), want, "strided views")
+    qt = big_q.transpose(1, 2)[..., :64].transpose(1, 2)
+    assert_parity(fc.flash_colsum(qt, k).cpu().numpy(), want, "transposed view")
+    half = fc.flash_colsum(q, k, out_dtype=torch.float16)
+    assert half.dtype == torch.float16
+    np.testing.assert_allclose(half.float().cpu().numpy(), want, atol=1e-3, rtol=1e-3)
+    assert fc.device_status() == 0
+
+
+def test_repeated_calls_reuse_scratch_safely(fc):
+    w = Workload("r", 2, 4, 384, 384, 64, "fp16", seed=51)
+    q, k = make_inputs(w)
+    qc, kc = q.cuda(), k.cuda()
+    want = c_oracle.colsum_c(q, k)
+    outs = [fc.flash_colsum(qc, kc) for _ in range(5)]
+    for o in outs:
+        assert_parity(o.cpu().numpy(), want, "repeat")
+    assert fc.device_status() == 0
+
+
+def test_error_handling(fc):
+    """The reference's error cases (tests/test_core.py:112-134), same messages."""
+    dev, dt = torch.device("cuda"), torch.float16
+    Q = torch.randn(2, 8, 128, 64, device=dev, dtype=dt)
+    K = torch.randn(2, 8, 1024, 64, device=dev, dtype=dt)
+    with pytest.raises(ValueError, match="batch size 1"):
+        fc.flash_colsum(Q, K, is_causal=True)
+    with pytest.raises(ValueError, match="CUDA"):
+        fc.flash_colsum(torch.randn(1, 8, 128, 64), torch.randn(1, 8, 128, 64))
+    K2 = torch.randn(2, 8, 256, 64, device=dev, dtype=dt)
+    with pytest.raises(ValueError, match="same shape"):
+        fc.flash_colsum(Q, K2)
+    with pytest.raises(ValueError, match="cls_len"):
+        fc.flash_colsum(Q, Q, cls_len=0)
+    with pytest.raises(ValueError, match="non-causal"):
+        fc.flash_colsum(Q[:1], K[:1], is_causal=True, cls_len=1)
+    with pytest.raises(ValueError, match="4D"):
+        fc.flash_colsum(Q[0], Q[0])
+    with pytest.raises(ValueError, match="head_dim"):
+        fc.flash_colsum(Q[..., :32], Q[..., :32])
+    with pytest.raises(ValueError, match="float16 and bfloat16"):
+        fc.flash_colsum(Q.float(), Q.float())
+
+
+# ------------------------------------------------------------------ full sizes
+def _torch_fp32_reference(q, k, causal, cls_len, head_chunk):
+    """Materialising fp32 evaluation on the GPU, a few heads at a time."""
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    rows = Sq if cls_len is None else min(cls_len, Sq)
+    acc = torch.zeros(B, Sk, dtype=torch.float64, device=q.device)
+    vis = None
+    if causal:
+        vis = (torch.arange(Sk, device=q.device)[None, :]
+               <= (max(0, Sk - Sq) + torch.arange(Sq, device=q.device))[:, None])
+    for h0 in range(0, H, head_chunk):
+        s = torch.matmul(q[:, h0:h0 + head_chunk, :rows].float(),
+                         k[:, h0:h0 + head_chunk].float().transpose(-1, -2)) / D ** 0.5
+        if vis is not None:
+            s = s.masked_fill(~vis[:rows], float("-inf"))
+        acc += torch.softmax(s, dim=-1).sum(dim=(1, 2), dtype=torch.float64)
+    return (acc / (H * rows)).cpu().numpy()
+
+
+@pytest.mark.parametrize("name,chunk", [("c2", 4), ("c2_kq", 4), ("c3", 16), ("c4", 32)])
+def test_headline_workloads_full_size(fc, name, chunk):
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        w = WORKLOADS[name]
+        q, k = make_inputs(w)
+        qc, kc = q.cuda(), k.cuda()
+        got = run_gpu(fc, w, qc, kc)
+        want = _torch_fp32_reference(qc, kc, w.is_causal, w.cls_len, chunk)
+        assert_parity(got, want, name)
+        np.testing.assert_allclose(got.sum(axis=1), 1.0, atol=1e-3)
+        assert (got >= 0).all()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def test_c5_long_context_properties_and_sampled_parity(fc):
+    """131072 keys, 512 suffix queries, outlier keys, bf16: rows sum to one, the
+    last key is seen by the last query only, and a 4-head slice matches the
+    materialising fp32 evaluation."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        w = WORKLOADS["c5"]
+        q, k = make_inputs(w)
+        qc, kc = q.cuda(), k.cuda()
+        got = run_gpu(fc, w, qc, kc)
+        assert got.shape == (1, w.Sk)
+        assert abs(got.sum() - 1.0) < 1e-3 and (got >= 0).all()
+        want = _torch_fp32_reference(qc, kc, True, None, 2)
+        assert_parity(got, want, "c5")
+        sl = Workload("c5_slice", 1, 4, 512, 131072, 128, "bf16", is_causal=True)
+        got4 = run_gpu(fc, sl, qc[:, 8:12], kc[:, 8:12])
+        want4 = _torch_fp32_reference(qc[:, 8:12], kc[:, 8:12], True, None, 2)
+        assert_parity(got4, want4, "c5 heads 8..11")
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev

@@ -1,0 +1,106 @@
+"""The tile schedule, mask rules and planning logic of the CUDA kernels, walked
+on the CPU by ``schedule_emulator.cpp`` (which includes the kernels' own
+header) and compared with the CPU checker."""
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle
+from oracle.naive_colsum import parity_errors
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SRC = os.path.join(HERE, "schedule_emulator.cpp")
+HDR = os.path.join(os.path.dirname(HERE), "flash_colsum_b200", "csrc", "schedule.h")
+LIB = os.path.join(HERE, "_schedule_emulator.so")
+
+
+@pytest.fixture(scope="module")
+def emu():
+    if (not os.path.exists(LIB)
+            or os.path.getmtime(LIB) < max(os.path.getmtime(SRC), os.path.getmtime(HDR))):
+        subprocess.run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-o", LIB, SRC], check=True)
+    lib = ctypes.CDLL(LIB)
+    lib.emulate_colsum.restype = ctypes.c_int
+    lib.emulate_colsum.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 5 + [ctypes.c_float] + \
+        [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_void_p]
+    return lib
+
+
+def run(emu, q, k, scale=None, causal=False, k_past=-1, cls_len=None, h_norm=0, sms=148):
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    if scale is None:
+        scale = 1.0 / D ** 0.5
+    out = np.zeros((B, Sk), dtype=np.float32)
+    nsplit = ctypes.c_int(0)
+    steps = ctypes.c_longlong(0)
+    qc, kc = q.contiguous(), k.contiguous()
+    rc = emu.emulate_colsum(qc.data_ptr(), kc.data_ptr(), out.ctypes.data, B, H, Sq, Sk, D, scale,
+                            int(causal), k_past, -1 if cls_len is None else cls_len, h_norm, sms,
+                            ctypes.addressof(nsplit), ctypes.addressof(steps))
+    assert rc == 0, f"schedule walk failed with code {rc}"
+    return out, nsplit.value, steps.value
+
+
+CASES = [
+    # B, H, Sq, Sk, D, causal, cls, sms
+    (2, 3, 128, 128, 16, False, None, 148),
+    (2, 2, 100, 100, 16, False, None, 148),
+    (1, 2, 577, 577, 8, False, None, 148),
+    (3, 2, 300, 300, 8, False, None, 7),        # few CTAs: ranges cut through key tiles
+    (2, 2, 300, 300, 8, False, 1, 148),
+    (1, 2, 300, 300, 8, False, 200, 5),
+    (1, 2, 40, 40, 8, False, 64, 148),          # cls_len beyond the sequence
+    (1, 3, 128, 1024, 8, True, None, 148),      # key ranges split (few items)
+    (1, 3, 24, 200, 8, True, None, 148),
+    (1, 2, 96, 96, 8, True, None, 148),
+    (1, 2, 64, 40, 8, True, None, 148),         # keys shorter than queries
+    (1, 2, 300, 700, 8, True, None, 148),
+    (1, 2, 300, 700, 8, True, None, 3),
+    (1, 1, 260, 2000, 4, True, None, 148),
+    (1, 2, 129, 129, 8, True, None, 2),
+]
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk,D,causal,cls,sms", CASES)
+def test_schedule_reproduces_the_checker(emu, B, H, Sq, Sk, D, causal, cls, sms):
+    g = torch.Generator().manual_seed(B * 1000 + Sq + Sk)
+    q = torch.randn(B, H, Sq, D, generator=g)
+    k = torch.randn(B, H, Sk, D, generator=g) * 1.5
+    got, nsplit, steps = run(emu, q, k, causal=causal, cls_len=cls, sms=sms)
+    want = c_oracle.colsum_c(q, k, is_causal=causal, cls_len=cls)
+    rel, mx = parity_errors(got, want)
+    assert rel < 2e-5 and mx < 2e-5, (rel, mx, nsplit, steps)
+
+
+def test_key_range_split_is_used_when_items_are_few(emu):
+    q = torch.randn(1, 2, 128, 8)
+    k = torch.randn(1, 2, 128 * 40, 8)
+    got, nsplit, _ = run(emu, q, k, causal=True)
+    assert nsplit > 1
+    want = c_oracle.colsum_c(q, k, is_causal=True)
+    assert parity_errors(got, want)[0] < 2e-5
+
+
+def test_explicit_k_past_and_negative_scale_and_head_norm(emu):
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(1, 2, 50, 8, generator=g)
+    k = torch.randn(1, 2, 400, 8, generator=g)
+    # explicit k_past smaller than Sk - Sq: trailing keys are visible to no query
+    got, _, _ = run(emu, q, k, causal=True, k_past=100)
+    want = c_oracle.colsum_c(q, k[:, :, :150], is_causal=True)
+    assert parity_errors(got[:, :150], want)[0] < 2e-5
+    assert np.all(got[:, 150:] == 0)
+    # negative scale
+    got, _, _ = run(emu, q, k[:, :, :50], scale=-0.3)
+    want = c_oracle.colsum_c(q, k[:, :, :50], scale=-0.3)
+    assert parity_errors(got, want)[0] < 2e-5
+    # normalising by a global head count halves the result of a two-head shard
+    got4, _, _ = run(emu, q, k[:, :, :50], h_norm=4)
+    got2, _, _ = run(emu, q, k[:, :, :50])
+    np.testing.assert_allclose(got4 * 2, got2, rtol=1e-5)
