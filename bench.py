@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the attention column mean on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one `flash_colsum` call over one batch of seeded synthetic input.
+At one GPU the workload is the batched non-causal headline shape (B=8, H=16,
+S=2048, D=64, fp16).  At N GPUs each rank runs that shape on its own batch shard
+(weak scaling, no collective: the output is batch-sharded), and the JSON line
+also carries the long-context causal shape (131072 keys, 512 suffix queries,
+D=128, bf16) with its 32 heads split over the ranks and one NCCL all-reduce of
+the fp32 per-key partials (strong scaling) under "causal_long_context".
+
+Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
+the reference's materialising implementation on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from flash_colsum_b200.inputs import WORKLOADS, Workload, make_inputs  # noqa: E402
+
+METRIC = "colsum_effective_tflops"
+UNIT = "TFLOP/s"
+L2_FLUSH_BYTES = 256 << 20
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"tflops": float(p["bf16_tflops"]), "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def load_traffic(kernel: str):
+    """DRAM bytes per launch of `kernel` from the committed ncu summary, if any."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        return json.load(f).get(kernel)
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def workload_call(fc, w: Workload, q, k, h_norm_fn=None):
+    return fc.flash_colsum(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
+
+
+def time_steps(fn, steps, warmup, flush_buf, barrier=None):
+    """Per-step CUDA-event timing with an untimed L2 flush before every step."""
+    for _ in range(warmup):
+        flush_buf.zero_()
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush_buf.zero_()
+        starts[i].record()
+        fn()
+        ends[i].record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return [s.elapsed_time(e) for s, e in zip(starts, ends)]
+
+
+def cpu_port_tflops(w: Workload, budget_s: float, batch_entries: int):
+    """The CPU restatement of the reference on a bounded sample of `w`."""
+    from oracle.naive_colsum import naive_colsum_torch
+    sample = Workload(w.name + "_sample", min(batch_entries, w.B), w.H, w.Sq, w.Sk, w.D, w.dtype,
+                      w.is_causal, w.cls_len, w.key_outliers, w.key_is_query, w.seed)
+    q, k = make_inputs(sample)
+    q, k = q.float(), k.float()
+    naive_colsum_torch(q, k, is_causal=w.is_causal, cls_len=w.cls_len)   # warm-up
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while True:
+        t0 = time.perf_counter()
+        naive_colsum_torch(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() > t_end or len(times) >= 50:
+            break
+    best = statistics.median(times)
+    return {"value": sample.flop / best / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": (f"{sample.B} of {w.B} batch entries of {w.name} in fp32, "
+                       f"median of {len(times)} calls of {best * 1e3:.1f} ms; host has "
+                       f"{os.cpu_count()} logical cores")}, best, sample
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = WORKLOADS["c2"]
+    from oracle.naive_colsum import naive_colsum_torch
+    sample = Workload("c2_sample", 1, w.H, w.Sq, w.Sk, w.D, w.dtype, seed=w.seed)
+    q, k = make_inputs(sample)
+    q, k = q.float(), k.float()
+    for _ in range(max(1, min(args.warmup, 2))):
+        naive_colsum_torch(q, k)
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        naive_colsum_torch(q, k)
+        times.append(time.perf_counter() - t0)
+    mean_s = sum(times) / len(times)
+    value = sample.flop / mean_s / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean_s * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
+        "data": "synthetic",
+        "config": {"workload": "c2: non-causal B=8 H=16 S=2048 D=64", "step": "one batch entry (B=1) per step",
+                   "l2": "host run"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": "1 of 8 batch entries per step, CPU restatement of naive_colsum in fp32"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-budget-s", type=float, default=12.0)
+    ap.add_argument("--skip-long-context", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    import flash_colsum_b200 as fc
+    from flash_colsum_b200 import _cabi
+    from flash_colsum_b200.sharded import flash_colsum_head_sharded, shard_range
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    peaks = load_peaks()
+    flush_buf = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+    # ------------------------------------------------------------ headline workload
+    w = WORKLOADS["c2"]
+    wr = Workload(w.name, w.B, w.H, w.Sq, w.Sk, w.D, w.dtype, seed=w.seed + rank)   # this rank's batch shard
+    q_host, k_host = make_inputs(wr)
+    q_host, k_host = q_host.pin_memory(), k_host.pin_memory()
+    q, k = q_host.to(dev), k_host.to(dev)
+    plan = _cabi.plan_info(w.B, w.H, w.Sq, w.Sk, False)
+    launches_per_call = 2 + (1 if plan["nsplit"] > 1 else 0)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    times = time_steps(lambda: fc.flash_colsum(q, k), args.steps, args.warmup, flush_buf, barrier)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_local = sum(times) / len(times)
+    ms_step = max_over_ranks(ms_local)
+    value = w.flop * world / (ms_step * 1e-3) / 1e12
+    assert fc.device_status() == 0, "a device-side wait expired during the timed region"
+
+    # per-kernel durations (events recorded by the library around each pass)
+    _cabi.set_profiling(True)
+    stats_ms, col_ms = [], []
+    for _ in range(max(5, min(args.steps, 20))):
+        flush_buf.zero_()
+        fc.flash_colsum(q, k)
+        a, _, c = _cabi.last_pass_ms()
+        stats_ms.append(a)
+        col_ms.append(c)
+    _cabi.set_profiling(False)
+    col_avg = sum(col_ms) / len(col_ms)
+    stats_avg = sum(stats_ms) / len(stats_ms)
+    pass_flop = w.flop / 2.0
+    achieved = pass_flop / (col_avg * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "kernel": "colsum_stream_kernel<64, column pass>",
+        "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
+        "peak_source": f"{peaks['source']} bf16 burst", "traffic": load_traffic("colsum_pass_c2"),
+        "launch_ms": col_avg, "flop_per_launch": pass_flop,
+        "other_kernels": {"statistics pass": {"launch_ms": stats_avg,
+                                              "achieved": pass_flop / (stats_avg * 1e-3) / 1e12}},
+    }
+
+    # ------------------------------------------------------------ end to end from host memory
+    def e2e_step():
+        qd = q_host.to(dev, non_blocking=True)
+        kd = k_host.to(dev, non_blocking=True)
+        return fc.flash_colsum(qd, kd).cpu()
+
+    e2e_times = []
+    for i in range(3 + max(5, args.steps // 2)):
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        e2e_step()
+        torch.cuda.synchronize()
+        if i >= 3:
+            e2e_times.append((time.perf_counter() - t0) * 1e3)
+    e2e_ms = max_over_ranks(sum(e2e_times) / len(e2e_times))
+    e2e = {"value": w.flop * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": int(q_host.numel() * 2 + k_host.numel() * 2),
+           "d2h_bytes_per_step": int(w.B * w.Sk * 4)}
+
+    # ------------------------------------------------------------ long-context causal, heads sharded
+    long_ctx = None
+    if not args.skip_long_context:
+        w5 = WORKLOADS["c5"]
+        lo, hi = shard_range(w5.H, world, rank)
+        g = torch.Generator(device=dev).manual_seed(1234)
+        # generated on the device: 1 GiB of keys per 32 heads; same distribution as the CPU generator
+        q5 = torch.randn(1, hi - lo, w5.Sq, w5.D, generator=g, device=dev, dtype=torch.float32)
+        k5 = torch.randn(1, hi - lo, w5.Sk, w5.D, generator=g, device=dev, dtype=torch.float32)
+        k5 *= (torch.rand(w5.Sk, generator=g, device=dev) * 1.5 + 0.5)[None, None, :, None]
+        q5, k5 = q5.to(torch.bfloat16), k5.to(torch.bfloat16)
+
+        def long_step():
+            return flash_colsum_head_sharded(q5, k5, w5.H, is_causal=True)
+
+        t5 = time_steps(long_step, max(5, args.steps // 2), 3, flush_buf, barrier)
+        ms5 = max_over_ranks(sum(t5) / len(t5))
+        out5 = long_step()
+        torch.cuda.synchronize()
+        long_ctx = {"workload": "c5: causal H=32 Q=512 K=131072 D=128 bf16, outlier keys",
+                    "parallelism": f"heads sharded over {world} GPU(s), one NCCL all-reduce of (1,131072) fp32"
+                    if world > 1 else "single GPU",
+                    "scaling": "strong", "ms_per_call": ms5, "value": w5.flop / (ms5 * 1e-3) / 1e12,
+                    "unit": UNIT, "frac_of_peak": w5.flop / (ms5 * 1e-3) / 1e12 / peaks["tflops"],
+                    "row_sum": float(out5.sum().item())}
+        del q5, k5
+    assert fc.device_status() == 0
+
+    # ------------------------------------------------------------ CPU baseline (rank 0, one GPU only)
+    cpu = None
+    if rank == 0 and world == 1:
+        cpu, _, _ = cpu_port_tflops(w, args.cpu_budget_s, 1)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+            "config": {"workload": "c2: non-causal B=8 H=16 S=2048 D=64 fp16 per GPU",
+                       "global_batch": w.B * world,
+                       "parallelism": "single GPU" if world == 1 else f"batch sharded over {world} GPUs, no collective",
+                       "flop_count": "4*B*H*Sq*Sk*D (two passes)",
+                       "l2": "256 MiB buffer written before every timed step (inputs are 64 MiB)",
+                       "plan": plan},
+            "frac_of_tensor_peak": value / world / peaks["tflops"],
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": launches_per_call * args.steps,
+            "clocks": clocks,
+            "causal_long_context": long_ctx,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

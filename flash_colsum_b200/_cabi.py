@@ -12,6 +12,7 @@ from . import build as _build
 EXPORTED_SYMBOLS = (
     "fcs_version", "fcs_last_error", "fcs_workspace_bytes",
     "fcs_colsum_batched", "fcs_colsum_non_batched", "fcs_colsum_causal",
+    "fcs_set_profiling", "fcs_last_pass_ms", "fcs_plan_info",
 )
 
 FCS_OK = 0
@@ -60,9 +61,39 @@ def load() -> ctypes.CDLL:
     lib.fcs_colsum_causal.restype = _i
     lib.fcs_colsum_causal.argtypes = [_p, _p, _p, _i, _i, _i, _i, _i] + [_i64] * 4 + \
         [_f, _i, _i, _p, _sz, _p, _p]
+    lib.fcs_set_profiling.restype = _i
+    lib.fcs_set_profiling.argtypes = [_i]
+    lib.fcs_last_pass_ms.restype = _i
+    lib.fcs_last_pass_ms.argtypes = [_p, _p, _p]
+    lib.fcs_plan_info.restype = _i
+    lib.fcs_plan_info.argtypes = [_i] * 5 + [_p] * 4
     _lib = lib
     return lib
 
 
 def last_error() -> str:
     return load().fcs_last_error().decode("utf-8", "replace")
+
+
+def set_profiling(enabled: bool) -> None:
+    load().fcs_set_profiling(int(bool(enabled)))
+
+
+def last_pass_ms():
+    """(statistics, merge, column) pass durations in ms of the last profiled call."""
+    vals = [ctypes.c_float(0.0) for _ in range(3)]
+    rc = load().fcs_last_pass_ms(*[ctypes.addressof(v) for v in vals])
+    if rc != FCS_OK:
+        raise RuntimeError(last_error())
+    return tuple(float(v.value) for v in vals)
+
+
+def plan_info(B: int, H: int, sq_rows: int, Sk: int, is_causal: bool) -> dict:
+    nsplit, sms = ctypes.c_int(0), ctypes.c_int(0)
+    items, steps = ctypes.c_longlong(0), ctypes.c_longlong(0)
+    rc = load().fcs_plan_info(B, H, sq_rows, Sk, int(is_causal), ctypes.addressof(nsplit),
+                              ctypes.addressof(items), ctypes.addressof(steps), ctypes.addressof(sms))
+    if rc != FCS_OK:
+        raise RuntimeError("fcs_plan_info rejected the sizes")
+    return {"nsplit": nsplit.value, "stats_items": items.value, "colsum_steps": steps.value,
+            "sms": sms.value}

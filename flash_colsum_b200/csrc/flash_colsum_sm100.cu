@@ -434,6 +434,28 @@ static int make_tensor_map(CUtensorMap* m, const void* base, int dtype, int B, i
     return FCS_OK;
 }
 
+// Optional per-pass timing: when enabled, events are recorded on the caller's
+// stream around each kernel of a call.
+struct PassTimers {
+    bool ready = false;
+    bool recorded = false;
+    cudaEvent_t ev[4];
+};
+static bool g_profiling = false;
+static PassTimers g_timers[64];
+
+static PassTimers* timers_for_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    PassTimers& t = g_timers[dev];
+    if (!t.ready) {
+        for (int i = 0; i < 4; ++i)
+            if (cudaEventCreate(&t.ev[i]) != cudaSuccess) return nullptr;
+        t.ready = true;
+    }
+    return &t;
+}
+
 template <int D, int MODE>
 static cudaError_t launch_stream(const CUtensorMap& tq, const CUtensorMap& tk, const Problem& p, int grid,
                                  cudaStream_t stream) {
@@ -516,10 +538,13 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
     const int grid1 = (int)(p.stats_items < sms ? p.stats_items : sms);
     const int grid2 = (int)(p.steps_total < sms ? p.steps_total : sms);
+    PassTimers* tm = g_profiling ? timers_for_current_device() : nullptr;
+    if (tm) { tm->recorded = false; cudaEventRecord(tm->ev[0], stream); }
     cudaError_t e;
     e = (D == 64) ? launch_stream<64, MODE_STATS>(tq, tk, p, grid1, stream)
                   : launch_stream<128, MODE_STATS>(tq, tk, p, grid1, stream);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics pass launch failed: %s", cudaGetErrorString(e));
+    if (tm) cudaEventRecord(tm->ev[1], stream);
     if (p.nsplit > 1) {
         const long long n = (long long)B * H * p.NQ * TILE;
         int blocks = (int)((n + 255) / 256);
@@ -528,9 +553,11 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
         e = cudaGetLastError();
         if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics merge launch failed: %s", cudaGetErrorString(e));
     }
+    if (tm) cudaEventRecord(tm->ev[2], stream);
     e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tq, tk, p, grid2, stream)
                   : launch_stream<128, MODE_COLSUM>(tq, tk, p, grid2, stream);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "column pass launch failed: %s", cudaGetErrorString(e));
+    if (tm) { cudaEventRecord(tm->ev[3], stream); tm->recorded = true; }
     return FCS_OK;
 }
 
@@ -544,6 +571,43 @@ extern "C" {
 int fcs_version(void) { return 100; }
 
 const char* fcs_last_error(void) { return fcs::g_err; }
+
+int fcs_set_profiling(int enabled) {
+    fcs::g_profiling = enabled != 0;
+    return FCS_OK;
+}
+
+int fcs_last_pass_ms(float* stats_ms, float* merge_ms, float* colsum_ms) {
+    fcs::g_err[0] = 0;
+    fcs::PassTimers* tm = fcs::timers_for_current_device();
+    if (!tm || !tm->recorded)
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "no profiled call has been made on this device");
+    cudaError_t e = cudaEventSynchronize(tm->ev[3]);
+    if (e != cudaSuccess) return fcs::fail(FCS_ERR_CUDA, "event synchronize failed: %s", cudaGetErrorString(e));
+    float a = 0.f, b = 0.f, c = 0.f;
+    cudaEventElapsedTime(&a, tm->ev[0], tm->ev[1]);
+    cudaEventElapsedTime(&b, tm->ev[1], tm->ev[2]);
+    cudaEventElapsedTime(&c, tm->ev[2], tm->ev[3]);
+    if (stats_ms) *stats_ms = a;
+    if (merge_ms) *merge_ms = b;
+    if (colsum_ms) *colsum_ms = c;
+    return FCS_OK;
+}
+
+int fcs_plan_info(int B, int H, int sq_rows, int Sk, int is_causal, int* nsplit, long long* stats_items,
+                  long long* colsum_steps, int* sms) {
+    if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0) return FCS_ERR_INVALID_ARGUMENT;
+    fcs::Problem p;
+    memset(&p, 0, sizeof(p));
+    const int k_past = Sk > sq_rows ? Sk - sq_rows : 0;
+    const int n_sm = fcs::num_sms();
+    fcs::plan(p, B, H, sq_rows, Sk, is_causal ? 1 : 0, k_past, n_sm);
+    if (nsplit) *nsplit = p.nsplit;
+    if (stats_items) *stats_items = p.stats_items;
+    if (colsum_steps) *colsum_steps = p.steps_total;
+    if (sms) *sms = n_sm;
+    return FCS_OK;
+}
 
 size_t fcs_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_causal) {
     if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0 || (D != 64 && D != 128)) return 0;

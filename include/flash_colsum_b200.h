@@ -105,6 +105,28 @@ int fcs_colsum_causal(const void *q, const void *k, float *out,
                       float scale, int k_past, int h_norm,
                       void *workspace, size_t workspace_bytes, int *status, void *stream);
 
+/*
+ * Measurement aids.  No counterpart in the reference, which times whole calls
+ * with a host clock (benchmarks/benchmark_colsum.py:42-56).
+ *
+ * fcs_set_profiling(1) makes every later fcs_colsum_* call record CUDA events
+ * on its stream around each of its kernels; fcs_last_pass_ms() waits for the
+ * last such call on the current device and returns the duration of the
+ * statistics pass, of the key-range merge (0 when the call needed none) and of
+ * the column pass.  Off by default; not thread-safe.
+ */
+int fcs_set_profiling(int enabled);
+int fcs_last_pass_ms(float *stats_ms, float *merge_ms, float *colsum_ms);
+
+/*
+ * How a call with these sizes is decomposed on the current device: key ranges
+ * per query tile in the statistics pass, its work items, the 128x128 score
+ * tiles of the column pass, and the SM count used for planning.  Host
+ * arithmetic only.
+ */
+int fcs_plan_info(int B, int H, int sq_rows, int Sk, int is_causal, int *nsplit,
+                  long long *stats_items, long long *colsum_steps, int *sms);
+
 #ifdef __cplusplus
 }
 #endif
