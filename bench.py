@@ -193,6 +193,49 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def kernel_only(args, fc, _cabi, dev, flush_buf, peaks):
+    """Device passes of one workload, per-pass durations; one JSON line."""
+    w = WORKLOADS[args.workload]
+    if args.batch > 0:
+        w = Workload(w.name, args.batch, w.H, w.Sq, w.Sk, w.D, w.dtype, w.is_causal, w.cls_len,
+                     w.key_outliers, w.key_is_query, w.seed)
+    g = torch.Generator(device=dev).manual_seed(w.seed)
+    q = torch.randn(w.B, w.H, w.Sq, w.D, generator=g, device=dev).to(w.torch_dtype)
+    k = torch.randn(w.B, w.H, w.Sk, w.D, generator=g, device=dev).to(w.torch_dtype)
+
+    def call():
+        return fc.flash_colsum(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
+
+    _cabi.set_profiling(True)
+    for _ in range(args.warmup):
+        flush_buf.zero_()
+        call()
+    torch.cuda.synchronize()
+    rows = []
+    for _ in range(args.steps):
+        flush_buf.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        call()
+        e1.record()
+        torch.cuda.synchronize()
+        rows.append((e0.elapsed_time(e1),) + _cabi.last_pass_ms())
+    _cabi.set_profiling(False)
+    n = len(rows)
+    total, st, mg, col = (sum(r[i] for r in rows) / n for i in range(4))
+    rows_used = w.rows_averaged
+    print(json.dumps({
+        "workload": w.name, "B": w.B, "H": w.H, "Sq": w.Sq, "Sk": w.Sk, "D": w.D, "dtype": w.dtype,
+        "causal": w.is_causal, "cls_len": w.cls_len, "steps": n, "ms_per_call": total,
+        "stats_ms": st, "merge_ms": mg, "colsum_ms": col,
+        "tflops_nominal": w.flop / (total * 1e-3) / 1e12,
+        "tflops_rows_used": w.flop_rows_used / (total * 1e-3) / 1e12,
+        "min_bytes_gbs": w.min_bytes / (total * 1e-3) / 1e9,
+        "frac_of_tensor_peak": w.flop / (total * 1e-3) / 1e12 / peaks["tflops"],
+        "plan": _cabi.plan_info(w.B, w.H, rows_used, w.Sk, w.is_causal),
+        "status": fc.device_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -201,6 +244,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
     ap.add_argument("--skip-long-context", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="time only the device passes of --workload (used for ncu captures)")
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="override the batch size (kernel-only mode)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -239,6 +286,10 @@ def main():
 
     peaks = load_peaks()
     flush_buf = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+    if args.kernel_only:
+        kernel_only(args, fc, _cabi, dev, flush_buf, peaks)
+        return
 
     # ------------------------------------------------------------ headline workload
     w = WORKLOADS["c2"]
