@@ -561,6 +561,31 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     return FCS_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Built-in scratch for callers that have no device allocator to draw from.
+// One copy lives in every device that loads this library, for the life of the
+// process.  The name below is a host-side handle in host code, not a device
+// address: the address is looked up per device with cudaGetSymbolAddress.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[FCS_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_address(void** out_ptr) {
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(FCS_ERR_UNSUPPORTED, "device ordinal %d is out of range", dev);
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fail(FCS_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        cached[dev] = ptr;
+    }
+    *out_ptr = cached[dev];
+    return FCS_OK;
+}
+
 }  // namespace fcs
 
 // ---------------------------------------------------------------------------
@@ -643,6 +668,29 @@ int fcs_colsum_causal(const void* q, const void* k, float* out, int H, int q_len
     return fcs::colsum_impl(q, k, out, k_len, 1, H, q_len, k_len, D, dtype, q_stride_h * H, q_stride_h,
                             q_stride_s, k_stride_h * H, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm,
                             workspace, workspace_bytes, status, stream);
+}
+
+int fcs_colsum_batched_static_scratch(const void* q, const void* k, float* out, int64_t out_ld, int B, int H,
+                                      int S, int D, int dtype, int64_t q_stride_b, int64_t q_stride_h,
+                                      int64_t q_stride_s, int64_t k_stride_b, int64_t k_stride_h,
+                                      int64_t k_stride_s, float scale, int cls_n, int h_norm, int* status,
+                                      void* stream) {
+    fcs::g_err[0] = 0;
+    if (B <= 0 || H <= 0 || S <= 0 || (D != 64 && D != 128))
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "bad sizes (B=%d H=%d S=%d D=%d)", B, H, S, D);
+    const int rows = (cls_n > 0 && cls_n < S) ? cls_n : S;
+    const size_t need = fcs_workspace_bytes(B, H, rows, S, D, 0);
+    if (need == 0 || need > (size_t)FCS_STATIC_SCRATCH_BYTES)
+        return fcs::fail(FCS_ERR_WORKSPACE,
+                         "this call needs %zu bytes of scratch but the built-in scratch holds %zu; "
+                         "use fcs_colsum_batched with a caller-provided workspace",
+                         need, (size_t)FCS_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    const int rc = fcs::static_scratch_address(&scratch);
+    if (rc != FCS_OK) return rc;
+    return fcs::colsum_impl(q, k, out, out_ld, B, H, S, S, D, dtype, q_stride_b, q_stride_h, q_stride_s,
+                            k_stride_b, k_stride_h, k_stride_s, scale, 0, 0, cls_n, h_norm, scratch,
+                            (size_t)FCS_STATIC_SCRATCH_BYTES, status, stream);
 }
 
 }  // extern "C"

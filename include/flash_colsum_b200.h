@@ -106,6 +106,41 @@ int fcs_colsum_causal(const void *q, const void *k, float *out,
                       void *workspace, size_t workspace_bytes, int *status, void *stream);
 
 /*
+ * Batched non-causal column mean for callers that cannot give the library a
+ * workspace.  It has no counterpart in the reference.
+ *
+ * Some hosts of this library have no device allocator to call: a plugin inside
+ * an inference server that handed all device memory to its own arena at start
+ * up, or a service bound through FFI (C, Go, Rust) that only ever holds the
+ * input and output buffers it was given.  For them the scratch of this entry
+ * point is a fixed array of FCS_STATIC_SCRATCH_BYTES built into the library's
+ * device image, so the call allocates nothing: no cudaMalloc, no cudaFree, no
+ * allocating library routine.  Every device that loads the library holds that
+ * array until the process exits.
+ *
+ * Same arguments and result as fcs_colsum_batched, minus the workspace.
+ *   - Limit: the call must need no more than FCS_STATIC_SCRATCH_BYTES of
+ *     scratch (fcs_workspace_bytes(B, H, rows, S, D, 0)); larger problems are
+ *     rejected with FCS_ERR_WORKSPACE and a message, nothing is launched.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and caches it.  Make
+ *     that first call outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the
+ *     previous call left there.  Each call rewrites every scratch value it
+ *     later reads and clears `out` itself, so back-to-back calls on one stream
+ *     are independent; two calls that overlap on the GPU (different streams,
+ *     or different host threads without ordering) race on the array and give
+ *     wrong results.
+ */
+#define FCS_STATIC_SCRATCH_BYTES (4u << 20)
+int fcs_colsum_batched_static_scratch(const void *q, const void *k, float *out, int64_t out_ld,
+                                      int B, int H, int S, int D, int dtype,
+                                      int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                      int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                                      float scale, int cls_n, int h_norm,
+                                      int *status, void *stream);
+
+/*
  * Measurement aids.  No counterpart in the reference, which times whole calls
  * with a host clock (benchmarks/benchmark_colsum.py:42-56).
  *
