@@ -37,8 +37,14 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB_PATH
-    if _build.is_stale():
+    path = os.environ.get("FLASH_COLSUM_B200_LIB")   # an explicit build to load instead
+    if path:
+        if not os.path.exists(path):
+            raise LibraryMissing(f"FLASH_COLSUM_B200_LIB={path} does not exist")
+    elif not _build.is_stale():
+        path = _build.LIB_PATH
+    else:
+        path = _build.LIB_PATH
         try:
             path = _build.build()
         except Exception as exc:  # no nvcc on this machine

@@ -29,25 +29,43 @@ namespace fcs {
 
 constexpr int NUM_TBUF = 4;        // accumulator buffers of 128 tensor-memory columns
 constexpr int TMEM_COLS = 512;
-constexpr int CONSUMER_WARPS = 8;  // two groups of four warps; a group owns lanes 0..127
-constexpr int PRODUCER_WARP = 8;
-constexpr int MMA_WARP = 9;
-constexpr int THREADS = 320;
+#ifndef FCS_NS64
+#define FCS_NS64 6
+#endif
+#ifndef FCS_EXP
+#define FCS_EXP 0
+#endif
+constexpr int NUM_LSE = 8;         // per-query-tile log-sum-exp vectors in flight (column pass)
+// Consumer warps come in groups of four (a group covers the 128 tensor-memory
+// lanes).  GROUPS_PER_TILE groups share one accumulator tile, each taking an
+// equal run of its columns; TILE_SLOTS tiles are being consumed at a time.
+constexpr int CONSUMER_GROUPS = 4;
+constexpr int GROUPS_PER_TILE = 2;
+constexpr int TILE_SLOTS = CONSUMER_GROUPS / GROUPS_PER_TILE;
+constexpr int GROUP_COLS = 128 / GROUPS_PER_TILE;
+constexpr int CONSUMER_WARPS = 4 * CONSUMER_GROUPS;
+constexpr int CONSUMER_THREADS = 32 * CONSUMER_WARPS;
+constexpr int PRODUCER_WARP = CONSUMER_WARPS;
+constexpr int MMA_WARP = CONSUMER_WARPS + 1;
+constexpr int THREADS = 32 * (CONSUMER_WARPS + 2);
+static_assert(GROUP_COLS % 64 == 0, "a group consumes whole 64-column blocks");
 
 template <int D>
 struct Layout {
     static constexpr int SLABS = D / 64;              // 64-element (128-byte) column slabs
     static constexpr int SLAB_BYTES = TILE * 128;
     static constexpr int TILE_BYTES = SLABS * SLAB_BYTES;
-    static constexpr int NS = (D == 64) ? 6 : 4;      // streamed-operand stages
+    static constexpr int NS = (D == 64) ? FCS_NS64 : 4;      // streamed-operand stages
     static constexpr int A_OFF = 0;
     static constexpr int B_OFF = 2 * TILE_BYTES;
-    static constexpr int BAR_OFF = B_OFF + NS * TILE_BYTES;
+    static constexpr int LSE_OFF = B_OFF + NS * TILE_BYTES;   // NUM_LSE slots of 128 floats
+    static constexpr int BAR_OFF = LSE_OFF + NUM_LSE * TILE * 4;
     // barriers: a_full[2] a_empty[2] b_full[NS] b_empty[NS] t_full[4] t_empty[4] merge[2]
-    static constexpr int NUM_BARS = 4 + 2 * NS + 2 * NUM_TBUF + 2;
+    //           l_full[NUM_LSE] l_empty[NUM_LSE]
+    static constexpr int NUM_BARS = 4 + 2 * NS + 2 * NUM_TBUF + 2 + 2 * NUM_LSE;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;        // tmem address, abort flag
-    static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // float2[2][128]
-    static constexpr int TOTAL = MERGE_OFF + 2 * TILE * 8;
+    static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // float2[2][groups-1][128]
+    static constexpr int TOTAL = MERGE_OFF + 2 * (CONSUMER_GROUPS - 1) * TILE * 8;
     static constexpr int DYN_BYTES = TOTAL + 1024;    // slack to align the base to 1024
 };
 
@@ -60,35 +78,44 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return r;
 }
 
-// Online (max, sum) update of one query row with 32 more scores.
-// `last_valid`: columns 0..last_valid of this chunk are visible (>= 31: all).
+// Online (max, sum) update of one query row with 64 more scores (two 32-column
+// register blocks).  `last_valid`: columns 0..last_valid are visible (>= 63: all).
 template <bool MASKED>
-__device__ __forceinline__ void stats_chunk(const uint32_t (&r)[32], int last_valid, float c,
-                                            float& m, float& l) {
-    float s[32];
+__device__ __forceinline__ void stats_block64(const uint32_t (&ra)[32], const uint32_t (&rb)[32],
+                                              int last_valid, float c, float& m, float& l) {
+    float s[64];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-        s[j] = __uint_as_float(r[j]);
-        if (MASKED) s[j] = (j <= last_valid) ? s[j] : -INFINITY;
+        s[j] = __uint_as_float(ra[j]);
+        s[32 + j] = __uint_as_float(rb[j]);
+    }
+    if (MASKED) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) s[j] = (j <= last_valid) ? s[j] : -INFINITY;
     }
     float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
+    float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-    for (int j = 6; j < 30; j += 4) {
+    for (int j = 12; j < 60; j += 8) {
         m0 = max3(m0, s[j], s[j + 1]);
         m1 = max3(m1, s[j + 2], s[j + 3]);
+        m2 = max3(m2, s[j + 4], s[j + 5]);
+        m3 = max3(m3, s[j + 6], s[j + 7]);
     }
-    float cm = max3(m0, m1, fmaxf(s[30], s[31]));
-    float scaled = (cm == -INFINITY) ? -INFINITY : cm * c;
+    m0 = max3(m0, s[60], s[61]);
+    m1 = max3(m1, s[62], s[63]);
+    const float cm = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+    const float scaled = (cm == -INFINITY) ? -INFINITY : cm * c;
     const float m_new = fmaxf(m, scaled);
     const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
     l *= ex2_approx(m - m_safe);
     m = m_new;
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
+    for (int j = 0; j < 64; j += 4) {
         float t0 = fmaf(s[j], c, -m_safe), t1 = fmaf(s[j + 1], c, -m_safe);
         float t2 = fmaf(s[j + 2], c, -m_safe), t3 = fmaf(s[j + 3], c, -m_safe);
-        if (MASKED) {
+        if (MASKED) {   // c may be 0 and s -inf: select after the multiply
             t0 = (j <= last_valid) ? t0 : -INFINITY;
             t1 = (j + 1 <= last_valid) ? t1 : -INFINITY;
             t2 = (j + 2 <= last_valid) ? t2 : -INFINITY;
@@ -100,11 +127,12 @@ __device__ __forceinline__ void stats_chunk(const uint32_t (&r)[32], int last_va
     l += (a0 + a1) + (a2 + a3);
 }
 
-// Add exp2(c*s - lse[q]) of 32 query columns into a key's accumulators.
+// Add exp2(c*s - lse[q]) of 32 query columns into a key's accumulators.  `nl`
+// points at the 32 values -(lse) of these columns in shared memory.
 // `first_valid`: columns >= first_valid of this chunk are visible (<= 0: all).
 template <bool MASKED>
-__device__ __forceinline__ void colsum_chunk(const uint32_t (&r)[32], const float4 (&nl)[8],
-                                             int first_valid, float c, float (&acc)[4]) {
+__device__ __forceinline__ void colsum_chunk(const uint32_t (&r)[32], const float4* nl, int first_valid,
+                                             float c, float (&acc)[4]) {
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
         const float4 n = nl[j >> 2];
@@ -120,6 +148,62 @@ __device__ __forceinline__ void colsum_chunk(const uint32_t (&r)[32], const floa
         }
         acc[0] += ex2_approx(t0); acc[1] += ex2_approx(t1);
         acc[2] += ex2_approx(t2); acc[3] += ex2_approx(t3);
+    }
+}
+
+// A group's GROUP_COLS columns of one accumulator tile, 64 at a time.
+// `taddr`, `lim`, `thr` and `nl` are relative to the group's first column.
+#ifndef FCS_EXP
+#define FCS_EXP 0
+#endif
+template <bool MASKED>
+__device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, float& m, float& l) {
+#if FCS_EXP == 4
+    return;
+#endif
+    uint32_t ra[32], rb[32];
+#pragma unroll
+    for (int blk = 0; blk < GROUP_COLS / 64; ++blk) {
+#if FCS_EXP == 2
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { ra[j] = __float_as_uint(m + j); rb[j] = __float_as_uint(l - j); }
+#else
+        tmem_ld_x32(taddr + blk * 64, ra);
+        tmem_ld_x32(taddr + blk * 64 + 32, rb);
+        tmem_ld_wait(ra);
+        tmem_ld_wait(rb);
+#endif
+#if FCS_EXP == 1
+        l += __uint_as_float(ra[0]) + __uint_as_float(rb[31]);
+#else
+        stats_block64<MASKED>(ra, rb, lim - blk * 64, c, m, l);
+#endif
+    }
+}
+template <bool MASKED>
+__device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, int thr, float c,
+                                            float (&acc)[4]) {
+#if FCS_EXP == 4
+    return;
+#endif
+    uint32_t ra[32], rb[32];
+#pragma unroll
+    for (int blk = 0; blk < GROUP_COLS / 64; ++blk) {
+#if FCS_EXP == 2
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { ra[j] = __float_as_uint(acc[0] + j); rb[j] = __float_as_uint(acc[1] - j); }
+#else
+        tmem_ld_x32(taddr + blk * 64, ra);
+        tmem_ld_x32(taddr + blk * 64 + 32, rb);
+        tmem_ld_wait(ra);
+        tmem_ld_wait(rb);
+#endif
+#if FCS_EXP == 1
+        acc[0] += __uint_as_float(ra[0]) + __uint_as_float(rb[31]) + nl[blk].x;
+#else
+        colsum_chunk<MASKED>(ra, nl + blk * 16, thr - blk * 64, c, acc);
+        colsum_chunk<MASKED>(rb, nl + blk * 16 + 8, thr - blk * 64 - 32, c, acc);
+#endif
     }
 }
 
@@ -145,6 +229,9 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
     auto t_full = [&](int i) { return bars + 8u * (4 + 2 * L::NS + i); };
     auto t_empty = [&](int i) { return bars + 8u * (4 + 2 * L::NS + NUM_TBUF + i); };
     auto merge_bar = [&](int i) { return bars + 8u * (4 + 2 * L::NS + 2 * NUM_TBUF + i); };
+    auto l_full = [&](int i) { return bars + 8u * (6 + 2 * L::NS + 2 * NUM_TBUF + i); };
+    auto l_empty = [&](int i) { return bars + 8u * (6 + 2 * L::NS + 2 * NUM_TBUF + NUM_LSE + i); };
+    const uint32_t lse_smem = smem_base + L::LSE_OFF;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFF + 4);
     float2* merge_buf = reinterpret_cast<float2*>(smem + L::MERGE_OFF);
@@ -158,8 +245,9 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), 1); }
         for (int i = 0; i < L::NS; ++i) { mbar_init(b_full(i), 1); mbar_init(b_empty(i), 1); }
-        for (int i = 0; i < NUM_TBUF; ++i) { mbar_init(t_full(i), 1); mbar_init(t_empty(i), 128); }
-        for (int i = 0; i < 2; ++i) mbar_init(merge_bar(i), 128);
+        for (int i = 0; i < NUM_TBUF; ++i) { mbar_init(t_full(i), 1); mbar_init(t_empty(i), 128 * GROUPS_PER_TILE); }
+        for (int i = 0; i < 2; ++i) mbar_init(merge_bar(i), 128 * (CONSUMER_GROUPS - 1));
+        for (int i = 0; i < NUM_LSE; ++i) { mbar_init(l_full(i), 1); mbar_init(l_empty(i), 128 * GROUPS_PER_TILE); }
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -176,81 +264,117 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // The producer and MMA warps run their loops with all 32 lanes converged (so
+    // that addresses, descriptors and counters stay in uniform registers) and
+    // elect one lane only around the instructions that must be issued once.
+    auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
+        const bool ok = mbar_wait(bar, parity, abort_flag, p.status, code);
+        return __all_sync(0xffffffffu, ok);
+    };
+
     if (warp == PRODUCER_WARP) {
-        // ------------------------------------------------ TMA producer (one thread)
-        if (lane == 0) {
-            WorkIter<MODE> it;
-            it.init(p, blockIdx.x, gridDim.x);
-            int a_cnt = 0, stage = 0;
-            uint32_t phase = 0;
-            for (; !it.done; it.next(p)) {
-                if (it.first) {
-                    const int ab = a_cnt & 1;
-                    if (!mbar_wait(a_empty(ab), ((a_cnt >> 1) & 1) ^ 1, abort_flag, p.status,
-                                   FCS_STATUS_WAIT_PRODUCER)) break;
+        // ------------------------------------------------ TMA producer
+        WorkIter<MODE> it;
+        it.init(p, blockIdx.x, gridDim.x);
+        int a_cnt = 0, stage = 0;
+        uint32_t phase = 0;
+        for (int i = 0; !it.done; it.next(p), ++i) {
+            if (it.first) {
+                const int ab = a_cnt & 1;
+                if (!wait_all(a_empty(ab), ((a_cnt >> 1) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
+                if (elect_one_sync()) {
+#if FCS_EXP == 5 || FCS_EXP == 7
+                    mbar_arrive(a_full(ab));
+#else
                     mbar_arrive_expect_tx(a_full(ab), L::TILE_BYTES);
 #pragma unroll
                     for (int sl = 0; sl < L::SLABS; ++sl)
                         tma_load_4d(a_smem + ab * L::TILE_BYTES + sl * L::SLAB_BYTES, tm_a,
                                     a_full(ab), sl * 64, it.a_row(), it.h, it.b);
+#endif
                 }
-                if (!mbar_wait(b_empty(stage), phase ^ 1, abort_flag, p.status,
-                               FCS_STATUS_WAIT_PRODUCER)) break;
+            }
+            if (!wait_all(b_empty(stage), phase ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
+            if (elect_one_sync()) {
+#if FCS_EXP == 5 || FCS_EXP == 7
+                mbar_arrive(b_full(stage));
+#else
                 mbar_arrive_expect_tx(b_full(stage), L::TILE_BYTES);
 #pragma unroll
                 for (int sl = 0; sl < L::SLABS; ++sl)
                     tma_load_4d(b_smem + stage * L::TILE_BYTES + sl * L::SLAB_BYTES, tm_b,
                                 b_full(stage), sl * 64, it.b_row(), it.h, it.b);
-                if (it.last) ++a_cnt;
-                if (++stage == L::NS) { stage = 0; phase ^= 1; }
+#endif
             }
+            if constexpr (MODE == MODE_COLSUM && FCS_EXP != 3 && FCS_EXP != 5 && FCS_EXP != 6 && FCS_EXP != 7) {
+                // -(lse) of the 128 queries of this tile, for the consumers
+                const int ls = i & (NUM_LSE - 1);
+                if (!wait_all(l_empty(ls), ((i / NUM_LSE) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
+                if (elect_one_sync()) {
+                    mbar_arrive_expect_tx(l_full(ls), TILE * 4);
+                    bulk_load(lse_smem + ls * TILE * 4,
+                              p.neg_lse + (((long long)it.b * p.H + it.h) * p.NQ + it.qt) * TILE, TILE * 4,
+                              l_full(ls));
+                }
+            }
+            __syncwarp();
+            if (it.last) ++a_cnt;
+            if (++stage == L::NS) { stage = 0; phase ^= 1; }
         }
     } else if (warp == MMA_WARP) {
-        // ------------------------------------------------ MMA issuer (one thread)
-        if (lane == 0) {
-            WorkIter<MODE> it;
-            it.init(p, blockIdx.x, gridDim.x);
-            int a_cnt = 0, stage = 0, i = 0;
-            uint32_t phase = 0;
-            for (; !it.done; it.next(p), ++i) {
-                const int ab = a_cnt & 1;
-                if (it.first) {
-                    if (!mbar_wait(a_full(ab), (a_cnt >> 1) & 1, abort_flag, p.status,
-                                   FCS_STATUS_WAIT_MMA)) break;
-                }
-                if (!mbar_wait(b_full(stage), phase, abort_flag, p.status, FCS_STATUS_WAIT_MMA)) break;
-                const int buf = i & (NUM_TBUF - 1);
-                if (!mbar_wait(t_empty(buf), ((i >> 2) & 1) ^ 1, abort_flag, p.status,
-                               FCS_STATUS_WAIT_MMA)) break;
-                tc_fence_after();
-                const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::TILE_BYTES);
-                const uint64_t db = umma_desc_k_sw128(b_smem + stage * L::TILE_BYTES);
-                const uint32_t d_tmem = tmem_base + buf * TILE;
+        // ------------------------------------------------ MMA issuer
+        WorkIter<MODE> it;
+        it.init(p, blockIdx.x, gridDim.x);
+        int a_cnt = 0, stage = 0, i = 0;
+        uint32_t phase = 0;
+        for (; !it.done; it.next(p), ++i) {
+            const int ab = a_cnt & 1;
+            if (it.first) {
+                if (!wait_all(a_full(ab), (a_cnt >> 1) & 1, FCS_STATUS_WAIT_MMA)) break;
+            }
+            if (!wait_all(b_full(stage), phase, FCS_STATUS_WAIT_MMA)) break;
+            const int buf = i & (NUM_TBUF - 1);
+#if FCS_EXP != 3 && FCS_EXP != 5 && FCS_EXP != 6 && FCS_EXP != 7
+            if (!wait_all(t_empty(buf), ((i >> 2) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) break;
+#endif
+            tc_fence_after();
+            const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::TILE_BYTES);
+            const uint64_t db = umma_desc_k_sw128(b_smem + stage * L::TILE_BYTES);
+            const uint32_t d_tmem = tmem_base + buf * TILE;
+            if (elect_one_sync()) {
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     // 32 bytes per 16-element step inside a slab, 16 KB per slab
                     const uint64_t off = (uint64_t)(((ks >> 2) * L::SLAB_BYTES + (ks & 3) * 32) >> 4);
+#if FCS_EXP != 6
                     umma_f16(d_tmem, da + off, db + off, p.idesc, ks > 0 ? 1u : 0u);
+#endif
                 }
                 umma_commit(b_empty(stage));
+#if FCS_EXP != 7
                 umma_commit(t_full(buf));
-                if (it.last) { umma_commit(a_empty(ab)); ++a_cnt; }
-                if (++stage == L::NS) { stage = 0; phase ^= 1; }
+#endif
+                if (it.last) umma_commit(a_empty(ab));
             }
+            __syncwarp();
+            if (it.last) ++a_cnt;
+            if (++stage == L::NS) { stage = 0; phase ^= 1; }
         }
     } else {
-        // ------------------------------------------------ consumers (8 warps)
-        const int wg = warp >> 2;                 // 0 or 1: takes every other tile
-        const int row = ((warp & 3) << 5) | lane; // tensor-memory lane of this thread
-        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16);
+        // ------------------------------------------------ consumers
+        const int wg = warp >> 2;                  // consumer group
+        const int slot_of_group = wg / GROUPS_PER_TILE;            // which tiles this group works on
+        const int col0 = (wg % GROUPS_PER_TILE) * GROUP_COLS;      // its first column of a tile
+        const int row = ((warp & 3) << 5) | lane;  // tensor-memory lane of this thread
+        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + col0;
         const float c = p.c;
         bool ok = true;
 
         if constexpr (MODE == MODE_STATS) {
             // the output is accumulated by the column pass: clear it here
             const long long n_out = (long long)p.B * p.Sk;
-            for (long long idx = (long long)blockIdx.x * (CONSUMER_WARPS * 32) + threadIdx.x; idx < n_out;
-                 idx += (long long)gridDim.x * (CONSUMER_WARPS * 32)) {
+            for (long long idx = (long long)blockIdx.x * CONSUMER_THREADS + threadIdx.x; idx < n_out;
+                 idx += (long long)gridDim.x * CONSUMER_THREADS) {
                 const long long bb = idx / p.Sk;
                 p.out[bb * p.out_ld + (idx - bb * p.Sk)] = 0.f;
             }
@@ -262,59 +386,58 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
         float acc[4] = {0.f, 0.f, 0.f, 0.f};       // column pass state
         int item_cnt = 0;
         for (int i = 0; !it.done; it.next(p), ++i) {
-            if ((i & 1) == wg) {
+#if FCS_EXP == 3 || FCS_EXP == 5 || FCS_EXP == 6 || FCS_EXP == 7
+            if (false) {
+#else
+            if ((i % TILE_SLOTS) == slot_of_group) {
+#endif
                 const int buf = i & (NUM_TBUF - 1);
                 ok = mbar_wait(t_full(buf), (i >> 2) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t taddr = lane_addr + buf * TILE;
-                uint32_t r[32];
                 if constexpr (MODE == MODE_STATS) {
-                    const int lim = stats_last_visible(p, it.qt, it.kt, row);
-                    const bool full = stats_tile_full(p, it.qt, it.kt);
-#pragma unroll 1
-                    for (int ch = 0; ch < 4; ++ch) {
-                        tmem_ld_x32(taddr + ch * 32, r);
-                        tmem_ld_wait(r);
-                        if (full) stats_chunk<false>(r, 31, c, m_run, l_run);
-                        else stats_chunk<true>(r, lim - ch * 32, c, m_run, l_run);
-                    }
+                    const int lim = stats_last_visible(p, it.qt, it.kt, row) - col0;
+                    if (stats_tile_full(p, it.qt, it.kt)) stats_tile<false>(taddr, lim, c, m_run, l_run);
+                    else stats_tile<true>(taddr, lim, c, m_run, l_run);
                 } else {
-                    const float4* nl4 = reinterpret_cast<const float4*>(
-                        p.neg_lse + (((long long)it.b * p.H + it.h) * p.NQ + it.qt) * TILE);
-                    const int thr = colsum_first_visible(p, it.kt, it.qt, row);
-                    const bool full = colsum_tile_full(p, it.kt, it.qt);
-#pragma unroll 1
-                    for (int ch = 0; ch < 4; ++ch) {
-                        tmem_ld_x32(taddr + ch * 32, r);
-                        float4 nl[8];
-#pragma unroll
-                        for (int v = 0; v < 8; ++v) nl[v] = __ldg(nl4 + ch * 8 + v);
-                        tmem_ld_wait(r);
-                        if (full) colsum_chunk<false>(r, nl, 0, c, acc);
-                        else colsum_chunk<true>(r, nl, thr - ch * 32, c, acc);
-                    }
+                    const int ls = i & (NUM_LSE - 1);
+                    ok = mbar_wait(l_full(ls), (i / NUM_LSE) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    const float4* nl = reinterpret_cast<const float4*>(smem + L::LSE_OFF + ls * TILE * 4) + col0 / 4;
+                    const int thr = colsum_first_visible(p, it.kt, it.qt, row) - col0;
+                    if (colsum_tile_full(p, it.kt, it.qt)) colsum_tile<false>(taddr, nl, thr, c, acc);
+                    else colsum_tile<true>(taddr, nl, thr, c, acc);
+                    mbar_arrive(l_empty(ls));
                 }
                 tc_fence_before();
                 mbar_arrive(t_empty(buf));
             }
             if constexpr (MODE == MODE_STATS) {
                 if (it.last) {
-                    // combine the two consumer groups' partial (max, sum) and store
+                    // combine the consumer groups' partial (max, sum) in group 0 and store
                     const int slot = item_cnt & 1;
-                    if (wg == 1) {
-                        merge_buf[slot * TILE + row] = make_float2(m_run, l_run);
+                    float2* mb = merge_buf + slot * (CONSUMER_GROUPS - 1) * TILE;
+                    if (wg != 0) {
+                        mb[(wg - 1) * TILE + row] = make_float2(m_run, l_run);
                         mbar_arrive(merge_bar(slot));
                     } else {
                         ok = mbar_wait(merge_bar(slot), (item_cnt >> 1) & 1, abort_flag, p.status,
                                        FCS_STATUS_WAIT_CONSUMER);
                         ok = __all_sync(0xffffffffu, ok);
                         if (!ok) break;
-                        const float2 o = merge_buf[slot * TILE + row];
-                        const float mm = fmaxf(m_run, o.x);
+                        float mm = m_run;
+#pragma unroll
+                        for (int g = 0; g < CONSUMER_GROUPS - 1; ++g) mm = fmaxf(mm, mb[g * TILE + row].x);
                         const float ms = (mm == -INFINITY) ? 0.f : mm;
-                        const float ll = l_run * exp2f(m_run - ms) + o.y * exp2f(o.x - ms);
+                        float ll = l_run * exp2f(m_run - ms);
+#pragma unroll
+                        for (int g = 0; g < CONSUMER_GROUPS - 1; ++g) {
+                            const float2 o = mb[g * TILE + row];
+                            ll += o.y * exp2f(o.x - ms);
+                        }
                         const long long bh = (long long)it.b * p.H + it.h;
                         const long long ridx = (bh * p.NQ + it.qt) * TILE + row;
                         if (p.nsplit == 1) {

@@ -9,9 +9,10 @@
 
 namespace fcs {
 
-// A wait that has not completed after this long reports a status code and
-// returns false instead of spinning forever.
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+// A wait that has not completed after this many SM cycles (about two seconds)
+// reports a status code and returns false instead of spinning forever.
+constexpr long long kWaitLimitCycles = 4000000000ll;
+constexpr uint32_t kSuspendHintNs = 20000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -21,6 +22,19 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
+}
+
+// True in exactly one lane of a fully converged warp.
+__device__ __forceinline__ bool elect_one_sync() {
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred px;\n\t"
+        "elect.sync _|px, 0xffffffff;\n\t"
+        "selp.b32 %0, 1, 0, px;\n\t"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
 }
 
 // ---------------------------------------------------------------- mbarrier
@@ -38,36 +52,41 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+// One poll.  The hint lets the hardware park the thread until the phase
+// completes (or the hint, in nanoseconds, runs out) instead of returning at once,
+// so that a waiting role does not take issue slots from the working warps.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
 
 // Bounded wait.  `abort_flag` (shared memory) is raised by whichever thread of
-// the CTA gives up first, so that every other role stops waiting promptly.
+// the CTA gives up first, so that every other role stops waiting promptly.  The
+// limit is counted on the SM's cycle counter, which is cheap to read; it is only
+// consulted every 16 polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
+    const long long t0 = clock64();
+    unsigned spins = 0;
     while (true) {
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i) {
-            if (mbar_try_wait(bar, parity)) return true;
-        }
-        if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
-            *abort_flag = 1;
-            if (status) atomicCAS(status, 0, code);
-            return false;
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 15u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
         }
     }
 }
@@ -85,6 +104,14 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
         " [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
         "r"(c3)
+        : "memory");
+}
+
+// `bytes` (multiple of 16) from 16-byte-aligned global memory into shared memory.
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(bar)
         : "memory");
 }
 
