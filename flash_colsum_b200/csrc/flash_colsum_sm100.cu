@@ -13,8 +13,10 @@
 //                    adds exp2(c*s - lse) into a per-key fp32 accumulator and
 //                    flushes that with one atomic add per (key tile, CTA range).
 //
-// Both operands are [128 x D] row tiles with the head dimension contiguous, so
-// the same shared-memory tile layout serves as A or B of the MMA.
+// Both operands are row tiles with the head dimension contiguous, so the same
+// shared-memory layout serves as A (128 resident rows) or B (256 streamed rows)
+// of the MMA; one step is a 128 x 256 x D MMA into one of two accumulator
+// buffers of 256 tensor-memory columns.
 #include "sm100_ptx.cuh"
 #include "schedule.h"
 
@@ -27,40 +29,33 @@
 
 namespace fcs {
 
-constexpr int NUM_TBUF = 4;        // accumulator buffers of 128 tensor-memory columns
+constexpr int NUM_TBUF = 2;        // accumulator buffers of 256 tensor-memory columns
 constexpr int TMEM_COLS = 512;
-#ifndef FCS_NS64
-#define FCS_NS64 6
-#endif
-#ifndef FCS_EXP
-#define FCS_EXP 0
-#endif
-constexpr int NUM_LSE = 8;         // per-query-tile log-sum-exp vectors in flight (column pass)
+constexpr int NUM_LSE = 4;         // per-query-block log-sum-exp vectors in flight (column pass)
 // Consumer warps come in groups of four (a group covers the 128 tensor-memory
-// lanes).  GROUPS_PER_TILE groups share one accumulator tile, each taking an
-// equal run of its columns; TILE_SLOTS tiles are being consumed at a time.
+// lanes); every group takes an equal run of the columns of each accumulator.
 constexpr int CONSUMER_GROUPS = 4;
-constexpr int GROUPS_PER_TILE = 2;
-constexpr int TILE_SLOTS = CONSUMER_GROUPS / GROUPS_PER_TILE;
-constexpr int GROUP_COLS = 128 / GROUPS_PER_TILE;
+constexpr int GROUP_COLS = BLOCK / CONSUMER_GROUPS;
 constexpr int CONSUMER_WARPS = 4 * CONSUMER_GROUPS;
 constexpr int CONSUMER_THREADS = 32 * CONSUMER_WARPS;
 constexpr int PRODUCER_WARP = CONSUMER_WARPS;
 constexpr int MMA_WARP = CONSUMER_WARPS + 1;
 constexpr int THREADS = 32 * (CONSUMER_WARPS + 2);
-static_assert(GROUP_COLS % 64 == 0, "a group consumes whole 64-column blocks");
+static_assert(GROUP_COLS == 64, "a group consumes one 64-column block per step");
 
 template <int D>
 struct Layout {
     static constexpr int SLABS = D / 64;              // 64-element (128-byte) column slabs
-    static constexpr int SLAB_BYTES = TILE * 128;
-    static constexpr int TILE_BYTES = SLABS * SLAB_BYTES;
-    static constexpr int NS = (D == 64) ? FCS_NS64 : 4;      // streamed-operand stages
+    static constexpr int A_SLAB_BYTES = TILE * 128;
+    static constexpr int B_SLAB_BYTES = BLOCK * 128;
+    static constexpr int A_BYTES = SLABS * A_SLAB_BYTES;
+    static constexpr int B_BYTES = SLABS * B_SLAB_BYTES;
+    static constexpr int NS = (D == 64) ? 4 : 2;      // streamed-operand stages
     static constexpr int A_OFF = 0;
-    static constexpr int B_OFF = 2 * TILE_BYTES;
-    static constexpr int LSE_OFF = B_OFF + NS * TILE_BYTES;   // NUM_LSE slots of 128 floats
-    static constexpr int BAR_OFF = LSE_OFF + NUM_LSE * TILE * 4;
-    // barriers: a_full[2] a_empty[2] b_full[NS] b_empty[NS] t_full[4] t_empty[4] merge[2]
+    static constexpr int B_OFF = 2 * A_BYTES;
+    static constexpr int LSE_OFF = B_OFF + NS * B_BYTES;   // NUM_LSE slots of 256 floats
+    static constexpr int BAR_OFF = LSE_OFF + NUM_LSE * BLOCK * 4;
+    // barriers: a_full[2] a_empty[2] b_full[NS] b_empty[NS] t_full[2] t_empty[2] merge[2]
     //           l_full[NUM_LSE] l_empty[NUM_LSE]
     static constexpr int NUM_BARS = 4 + 2 * NS + 2 * NUM_TBUF + 2 + 2 * NUM_LSE;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;        // tmem address, abort flag
@@ -128,11 +123,11 @@ __device__ __forceinline__ void stats_block64(const uint32_t (&ra)[32], const ui
 }
 
 // Add exp2(c*s - lse[q]) of 32 query columns into a key's accumulators.  `nl`
-// points at the 32 values -(lse) of these columns in shared memory.
-// `first_valid`: columns >= first_valid of this chunk are visible (<= 0: all).
+// points at the 32 values -(lse) of these columns in shared memory.  Columns
+// first_valid <= j < end_valid of this chunk are visible.
 template <bool MASKED>
 __device__ __forceinline__ void colsum_chunk(const uint32_t (&r)[32], const float4* nl, int first_valid,
-                                             float c, float (&acc)[4]) {
+                                             int end_valid, float c, float (&acc)[4]) {
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
         const float4 n = nl[j >> 2];
@@ -141,86 +136,56 @@ __device__ __forceinline__ void colsum_chunk(const uint32_t (&r)[32], const floa
         float t2 = fmaf(__uint_as_float(r[j + 2]), c, n.z);
         float t3 = fmaf(__uint_as_float(r[j + 3]), c, n.w);
         if (MASKED) {
-            t0 = (j >= first_valid) ? t0 : -INFINITY;
-            t1 = (j + 1 >= first_valid) ? t1 : -INFINITY;
-            t2 = (j + 2 >= first_valid) ? t2 : -INFINITY;
-            t3 = (j + 3 >= first_valid) ? t3 : -INFINITY;
+            t0 = (j >= first_valid && j < end_valid) ? t0 : -INFINITY;
+            t1 = (j + 1 >= first_valid && j + 1 < end_valid) ? t1 : -INFINITY;
+            t2 = (j + 2 >= first_valid && j + 2 < end_valid) ? t2 : -INFINITY;
+            t3 = (j + 3 >= first_valid && j + 3 < end_valid) ? t3 : -INFINITY;
         }
         acc[0] += ex2_approx(t0); acc[1] += ex2_approx(t1);
         acc[2] += ex2_approx(t2); acc[3] += ex2_approx(t3);
     }
 }
 
-// A group's GROUP_COLS columns of one accumulator tile, 64 at a time.
-// `taddr`, `lim`, `thr` and `nl` are relative to the group's first column.
-#ifndef FCS_EXP
-#define FCS_EXP 0
-#endif
+// A group's 64 columns of one accumulator.  `taddr`, `lim`, `thr`, `end` and
+// `nl` are relative to the group's first column.
 template <bool MASKED>
 __device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, float& m, float& l) {
-#if FCS_EXP == 4
-    return;
-#endif
     uint32_t ra[32], rb[32];
-#pragma unroll
-    for (int blk = 0; blk < GROUP_COLS / 64; ++blk) {
-#if FCS_EXP == 2
-#pragma unroll
-        for (int j = 0; j < 32; ++j) { ra[j] = __float_as_uint(m + j); rb[j] = __float_as_uint(l - j); }
-#else
-        tmem_ld_x32(taddr + blk * 64, ra);
-        tmem_ld_x32(taddr + blk * 64 + 32, rb);
-        tmem_ld_wait(ra);
-        tmem_ld_wait(rb);
-#endif
-#if FCS_EXP == 1
-        l += __uint_as_float(ra[0]) + __uint_as_float(rb[31]);
-#else
-        stats_block64<MASKED>(ra, rb, lim - blk * 64, c, m, l);
-#endif
-    }
+    tmem_ld_x32(taddr, ra);
+    tmem_ld_x32(taddr + 32, rb);
+    tmem_ld_wait(ra);
+    tmem_ld_wait(rb);
+    stats_block64<MASKED>(ra, rb, lim, c, m, l);
 }
 template <bool MASKED>
-__device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, int thr, float c,
+__device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, int thr, int end, float c,
                                             float (&acc)[4]) {
-#if FCS_EXP == 4
-    return;
-#endif
-    uint32_t ra[32], rb[32];
-#pragma unroll
-    for (int blk = 0; blk < GROUP_COLS / 64; ++blk) {
-#if FCS_EXP == 2
-#pragma unroll
-        for (int j = 0; j < 32; ++j) { ra[j] = __float_as_uint(acc[0] + j); rb[j] = __float_as_uint(acc[1] - j); }
-#else
-        tmem_ld_x32(taddr + blk * 64, ra);
-        tmem_ld_x32(taddr + blk * 64 + 32, rb);
-        tmem_ld_wait(ra);
-        tmem_ld_wait(rb);
-#endif
-#if FCS_EXP == 1
-        acc[0] += __uint_as_float(ra[0]) + __uint_as_float(rb[31]) + nl[blk].x;
-#else
-        colsum_chunk<MASKED>(ra, nl + blk * 16, thr - blk * 64, c, acc);
-        colsum_chunk<MASKED>(rb, nl + blk * 16 + 8, thr - blk * 64 - 32, c, acc);
-#endif
-    }
+    uint32_t r[32];
+    tmem_ld_x32(taddr, r);
+    tmem_ld_wait(r);
+    colsum_chunk<MASKED>(r, nl, thr, end, c, acc);
+    tmem_ld_x32(taddr + 32, r);
+    tmem_ld_wait(r);
+    colsum_chunk<MASKED>(r, nl + 8, thr - 32, end - 32, c, acc);
 }
 
 // ---------------------------------------------------------------------------
-// The streaming kernel
+// The streaming kernel.  tm_a: resident operand (box of 128 rows), tm_b:
+// streamed operand (box of 256 rows).
 // ---------------------------------------------------------------------------
 template <int D, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
-colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
-                     const __grid_constant__ CUtensorMap tm_k, const Problem p) {
+colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
+                     const __grid_constant__ CUtensorMap tm_b, const Problem p) {
     using L = Layout<D>;
+    using Items = typename ItemsOf<MODE>::type;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t a_smem = smem_base + L::A_OFF;
     const uint32_t b_smem = smem_base + L::B_OFF;
+    const uint32_t lse_smem = smem_base + L::LSE_OFF;
     const uint32_t bars = smem_base + L::BAR_OFF;
     auto a_full = [&](int i) { return bars + 8u * i; };
     auto a_empty = [&](int i) { return bars + 8u * (2 + i); };
@@ -231,7 +196,6 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
     auto merge_bar = [&](int i) { return bars + 8u * (4 + 2 * L::NS + 2 * NUM_TBUF + i); };
     auto l_full = [&](int i) { return bars + 8u * (6 + 2 * L::NS + 2 * NUM_TBUF + i); };
     auto l_empty = [&](int i) { return bars + 8u * (6 + 2 * L::NS + 2 * NUM_TBUF + NUM_LSE + i); };
-    const uint32_t lse_smem = smem_base + L::LSE_OFF;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFF + 4);
     float2* merge_buf = reinterpret_cast<float2*>(smem + L::MERGE_OFF);
@@ -239,21 +203,18 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    const CUtensorMap* tm_a = (MODE == MODE_STATS) ? &tm_q : &tm_k;   // resident operand
-    const CUtensorMap* tm_b = (MODE == MODE_STATS) ? &tm_k : &tm_q;   // streamed operand
-
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), 1); }
         for (int i = 0; i < L::NS; ++i) { mbar_init(b_full(i), 1); mbar_init(b_empty(i), 1); }
-        for (int i = 0; i < NUM_TBUF; ++i) { mbar_init(t_full(i), 1); mbar_init(t_empty(i), 128 * GROUPS_PER_TILE); }
+        for (int i = 0; i < NUM_TBUF; ++i) { mbar_init(t_full(i), 1); mbar_init(t_empty(i), CONSUMER_THREADS); }
         for (int i = 0; i < 2; ++i) mbar_init(merge_bar(i), 128 * (CONSUMER_GROUPS - 1));
-        for (int i = 0; i < NUM_LSE; ++i) { mbar_init(l_full(i), 1); mbar_init(l_empty(i), 128 * GROUPS_PER_TILE); }
+        for (int i = 0; i < NUM_LSE; ++i) { mbar_init(l_full(i), 1); mbar_init(l_empty(i), CONSUMER_THREADS); }
         *abort_flag = 0;
         mbar_fence_init();
     }
     if (warp == PRODUCER_WARP && lane == 0) {
-        prefetch_tensormap(&tm_q);
-        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
     }
     if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -272,99 +233,91 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
         return __all_sync(0xffffffffu, ok);
     };
 
-    if (warp == PRODUCER_WARP) {
-        // ------------------------------------------------ TMA producer
-        WorkIter<MODE> it;
-        it.init(p, blockIdx.x, gridDim.x);
-        int a_cnt = 0, stage = 0;
-        uint32_t phase = 0;
-        for (int i = 0; !it.done; it.next(p), ++i) {
-            if (it.first) {
+    if (warp >= CONSUMER_WARPS) {
+        if (warp == PRODUCER_WARP) {
+            // -------------------------------------------- TMA producer
+            Items it;
+            it.init(p, blockIdx.x, gridDim.x);
+            int a_cnt = 0, stage = 0, n = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (; ok && !it.done; it.next(p), ++a_cnt) {
                 const int ab = a_cnt & 1;
                 if (!wait_all(a_empty(ab), ((a_cnt >> 1) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
                 if (elect_one_sync()) {
-#if FCS_EXP == 5 || FCS_EXP == 7
-                    mbar_arrive(a_full(ab));
-#else
-                    mbar_arrive_expect_tx(a_full(ab), L::TILE_BYTES);
+                    mbar_arrive_expect_tx(a_full(ab), L::A_BYTES);
 #pragma unroll
                     for (int sl = 0; sl < L::SLABS; ++sl)
-                        tma_load_4d(a_smem + ab * L::TILE_BYTES + sl * L::SLAB_BYTES, tm_a,
-                                    a_full(ab), sl * 64, it.a_row(), it.h, it.b);
-#endif
+                        tma_load_4d(a_smem + ab * L::A_BYTES + sl * L::A_SLAB_BYTES, &tm_a, a_full(ab),
+                                    sl * 64, it.a_row(), it.h, it.b);
                 }
-            }
-            if (!wait_all(b_empty(stage), phase ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
-            if (elect_one_sync()) {
-#if FCS_EXP == 5 || FCS_EXP == 7
-                mbar_arrive(b_full(stage));
-#else
-                mbar_arrive_expect_tx(b_full(stage), L::TILE_BYTES);
+                const float* lse_src = nullptr;
+                if constexpr (MODE == MODE_COLSUM)
+                    lse_src = p.neg_lse + ((long long)it.b * p.H + it.h) * p.lse_rows;
+                for (int st = it.s0; st < it.s1; ++st, ++n) {
+                    if (!wait_all(b_empty(stage), phase ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
+                    if (elect_one_sync()) {
+                        mbar_arrive_expect_tx(b_full(stage), L::B_BYTES);
 #pragma unroll
-                for (int sl = 0; sl < L::SLABS; ++sl)
-                    tma_load_4d(b_smem + stage * L::TILE_BYTES + sl * L::SLAB_BYTES, tm_b,
-                                b_full(stage), sl * 64, it.b_row(), it.h, it.b);
-#endif
-            }
-            if constexpr (MODE == MODE_COLSUM && FCS_EXP != 3 && FCS_EXP != 5 && FCS_EXP != 6 && FCS_EXP != 7) {
-                // -(lse) of the 128 queries of this tile, for the consumers
-                const int ls = i & (NUM_LSE - 1);
-                if (!wait_all(l_empty(ls), ((i / NUM_LSE) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
-                if (elect_one_sync()) {
-                    mbar_arrive_expect_tx(l_full(ls), TILE * 4);
-                    bulk_load(lse_smem + ls * TILE * 4,
-                              p.neg_lse + (((long long)it.b * p.H + it.h) * p.NQ + it.qt) * TILE, TILE * 4,
-                              l_full(ls));
+                        for (int sl = 0; sl < L::SLABS; ++sl)
+                            tma_load_4d(b_smem + stage * L::B_BYTES + sl * L::B_SLAB_BYTES, &tm_b,
+                                        b_full(stage), sl * 64, it.b_row(st), it.h, it.b);
+                    }
+                    if constexpr (MODE == MODE_COLSUM) {
+                        // -(lse) of the 256 queries of this block, for the consumers
+                        const int ls = n & (NUM_LSE - 1);
+                        if (!wait_all(l_empty(ls), ((n / NUM_LSE) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) {
+                            ok = false; break;
+                        }
+                        if (elect_one_sync()) {
+                            mbar_arrive_expect_tx(l_full(ls), BLOCK * 4);
+                            bulk_load(lse_smem + ls * BLOCK * 4, lse_src + (long long)st * BLOCK, BLOCK * 4,
+                                      l_full(ls));
+                        }
+                    }
+                    __syncwarp();
+                    if (++stage == L::NS) { stage = 0; phase ^= 1; }
                 }
             }
-            __syncwarp();
-            if (it.last) ++a_cnt;
-            if (++stage == L::NS) { stage = 0; phase ^= 1; }
-        }
-    } else if (warp == MMA_WARP) {
-        // ------------------------------------------------ MMA issuer
-        WorkIter<MODE> it;
-        it.init(p, blockIdx.x, gridDim.x);
-        int a_cnt = 0, stage = 0, i = 0;
-        uint32_t phase = 0;
-        for (; !it.done; it.next(p), ++i) {
-            const int ab = a_cnt & 1;
-            if (it.first) {
+        } else if (warp == MMA_WARP) {
+            // -------------------------------------------- MMA issuer
+            Items it;
+            it.init(p, blockIdx.x, gridDim.x);
+            int a_cnt = 0, stage = 0, n = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (; ok && !it.done; it.next(p), ++a_cnt) {
+                const int ab = a_cnt & 1;
                 if (!wait_all(a_full(ab), (a_cnt >> 1) & 1, FCS_STATUS_WAIT_MMA)) break;
-            }
-            if (!wait_all(b_full(stage), phase, FCS_STATUS_WAIT_MMA)) break;
-            const int buf = i & (NUM_TBUF - 1);
-#if FCS_EXP != 3 && FCS_EXP != 5 && FCS_EXP != 6 && FCS_EXP != 7
-            if (!wait_all(t_empty(buf), ((i >> 2) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) break;
-#endif
-            tc_fence_after();
-            const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::TILE_BYTES);
-            const uint64_t db = umma_desc_k_sw128(b_smem + stage * L::TILE_BYTES);
-            const uint32_t d_tmem = tmem_base + buf * TILE;
-            if (elect_one_sync()) {
+                const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::A_BYTES);
+                for (int st = it.s0; st < it.s1; ++st, ++n) {
+                    if (!wait_all(b_full(stage), phase, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+                    const int buf = n & (NUM_TBUF - 1);
+                    if (!wait_all(t_empty(buf), ((n >> 1) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t db = umma_desc_k_sw128(b_smem + stage * L::B_BYTES);
+                    const uint32_t d_tmem = tmem_base + buf * BLOCK;
+                    if (elect_one_sync()) {
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    // 32 bytes per 16-element step inside a slab, 16 KB per slab
-                    const uint64_t off = (uint64_t)(((ks >> 2) * L::SLAB_BYTES + (ks & 3) * 32) >> 4);
-#if FCS_EXP != 6
-                    umma_f16(d_tmem, da + off, db + off, p.idesc, ks > 0 ? 1u : 0u);
-#endif
+                        for (int ks = 0; ks < D / 16; ++ks) {
+                            // 32 bytes per 16-element step inside a slab
+                            const uint64_t oa = (uint64_t)(((ks >> 2) * L::A_SLAB_BYTES + (ks & 3) * 32) >> 4);
+                            const uint64_t ob = (uint64_t)(((ks >> 2) * L::B_SLAB_BYTES + (ks & 3) * 32) >> 4);
+                            umma_f16(d_tmem, da + oa, db + ob, p.idesc, ks > 0 ? 1u : 0u);
+                        }
+                        umma_commit(b_empty(stage));
+                        umma_commit(t_full(buf));
+                        if (st + 1 == it.s1) umma_commit(a_empty(ab));
+                    }
+                    __syncwarp();
+                    if (++stage == L::NS) { stage = 0; phase ^= 1; }
                 }
-                umma_commit(b_empty(stage));
-#if FCS_EXP != 7
-                umma_commit(t_full(buf));
-#endif
-                if (it.last) umma_commit(a_empty(ab));
             }
-            __syncwarp();
-            if (it.last) ++a_cnt;
-            if (++stage == L::NS) { stage = 0; phase ^= 1; }
         }
     } else {
         // ------------------------------------------------ consumers
         const int wg = warp >> 2;                  // consumer group
-        const int slot_of_group = wg / GROUPS_PER_TILE;            // which tiles this group works on
-        const int col0 = (wg % GROUPS_PER_TILE) * GROUP_COLS;      // its first column of a tile
+        const int col0 = wg * GROUP_COLS;          // its first column of every accumulator
         const int row = ((warp & 3) << 5) | lane;  // tensor-memory lane of this thread
         const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + col0;
         const float c = p.c;
@@ -380,79 +333,85 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
         }
 
-        WorkIter<MODE> it;
+        Items it;
         it.init(p, blockIdx.x, gridDim.x);
         float m_run = -INFINITY, l_run = 0.f;      // statistics pass state
         float acc[4] = {0.f, 0.f, 0.f, 0.f};       // column pass state
-        int item_cnt = 0;
-        for (int i = 0; !it.done; it.next(p), ++i) {
-#if FCS_EXP == 3 || FCS_EXP == 5 || FCS_EXP == 6 || FCS_EXP == 7
-            if (false) {
-#else
-            if ((i % TILE_SLOTS) == slot_of_group) {
-#endif
-                const int buf = i & (NUM_TBUF - 1);
-                ok = mbar_wait(t_full(buf), (i >> 2) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+        int item_cnt = 0, n = 0;
+        for (; ok && !it.done; it.next(p), ++item_cnt) {
+            for (int st = it.s0; st < it.s1; ++st, ++n) {
+                const int buf = n & (NUM_TBUF - 1);
+                ok = mbar_wait(t_full(buf), (n >> 1) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t taddr = lane_addr + buf * TILE;
+                const uint32_t taddr = lane_addr + buf * BLOCK;
                 if constexpr (MODE == MODE_STATS) {
-                    const int lim = stats_last_visible(p, it.qt, it.kt, row) - col0;
-                    if (stats_tile_full(p, it.qt, it.kt)) stats_tile<false>(taddr, lim, c, m_run, l_run);
-                    else stats_tile<true>(taddr, lim, c, m_run, l_run);
+                    const int lim = stats_last_visible(p, it.qt, st, row) - col0;
+                    if (stats_tile_full(p, it.qt, st)) {
+                        stats_tile<false>(taddr, lim, c, m_run, l_run);
+                    } else {
+                        // skip the block when no row of the tile sees any of its columns
+                        const int lim_last_row = stats_last_visible(p, it.qt, st, TILE - 1) - col0;
+                        if (lim_last_row >= 0) stats_tile<true>(taddr, lim, c, m_run, l_run);
+                    }
                 } else {
-                    const int ls = i & (NUM_LSE - 1);
-                    ok = mbar_wait(l_full(ls), (i / NUM_LSE) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+                    const int ls = n & (NUM_LSE - 1);
+                    ok = mbar_wait(l_full(ls), (n / NUM_LSE) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
-                    const float4* nl = reinterpret_cast<const float4*>(smem + L::LSE_OFF + ls * TILE * 4) + col0 / 4;
-                    const int thr = colsum_first_visible(p, it.kt, it.qt, row) - col0;
-                    if (colsum_tile_full(p, it.kt, it.qt)) colsum_tile<false>(taddr, nl, thr, c, acc);
-                    else colsum_tile<true>(taddr, nl, thr, c, acc);
+                    const float4* nl = reinterpret_cast<const float4*>(smem + L::LSE_OFF + ls * BLOCK * 4) + col0 / 4;
+                    const int thr = colsum_first_visible(p, it.kt, st, row) - col0;
+                    const int end = colsum_end_visible(p, st) - col0;
+                    if (colsum_tile_full(p, it.kt, st)) {
+                        colsum_tile<false>(taddr, nl, thr, end, c, acc);
+                    } else {
+                        // skip the block when no key of the tile is seen by any of its queries
+                        const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - col0;
+                        if (end > 0 && thr_first_row < GROUP_COLS) colsum_tile<true>(taddr, nl, thr, end, c, acc);
+                    }
                     mbar_arrive(l_empty(ls));
                 }
                 tc_fence_before();
                 mbar_arrive(t_empty(buf));
             }
+            if (!ok) break;
             if constexpr (MODE == MODE_STATS) {
-                if (it.last) {
-                    // combine the consumer groups' partial (max, sum) in group 0 and store
-                    const int slot = item_cnt & 1;
-                    float2* mb = merge_buf + slot * (CONSUMER_GROUPS - 1) * TILE;
-                    if (wg != 0) {
-                        mb[(wg - 1) * TILE + row] = make_float2(m_run, l_run);
-                        mbar_arrive(merge_bar(slot));
-                    } else {
-                        ok = mbar_wait(merge_bar(slot), (item_cnt >> 1) & 1, abort_flag, p.status,
-                                       FCS_STATUS_WAIT_CONSUMER);
-                        ok = __all_sync(0xffffffffu, ok);
-                        if (!ok) break;
-                        float mm = m_run;
+                // combine the consumer groups' partial (max, sum) in group 0 and store
+                const int slot = item_cnt & 1;
+                float2* mb = merge_buf + slot * (CONSUMER_GROUPS - 1) * TILE;
+                if (wg != 0) {
+                    mb[(wg - 1) * TILE + row] = make_float2(m_run, l_run);
+                    mbar_arrive(merge_bar(slot));
+                } else {
+                    ok = mbar_wait(merge_bar(slot), (item_cnt >> 1) & 1, abort_flag, p.status,
+                                   FCS_STATUS_WAIT_CONSUMER);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    float mm = m_run;
 #pragma unroll
-                        for (int g = 0; g < CONSUMER_GROUPS - 1; ++g) mm = fmaxf(mm, mb[g * TILE + row].x);
-                        const float ms = (mm == -INFINITY) ? 0.f : mm;
-                        float ll = l_run * exp2f(m_run - ms);
+                    for (int g = 0; g < CONSUMER_GROUPS - 1; ++g) mm = fmaxf(mm, mb[g * TILE + row].x);
+                    const float ms = (mm == -INFINITY) ? 0.f : mm;
+                    float ll = l_run * exp2f(m_run - ms);
 #pragma unroll
-                        for (int g = 0; g < CONSUMER_GROUPS - 1; ++g) {
-                            const float2 o = mb[g * TILE + row];
-                            ll += o.y * exp2f(o.x - ms);
-                        }
-                        const long long bh = (long long)it.b * p.H + it.h;
-                        const long long ridx = (bh * p.NQ + it.qt) * TILE + row;
-                        if (p.nsplit == 1) {
-                            const bool real = (it.qt * TILE + row) < p.Sq;
-                            p.neg_lse[ridx] = real ? -(mm + log2f(ll) + p.log2_norm) : -INFINITY;
-                        } else {
-                            reinterpret_cast<float2*>(p.part)[(long long)it.sp * ((long long)p.B * p.H * p.NQ * TILE) + ridx] =
-                                make_float2(mm, ll);
-                        }
+                    for (int g = 0; g < CONSUMER_GROUPS - 1; ++g) {
+                        const float2 o = mb[g * TILE + row];
+                        ll += o.y * exp2f(o.x - ms);
                     }
-                    m_run = -INFINITY; l_run = 0.f;
-                    ++item_cnt;
+                    const long long bh = (long long)it.b * p.H + it.h;
+                    const int q_abs = it.qt * TILE + row;
+                    if (p.nsplit == 1) {
+                        p.neg_lse[bh * p.lse_rows + q_abs] =
+                            (q_abs < p.Sq) ? -(mm + log2f(ll) + p.log2_norm) : -INFINITY;
+                    } else {
+                        const long long rows = (long long)p.NQ * TILE;
+                        reinterpret_cast<float2*>(p.part)[((long long)it.sp * p.B * p.H + bh) * rows + q_abs] =
+                            make_float2(mm, ll);
+                    }
                 }
+                m_run = -INFINITY; l_run = 0.f;
             } else {
-                if (it.flush) {
+                if (it.flush()) {
                     const int k_abs = it.kt * TILE + row;
                     if (k_abs < p.Sk)
                         atomicAdd(p.out + (long long)it.b * p.out_ld + k_abs,
@@ -476,15 +435,16 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_q,
 // Combine the key-range partials of the statistics pass into the per-row value
 // the column pass subtracts.
 __global__ void merge_stats_kernel(const Problem p) {
-    const long long rows_per_bh = (long long)p.NQ * TILE;
-    const long long n = (long long)p.B * p.H * rows_per_bh;
+    const long long rows = (long long)p.NQ * TILE;
+    const long long n = (long long)p.B * p.H * rows;
+    const float2* part = reinterpret_cast<const float2*>(p.part);
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
          idx += (long long)gridDim.x * blockDim.x) {
-        const int q_abs = (int)(idx % rows_per_bh);
+        const long long bh = idx / rows;
+        const int q_abs = (int)(idx - bh * rows);
         float v = -INFINITY;
         if (q_abs < p.Sq) {
             float mm = -INFINITY;
-            const float2* part = reinterpret_cast<const float2*>(p.part);
             for (int s = 0; s < p.nsplit; ++s) mm = fmaxf(mm, part[s * n + idx].x);
             float ll = 0.f;
             for (int s = 0; s < p.nsplit; ++s) {
@@ -493,7 +453,7 @@ __global__ void merge_stats_kernel(const Problem p) {
             }
             v = -(mm + log2f(ll) + p.log2_norm);
         }
-        p.neg_lse[idx] = v;
+        p.neg_lse[bh * p.lse_rows + q_abs] = v;
     }
 }
 
@@ -539,15 +499,15 @@ static int num_sms() {
     return cached[dev];
 }
 
-// (D, S, H, B) view of a [B, H, S, D] tensor, boxes of 128 rows x 64 elements,
-// 128-byte swizzle, out-of-range rows read as zero.
+// (D, S, H, B) view of a [B, H, S, D] tensor, boxes of `box_rows` rows x 64
+// elements, 128-byte swizzle, out-of-range rows read as zero.
 static int make_tensor_map(CUtensorMap* m, const void* base, int dtype, int B, int H, int S, int D,
-                           int64_t sb, int64_t sh, int64_t ss) {
+                           int64_t sb, int64_t sh, int64_t ss, int box_rows) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(FCS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
     cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
-    cuuint32_t box[4] = {64, (cuuint32_t)TILE, 1, 1};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(m, dtype == FCS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                      4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -580,7 +540,7 @@ static PassTimers* timers_for_current_device() {
 }
 
 template <int D, int MODE>
-static cudaError_t launch_stream(const CUtensorMap& tq, const CUtensorMap& tk, const Problem& p, int grid,
+static cudaError_t launch_stream(const CUtensorMap& ta, const CUtensorMap& tb, const Problem& p, int grid,
                                  cudaStream_t stream) {
     static bool configured[64] = {false};
     int dev = 0;
@@ -592,7 +552,7 @@ static cudaError_t launch_stream(const CUtensorMap& tq, const CUtensorMap& tk, c
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    kern<<<grid, THREADS, Layout<D>::DYN_BYTES, stream>>>(tq, tk, p);
+    kern<<<grid, THREADS, Layout<D>::DYN_BYTES, stream>>>(ta, tb, p);
     return cudaGetLastError();
 }
 
@@ -650,13 +610,17 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     p.c = fabsf(scale) * 1.4426950408889634f;
     p.log2_norm = log2f((float)h_norm * (float)Sq);
     const uint32_t fmt = dtype == FCS_DTYPE_BF16 ? 1u : 0u;
-    // fp32 accumulate, K-major A and B, M = N = 128; a negative scale negates A
+    // fp32 accumulate, K-major A and B, M = 128, N = 256; a negative scale negates A
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((scale < 0.f ? 1u : 0u) << 13) |
-              ((uint32_t)(TILE >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
+              ((uint32_t)(BLOCK >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
 
-    CUtensorMap tq, tk;
-    if ((rc = make_tensor_map(&tq, q, dtype, B, H, Sq, D, qsb, qsh, qss)) != FCS_OK) return rc;
-    if ((rc = make_tensor_map(&tk, k, dtype, B, H, Sk, D, ksb, ksh, kss)) != FCS_OK) return rc;
+    // each tensor is the resident operand (128-row boxes) of one pass and the
+    // streamed operand (256-row boxes) of the other
+    CUtensorMap tq_a, tq_b, tk_a, tk_b;
+    if ((rc = make_tensor_map(&tq_a, q, dtype, B, H, Sq, D, qsb, qsh, qss, TILE)) != FCS_OK) return rc;
+    if ((rc = make_tensor_map(&tq_b, q, dtype, B, H, Sq, D, qsb, qsh, qss, BLOCK)) != FCS_OK) return rc;
+    if ((rc = make_tensor_map(&tk_a, k, dtype, B, H, Sk, D, ksb, ksh, kss, TILE)) != FCS_OK) return rc;
+    if ((rc = make_tensor_map(&tk_b, k, dtype, B, H, Sk, D, ksb, ksh, kss, BLOCK)) != FCS_OK) return rc;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
     const int grid1 = (int)(p.stats_items < sms ? p.stats_items : sms);
@@ -664,8 +628,8 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     PassTimers* tm = g_profiling ? timers_for_current_device() : nullptr;
     if (tm) { tm->recorded = false; cudaEventRecord(tm->ev[0], stream); }
     cudaError_t e;
-    e = (D == 64) ? launch_stream<64, MODE_STATS>(tq, tk, p, grid1, stream)
-                  : launch_stream<128, MODE_STATS>(tq, tk, p, grid1, stream);
+    e = (D == 64) ? launch_stream<64, MODE_STATS>(tq_a, tk_b, p, grid1, stream)
+                  : launch_stream<128, MODE_STATS>(tq_a, tk_b, p, grid1, stream);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics pass launch failed: %s", cudaGetErrorString(e));
     if (tm) cudaEventRecord(tm->ev[1], stream);
     if (p.nsplit > 1) {
@@ -677,8 +641,8 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
         if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics merge launch failed: %s", cudaGetErrorString(e));
     }
     if (tm) cudaEventRecord(tm->ev[2], stream);
-    e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tq, tk, p, grid2, stream)
-                  : launch_stream<128, MODE_COLSUM>(tq, tk, p, grid2, stream);
+    e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tk_a, tq_b, p, grid2, stream)
+                  : launch_stream<128, MODE_COLSUM>(tk_a, tq_b, p, grid2, stream);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "column pass launch failed: %s", cudaGetErrorString(e));
     if (tm) { cudaEventRecord(tm->ev[3], stream); tm->recorded = true; }
     return FCS_OK;

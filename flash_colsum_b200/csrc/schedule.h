@@ -2,6 +2,11 @@
 // kernels and by the host code that plans a call.  Everything here is plain
 // integer logic, usable from host and device, so the step sequences and the
 // mask rules can be checked on a CPU.
+//
+// Geometry.  One MMA step multiplies a resident [128 x D] operand tile by a
+// streamed [256 x D] operand block and fills a 128 x 256 fp32 accumulator:
+//   statistics pass: resident = 128 queries, streamed = 256 keys;
+//   column pass:     resident = 128 keys,    streamed = 256 queries.
 #pragma once
 
 #include <stddef.h>
@@ -15,26 +20,27 @@
 
 namespace fcs {
 
-constexpr int TILE = 128;      // rows of an operand tile; one step is a 128x128 score tile
+constexpr int TILE = 128;      // rows of the resident operand tile (MMA M)
+constexpr int BLOCK = 256;     // rows of the streamed operand block (MMA N)
 constexpr int MAX_SPLIT = 64;  // most key ranges a query tile is split into
 
 enum : int { MODE_STATS = 0, MODE_COLSUM = 1 };
 
-struct float2_ { float x, y; };
-
 struct Problem {
     int B, H, Sq, Sk;   // Sq: query rows that enter the mean
-    int NQ, NKT;        // query tiles, key tiles
+    int NQ, NKT;        // 128-row query tiles / key tiles (resident operands)
+    int NQB, NKB;       // 256-row query blocks / key blocks (streamed operands)
     int NKC;            // key tiles that hold at least one visible key (column pass)
     int causal, k_past; // key j is visible to query i iff j <= k_past + i
     int nsplit;         // key ranges per (b, h, query tile) in the statistics pass
-    int kreg;           // leading key tiles that every query tile contributes to
+    int kreg;           // leading key tiles that every query block contributes to
     long long stats_items;
     long long steps_per_batch;  // column pass: steps of one batch entry
     long long steps_total;
+    long long lse_rows;         // rows of neg_lse per (b, h): NQB * 256
     float c;            // |scale| * log2(e)
     float log2_norm;    // log2(h_norm * R)
-    float* neg_lse;     // [B*H][NQ*128]   -(lse2 + log2_norm), -inf on padding rows
+    float* neg_lse;     // [B*H][lse_rows]   -(lse2 + log2_norm)
     void* part;         // float2 [nsplit][B*H][NQ*128]   (max, sum) per key range
     float* out;
     long long out_ld;
@@ -44,65 +50,66 @@ struct Problem {
 
 FCS_HD inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-// Key tiles a query tile needs in the statistics pass.
-FCS_HD inline int stats_key_tiles(const Problem& p, int qt) {
-    if (!p.causal) return p.NKT;
+// Key blocks a query tile needs in the statistics pass.
+FCS_HD inline int stats_key_blocks(const Problem& p, int qt) {
+    if (!p.causal) return p.NKB;
     int q_end = (qt + 1) * TILE;
     if (q_end > p.Sq) q_end = p.Sq;
     long long k_end = (long long)p.k_past + q_end;   // keys visible to the tile's last row
     if (k_end > p.Sk) k_end = p.Sk;
-    return ceil_div((int)k_end, TILE);
+    return ceil_div((int)k_end, BLOCK);
 }
-// First query tile that contributes to a key tile in the column pass.
-FCS_HD inline int colsum_first_q_tile(const Problem& p, int kt) {
+// First query block that contributes to a key tile in the column pass.
+FCS_HD inline int colsum_first_q_block(const Problem& p, int kt) {
     if (!p.causal) return 0;
-    long long d = (long long)kt * TILE - p.k_past;
-    return d <= 0 ? 0 : (int)(d / TILE);
+    const long long d = (long long)kt * TILE - p.k_past;   // first query that sees the tile's first key
+    return d <= 0 ? 0 : (int)(d / BLOCK);
 }
 
-// Statistics pass, score tile (qt, kt): the last visible key column (relative to
-// the tile) for tile row `row`; and whether every element of the tile is visible.
-FCS_HD inline int stats_last_visible(const Problem& p, int qt, int kt, int row) {
+// Statistics pass, score tile (query tile qt, key block kb): the last visible key
+// column (0..255, or -1) for tile row `row`, and whether every element is visible.
+FCS_HD inline int stats_last_visible(const Problem& p, int qt, int kb, int row) {
     long long lim = p.Sk - 1;
     if (p.causal) {
         const long long v = (long long)p.k_past + (long long)qt * TILE + row;
         if (v < lim) lim = v;
     }
-    lim -= (long long)kt * TILE;
-    return lim > TILE ? TILE : (lim < -1 ? -1 : (int)lim);
+    lim -= (long long)kb * BLOCK;
+    return lim > BLOCK ? BLOCK : (lim < -1 ? -1 : (int)lim);
 }
-FCS_HD inline bool stats_tile_full(const Problem& p, int qt, int kt) {
-    bool full = ((long long)kt * TILE + TILE <= p.Sk);
+FCS_HD inline bool stats_tile_full(const Problem& p, int qt, int kb) {
+    bool full = ((long long)kb * BLOCK + BLOCK <= p.Sk);
     if (p.causal)
-        full = full && ((long long)kt * TILE + TILE - 1 <= (long long)p.k_past + (long long)qt * TILE);
+        full = full && ((long long)kb * BLOCK + BLOCK - 1 <= (long long)p.k_past + (long long)qt * TILE);
     return full;
 }
-// Column pass, transposed score tile (kt, qt): the first visible query column
-// (relative to the tile) for key row `row`; and whether the whole tile is visible.
-FCS_HD inline int colsum_first_visible(const Problem& p, int kt, int qt, int row) {
+// Column pass, transposed score tile (key tile kt, query block qb): query columns
+// [first, end) are visible for key row `row`; and whether the whole tile is.
+FCS_HD inline int colsum_first_visible(const Problem& p, int kt, int qb, int row) {
     if (!p.causal) return 0;
-    const long long t = (long long)kt * TILE + row - p.k_past - (long long)qt * TILE;
-    return t > TILE ? TILE : (t < 0 ? 0 : (int)t);
+    const long long t = (long long)kt * TILE + row - p.k_past - (long long)qb * BLOCK;
+    return t > BLOCK ? BLOCK : (t < 0 ? 0 : (int)t);
 }
-FCS_HD inline bool colsum_tile_full(const Problem& p, int kt, int qt) {
-    return !p.causal || ((long long)kt * TILE + TILE - 1 - p.k_past - (long long)qt * TILE <= 0);
+FCS_HD inline int colsum_end_visible(const Problem& p, int qb) {
+    const long long n = (long long)p.Sq - (long long)qb * BLOCK;
+    return n > BLOCK ? BLOCK : (n < 0 ? 0 : (int)n);
+}
+FCS_HD inline bool colsum_tile_full(const Problem& p, int kt, int qb) {
+    if ((long long)qb * BLOCK + BLOCK > p.Sq) return false;
+    return !p.causal || ((long long)kt * TILE + TILE - 1 - p.k_past - (long long)qb * BLOCK <= 0);
 }
 
 // ---------------------------------------------------------------------------
-// Work iterators.  Every role of a CTA (producer, MMA issuer, both consumer
-// groups) walks the same deterministic sequence of steps.  An "item" is a run
-// of steps that share the resident operand tile (`first`/`last` mark its ends);
-// `flush` marks the step after which the column pass adds its accumulators
-// into the output.
+// Item iterators.  Every role of a CTA (producer, MMA issuer, consumers) walks
+// the same deterministic sequence of items; an item is a run of steps that
+// share the resident operand tile, its steps are the streamed blocks
+// [s0, s1).
 // ---------------------------------------------------------------------------
-template <int MODE>
-struct WorkIter;
 
 // Statistics pass: item = (b, h, query tile, key range), taken round-robin.
-template <>
-struct WorkIter<MODE_STATS> {
-    bool done, first, last, flush;
-    int b, h, qt, kt, sp, kt_end, grid;
+struct StatsItems {
+    bool done;
+    int b, h, qt, sp, s0, s1, grid;   // steps = key blocks s0..s1-1
     long long item;
 
     FCS_HD void load(const Problem& p) {
@@ -113,53 +120,51 @@ struct WorkIter<MODE_STATS> {
         const long long bh = t / p.NQ;
         h = (int)(bh % p.H);
         b = (int)(bh / p.H);
-        const int nk = stats_key_tiles(p, qt);
-        kt = (int)((long long)sp * nk / p.nsplit);
-        kt_end = (int)((long long)(sp + 1) * nk / p.nsplit);
-        first = true;
-        last = (kt + 1 >= kt_end);
+        const int nk = stats_key_blocks(p, qt);
+        s0 = (int)((long long)sp * nk / p.nsplit);
+        s1 = (int)((long long)(sp + 1) * nk / p.nsplit);
     }
     FCS_HD void init(const Problem& p, int cta, int grid_) {
-        done = false; flush = false;
+        done = false;
         grid = grid_;
         item = cta;
         load(p);
     }
     FCS_HD void next(const Problem& p) {
-        if (kt + 1 < kt_end) {
-            ++kt; first = false; last = (kt + 1 >= kt_end);
-        } else {
-            item += grid;
-            load(p);
-        }
+        item += grid;
+        load(p);
     }
-    FCS_HD int a_row() const { return qt * TILE; }   // resident operand = query tile
-    FCS_HD int b_row() const { return kt * TILE; }   // streamed operand = key tile
+    FCS_HD int a_row() const { return qt * TILE; }        // resident = query tile
+    FCS_HD int b_row(int s) const { return s * BLOCK; }   // streamed = key block
+    FCS_HD bool flush() const { return false; }
 };
 
-// Column pass: steps ordered (b, key tile, h, query tile); a CTA takes one
-// contiguous range of them.
-template <>
-struct WorkIter<MODE_COLSUM> {
-    bool done, first, last, flush;
-    int b, h, qt, kt, qlo;
+// Column pass: steps ordered (b, key tile, h, query block); a CTA takes one
+// contiguous range of them, cut into items at (b, key tile, h) boundaries.
+// `flush` marks the item after which the per-key accumulators are added into
+// the output (the CTA leaves the (b, key tile) group or ends).
+struct ColsumItems {
+    bool done, flush_;
+    int b, h, kt, s0, s1, qlo;        // steps = query blocks s0..s1-1
     long long s, s_end;
 
-    FCS_HD void flags(const Problem& p) {
-        const bool end = (s + 1 >= s_end);
-        last = (qt + 1 >= p.NQ) || end;
-        flush = ((qt + 1 >= p.NQ) && (h + 1 >= p.H)) || end;
+    FCS_HD void cut(const Problem& p) {
+        long long n = p.NQB - s0;
+        if (n > s_end - s) n = s_end - s;
+        s1 = s0 + (int)n;
+        const bool end = (s + n >= s_end);
+        flush_ = ((s1 >= p.NQB) && (h + 1 >= p.H)) || end;
     }
     FCS_HD void init(const Problem& p, int cta, int grid) {
         s = p.steps_total * cta / grid;
         s_end = p.steps_total * (cta + 1) / grid;
         done = (s >= s_end);
-        first = last = flush = false;
-        b = h = qt = kt = qlo = 0;
+        flush_ = false;
+        b = h = kt = s0 = s1 = qlo = 0;
         if (done) return;
         b = (int)(s / p.steps_per_batch);
         long long r = s % p.steps_per_batch;
-        const long long per_kt = (long long)p.H * p.NQ;
+        const long long per_kt = (long long)p.H * p.NQB;
         const long long regular = per_kt * p.kreg;
         if (r < regular) {
             kt = (int)(r / per_kt);
@@ -168,42 +173,41 @@ struct WorkIter<MODE_COLSUM> {
         } else {
             r -= regular;
             kt = p.kreg;
-            qlo = colsum_first_q_tile(p, kt);
+            qlo = colsum_first_q_block(p, kt);
             for (int guard = 0; guard < p.NKC; ++guard) {
-                const long long n = (long long)p.H * (p.NQ - qlo);
+                const long long n = (long long)p.H * (p.NQB - qlo);
                 if (r < n) break;
                 r -= n;
                 ++kt;
-                qlo = colsum_first_q_tile(p, kt);
+                qlo = colsum_first_q_block(p, kt);
             }
         }
-        const int nq = p.NQ - qlo;
+        const int nq = p.NQB - qlo;
         h = (int)(r / nq);
-        qt = qlo + (int)(r % nq);
-        first = true;
-        flags(p);
+        s0 = qlo + (int)(r % nq);
+        cut(p);
     }
     FCS_HD void next(const Problem& p) {
-        ++s;
+        s += s1 - s0;
         if (s >= s_end) { done = true; return; }
-        if (qt + 1 < p.NQ) {
-            ++qt; first = false;
+        if (h + 1 < p.H) {
+            ++h;
         } else {
-            first = true;
-            if (h + 1 < p.H) {
-                ++h;
-            } else {
-                h = 0;
-                if (kt + 1 < p.NKC) { ++kt; } else { kt = 0; ++b; }
-                qlo = colsum_first_q_tile(p, kt);
-            }
-            qt = qlo;
+            h = 0;
+            if (kt + 1 < p.NKC) { ++kt; } else { kt = 0; ++b; }
+            qlo = colsum_first_q_block(p, kt);
         }
-        flags(p);
+        s0 = qlo;
+        cut(p);
     }
-    FCS_HD int a_row() const { return kt * TILE; }   // resident operand = key tile
-    FCS_HD int b_row() const { return qt * TILE; }   // streamed operand = query tile
+    FCS_HD int a_row() const { return kt * TILE; }        // resident = key tile
+    FCS_HD int b_row(int st) const { return st * BLOCK; } // streamed = query block
+    FCS_HD bool flush() const { return flush_; }
 };
+
+template <int MODE> struct ItemsOf;
+template <> struct ItemsOf<MODE_STATS> { typedef StatsItems type; };
+template <> struct ItemsOf<MODE_COLSUM> { typedef ColsumItems type; };
 
 // ---------------------------------------------------------------------------
 // Planning (host): fills the shape-derived fields of `p`.
@@ -212,12 +216,15 @@ inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_pas
     p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk;
     p.NQ = ceil_div(Sq, TILE);
     p.NKT = ceil_div(Sk, TILE);
+    p.NQB = ceil_div(Sq, BLOCK);
+    p.NKB = ceil_div(Sk, BLOCK);
+    p.lse_rows = (long long)p.NQB * BLOCK;
     p.causal = causal;
     p.k_past = causal ? k_past : 0;
     // statistics pass: split the key range when (b, h, query tile) items are too
-    // few to fill the SMs; never into more ranges than the shortest item has tiles
+    // few to fill the SMs; never into more ranges than the shortest item has blocks
     const long long base_items = (long long)B * H * p.NQ;
-    int max_split = stats_key_tiles(p, 0);
+    int max_split = stats_key_blocks(p, 0);
     if (max_split > MAX_SPLIT) max_split = MAX_SPLIT;
     int best = 1;
     double best_eff = 0.0;
@@ -235,14 +242,17 @@ inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_pas
         long long visible = (long long)p.k_past + Sq;   // keys past this are seen by no query
         if (visible > Sk) visible = Sk;
         p.NKC = ceil_div((int)visible, TILE);
-        const long long kr = (long long)p.k_past / TILE + 1;
+        // key tiles whose first key is seen by query block 0's ... first block: d < BLOCK
+        const long long kr = ((long long)p.k_past + BLOCK - 1) / TILE + 1;
         p.kreg = kr > p.NKC ? p.NKC : (int)kr;
+        // keep only tiles with first_q_block == 0
+        while (p.kreg > 0 && colsum_first_q_block(p, p.kreg - 1) != 0) --p.kreg;
     } else {
         p.NKC = p.NKT;
         p.kreg = p.NKT;
     }
-    long long steps = (long long)p.kreg * H * p.NQ;
-    for (int kt = p.kreg; kt < p.NKC; ++kt) steps += (long long)H * (p.NQ - colsum_first_q_tile(p, kt));
+    long long steps = (long long)p.kreg * H * p.NQB;
+    for (int kt = p.kreg; kt < p.NKC; ++kt) steps += (long long)H * (p.NQB - colsum_first_q_block(p, kt));
     p.steps_per_batch = steps;
     p.steps_total = steps * B;
 }
@@ -251,10 +261,9 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // Scratch layout: [neg_lse | part]; returns the total and the offset of `part`.
 inline size_t workspace_layout(const Problem& p, size_t* part_off) {
-    const size_t rows = (size_t)p.B * p.H * p.NQ * TILE;
-    size_t off = align_up(rows * sizeof(float), 256);
+    size_t off = align_up((size_t)p.B * p.H * (size_t)p.lse_rows * sizeof(float), 256);
     if (part_off) *part_off = off;
-    if (p.nsplit > 1) off += align_up(rows * 2 * sizeof(float) * p.nsplit, 256);
+    if (p.nsplit > 1) off += align_up((size_t)p.B * p.H * p.NQ * TILE * 2 * sizeof(float) * p.nsplit, 256);
     return off;
 }
 
