@@ -100,11 +100,18 @@ __device__ __forceinline__ void stats_block64(const uint32_t (&ra)[32], const ui
     m0 = max3(m0, s[60], s[61]);
     m1 = max3(m1, s[62], s[63]);
     const float cm = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-    const float scaled = (cm == -INFINITY) ? -INFINITY : cm * c;
-    const float m_new = fmaxf(m, scaled);
-    const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-    l *= ex2_approx(m - m_safe);
-    m = m_new;
+    float m_safe;
+    if (MASKED) {   // a row may see nothing of this block (or nothing yet): keep -inf out of the arithmetic
+        const float scaled = (cm == -INFINITY) ? -INFINITY : cm * c;
+        const float m_new = fmaxf(m, scaled);
+        m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+        l *= ex2_approx(m - m_safe);
+        m = m_new;
+    } else {        // all 64 scores are finite
+        m_safe = fmaxf(m, cm * c);
+        l *= ex2_approx(m - m_safe);
+        m = m_safe;
+    }
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
     for (int j = 0; j < 64; j += 4) {
@@ -339,6 +346,10 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
         float acc[4] = {0.f, 0.f, 0.f, 0.f};       // column pass state
         int item_cnt = 0, n = 0;
         for (; ok && !it.done; it.next(p), ++item_cnt) {
+            // steps f_lo <= st < f_hi need no masks: their per-step work is kept minimal
+            int f_lo, f_hi;
+            if constexpr (MODE == MODE_STATS) stats_full_range(p, it.qt, f_lo, f_hi);
+            else colsum_full_range(p, it.kt, f_lo, f_hi);
             for (int st = it.s0; st < it.s1; ++st, ++n) {
                 const int buf = n & (NUM_TBUF - 1);
                 ok = mbar_wait(t_full(buf), (n >> 1) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
@@ -346,11 +357,12 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t taddr = lane_addr + buf * BLOCK;
+                const bool full = (st >= f_lo) && (st < f_hi);
                 if constexpr (MODE == MODE_STATS) {
-                    const int lim = stats_last_visible(p, it.qt, st, row) - col0;
-                    if (stats_tile_full(p, it.qt, st)) {
-                        stats_tile<false>(taddr, lim, c, m_run, l_run);
+                    if (full) {
+                        stats_tile<false>(taddr, GROUP_COLS, c, m_run, l_run);
                     } else {
+                        const int lim = stats_last_visible(p, it.qt, st, row) - col0;
                         // skip the block when no row of the tile sees any of its columns
                         const int lim_last_row = stats_last_visible(p, it.qt, st, TILE - 1) - col0;
                         if (lim_last_row >= 0) stats_tile<true>(taddr, lim, c, m_run, l_run);
@@ -361,11 +373,11 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     const float4* nl = reinterpret_cast<const float4*>(smem + L::LSE_OFF + ls * BLOCK * 4) + col0 / 4;
-                    const int thr = colsum_first_visible(p, it.kt, st, row) - col0;
-                    const int end = colsum_end_visible(p, st) - col0;
-                    if (colsum_tile_full(p, it.kt, st)) {
-                        colsum_tile<false>(taddr, nl, thr, end, c, acc);
+                    if (full) {
+                        colsum_tile<false>(taddr, nl, 0, GROUP_COLS, c, acc);
                     } else {
+                        const int thr = colsum_first_visible(p, it.kt, st, row) - col0;
+                        const int end = colsum_end_visible(p, st) - col0;
                         // skip the block when no key of the tile is seen by any of its queries
                         const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - col0;
                         if (end > 0 && thr_first_row < GROUP_COLS) colsum_tile<true>(taddr, nl, thr, end, c, acc);

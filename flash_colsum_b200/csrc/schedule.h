@@ -99,6 +99,26 @@ FCS_HD inline bool colsum_tile_full(const Problem& p, int kt, int qb) {
     return !p.causal || ((long long)kt * TILE + TILE - 1 - p.k_past - (long long)qb * BLOCK <= 0);
 }
 
+// Steps lo <= st < hi of an item are fully visible (the *_tile_full rule, solved
+// for the step index), so that the per-step mask arithmetic can be skipped.
+FCS_HD inline void stats_full_range(const Problem& p, int qt, int& lo, int& hi) {
+    lo = 0;
+    long long h = p.Sk / BLOCK;
+    if (p.causal) {
+        const long long c = ((long long)p.k_past + (long long)qt * TILE + 1) / BLOCK;
+        if (c < h) h = c;
+    }
+    hi = (int)h;
+}
+FCS_HD inline void colsum_full_range(const Problem& p, int kt, int& lo, int& hi) {
+    hi = p.Sq / BLOCK;
+    lo = 0;
+    if (p.causal) {
+        const long long d = (long long)kt * TILE + TILE - 1 - p.k_past;
+        if (d > 0) lo = (int)((d + BLOCK - 1) / BLOCK);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Item iterators.  Every role of a CTA (producer, MMA issuer, consumers) walks
 // the same deterministic sequence of items; an item is a run of steps that

@@ -65,8 +65,11 @@ extern "C" int emulate_colsum(const float* q, const float* k, float* out, int B,
             if (it.s0 >= it.s1) return -15;   // an item without steps would never write its rows
             float m[4][TILE], l[4][TILE];
             for (int g = 0; g < G; ++g) for (int r = 0; r < TILE; ++r) { m[g][r] = -INFINITY; l[g][r] = 0.f; }
+            int f_lo, f_hi;
+            stats_full_range(p, it.qt, f_lo, f_hi);
             for (int st = it.s0; st < it.s1; ++st) {
                 const bool full = stats_tile_full(p, it.qt, st);
+                if (full != (st >= f_lo && st < f_hi)) return -17;   // the range form of the rule disagrees
                 for (int g = 0; g < G; ++g) {
                     const int col0 = g * GC;
                     const bool skip = !full && (stats_last_visible(p, it.qt, st, TILE - 1) - col0 < 0);
@@ -152,9 +155,12 @@ extern "C" int emulate_colsum(const float* q, const float* k, float* out, int B,
             if (it.s0 < 0 || it.s1 > p.NQB || it.kt < 0 || it.kt >= p.NKC || it.h < 0 || it.h >= H || it.b >= B)
                 return -21;
             const float* nl_bh = neg_lse.data() + ((long long)it.b * H + it.h) * p.lse_rows;
+            int f_lo, f_hi;
+            colsum_full_range(p, it.kt, f_lo, f_hi);
             for (int st = it.s0; st < it.s1; ++st) {
                 ++walked;
                 const bool full = colsum_tile_full(p, it.kt, st);
+                if (full != (st >= f_lo && st < f_hi)) return -27;   // the range form of the rule disagrees
                 const float* nl = nl_bh + (long long)st * BLOCK;
                 for (int g = 0; g < G; ++g) {
                     const int col0 = g * GC;
