@@ -31,6 +31,15 @@ namespace fcs {
 
 constexpr int NUM_TBUF = 2;        // accumulator buffers of 256 tensor-memory columns
 constexpr int TMEM_COLS = 512;
+// Of every 16 pairs of exps on fully visible tiles, this many are evaluated by
+// the polynomial on the FMA pipe instead of the special-function unit (which
+// issues 16 results per clock per SM and is the busiest unit of both passes).
+#ifndef FCS_POLY_PAIRS
+#define FCS_POLY_PAIRS 5
+#endif
+__host__ __device__ constexpr bool pair_uses_polynomial(int pair) {
+    return ((pair * FCS_POLY_PAIRS) % 16) < FCS_POLY_PAIRS;
+}
 constexpr int NUM_LSE = 4;         // per-query-block log-sum-exp vectors in flight (column pass)
 // Consumer warps come in groups of four (a group covers the 128 tensor-memory
 // lanes); every group takes an equal run of the columns of each accumulator.
@@ -112,6 +121,27 @@ __device__ __forceinline__ void stats_block64(const uint32_t (&ra)[32], const ui
         l *= ex2_approx(m - m_safe);
         m = m_safe;
     }
+    if constexpr (!MASKED) {
+        // exp2(c*s - m) two at a time; a fixed share of the pairs avoids the special-function unit
+        const f32x2 c2 = pack2(c, c), nm2 = pack2(-m_safe, -m_safe);
+        f32x2 s0 = pack2(0.f, 0.f), s1 = s0;
+#pragma unroll
+        for (int pr = 0; pr < 32; ++pr) {
+            const f32x2 t = fma2(pack2(s[2 * pr], s[2 * pr + 1]), c2, nm2);
+            f32x2 e;
+            if (pair_uses_polynomial(pr & 15)) {
+                e = ex2_poly2(t);
+            } else {
+                float t0, t1;
+                unpack2(t, t0, t1);
+                e = pack2(ex2_approx(t0), ex2_approx(t1));
+            }
+            if (pr & 1) s1 = add2(s1, e); else s0 = add2(s0, e);
+        }
+        float x0, x1;
+        unpack2(add2(s0, s1), x0, x1);
+        l += x0 + x1;
+    } else {
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
     for (int j = 0; j < 64; j += 4) {
@@ -127,6 +157,7 @@ __device__ __forceinline__ void stats_block64(const uint32_t (&ra)[32], const ui
         a2 += ex2_approx(t2); a3 += ex2_approx(t3);
     }
     l += (a0 + a1) + (a2 + a3);
+    }
 }
 
 // Add exp2(c*s - lse[q]) of 32 query columns into a key's accumulators.  `nl`
@@ -135,6 +166,26 @@ __device__ __forceinline__ void stats_block64(const uint32_t (&ra)[32], const ui
 template <bool MASKED>
 __device__ __forceinline__ void colsum_chunk(const uint32_t (&r)[32], const float4* nl, int first_valid,
                                              int end_valid, float c, float (&acc)[4]) {
+    if constexpr (!MASKED) {
+        const f32x2 c2 = pack2(c, c);
+        f32x2 a01 = pack2(acc[0], acc[1]), a23 = pack2(acc[2], acc[3]);
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 n = nl[j >> 2];
+            const f32x2 ta = fma2(pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), c2, pack2(n.x, n.y));
+            const f32x2 tb = fma2(pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), c2, pack2(n.z, n.w));
+            f32x2 ea, eb;
+            float u0, u1;
+            if (pair_uses_polynomial((j >> 1) & 15)) { ea = ex2_poly2(ta); }
+            else { unpack2(ta, u0, u1); ea = pack2(ex2_approx(u0), ex2_approx(u1)); }
+            if (pair_uses_polynomial(((j >> 1) + 1) & 15)) { eb = ex2_poly2(tb); }
+            else { unpack2(tb, u0, u1); eb = pack2(ex2_approx(u0), ex2_approx(u1)); }
+            a01 = add2(a01, ea);
+            a23 = add2(a23, eb);
+        }
+        unpack2(a01, acc[0], acc[1]);
+        unpack2(a23, acc[2], acc[3]);
+    } else {
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
         const float4 n = nl[j >> 2];
@@ -150,6 +201,7 @@ __device__ __forceinline__ void colsum_chunk(const uint32_t (&r)[32], const floa
         }
         acc[0] += ex2_approx(t0); acc[1] += ex2_approx(t1);
         acc[2] += ex2_approx(t2); acc[3] += ex2_approx(t3);
+    }
     }
 }
 

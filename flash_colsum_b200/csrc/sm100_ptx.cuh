@@ -193,4 +193,59 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// Two fp32 values in one 64-bit register, for the packed fp32 instructions.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 add2_round_down(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+// exp2 of two values without the special-function unit, for arguments <= 0
+// (clamped at -126, where the result is 2^-126 rather than 0).
+// t = n + f with n = floor(t): adding 1.5 * 2^23 rounding down leaves n in the low
+// mantissa bits; 2^f on [0, 1) is a cubic with p(0) = 1 whose relative error is
+// below 9.4e-5 and averages to zero over f; n goes straight into the exponent.
+__device__ __forceinline__ f32x2 ex2_poly2(f32x2 t) {
+    float t0, t1;
+    unpack2(t, t0, t1);
+    const f32x2 tc = pack2(fmaxf(t0, -126.f), fmaxf(t1, -126.f));
+    const f32x2 magic = pack2(12582912.f, 12582912.f);
+    const f32x2 r = add2_round_down(tc, magic);
+    const f32x2 f = sub2(tc, sub2(r, magic));
+    f32x2 p = fma2(f, pack2(0.0774298682808876f, 0.0774298682808876f),
+                   pack2(0.2271328568458557f, 0.2271328568458557f));
+    p = fma2(p, f, pack2(0.6952500343322754f, 0.6952500343322754f));
+    p = fma2(p, f, pack2(1.0f, 1.0f));
+    float p0, p1, r0, r1;
+    unpack2(p, p0, p1);
+    unpack2(r, r0, r1);
+    p0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(r0) << 23));
+    p1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(r1) << 23));
+    return pack2(p0, p1);
+}
+
 }  // namespace fcs
