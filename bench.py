@@ -244,6 +244,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
     ap.add_argument("--skip-long-context", action="store_true")
+    ap.add_argument("--nccl-reduce", action="store_true",
+                    help="reduce the head-sharded partials with an NCCL all-reduce instead of peer-memory atomics")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the device passes of --workload (used for ncu captures)")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
@@ -365,19 +367,32 @@ def main():
         k5 *= (torch.rand(w5.Sk, generator=g, device=dev) * 1.5 + 0.5)[None, None, :, None]
         q5, k5 = q5.to(torch.bfloat16), k5.to(torch.bfloat16)
 
+        peer = None
+        reduce_kind = "single GPU"
+        if world > 1:
+            reduce_kind = "one NCCL all-reduce of (1,131072) fp32"
+            if not args.nccl_reduce:
+                try:
+                    from flash_colsum_b200.sharded import PeerAccumulator
+                    peer = PeerAccumulator(w5.Sk, dev, dst=0)
+                    reduce_kind = ("column-pass atomics into rank 0's peer-mapped (1,131072) fp32 buffer over "
+                                   "NVLink, device barriers before and after (no collective)")
+                except Exception as exc:   # symmetric memory not available: keep the collective
+                    peer = None
+                    reduce_kind += f" (peer-memory path unavailable: {type(exc).__name__})"
+
         def long_step():
-            return flash_colsum_head_sharded(q5, k5, w5.H, is_causal=True)
+            return flash_colsum_head_sharded(q5, k5, w5.H, is_causal=True, peer=peer)
 
         t5 = time_steps(long_step, max(5, args.steps // 2), 3, flush_buf, barrier)
         ms5 = max_over_ranks(sum(t5) / len(t5))
         out5 = long_step()
         torch.cuda.synchronize()
         long_ctx = {"workload": "c5: causal H=32 Q=512 K=131072 D=128 bf16, outlier keys",
-                    "parallelism": f"heads sharded over {world} GPU(s), one NCCL all-reduce of (1,131072) fp32"
-                    if world > 1 else "single GPU",
+                    "parallelism": f"heads sharded over {world} GPU(s); reduce: {reduce_kind}",
                     "scaling": "strong", "ms_per_call": ms5, "value": w5.flop / (ms5 * 1e-3) / 1e12,
                     "unit": UNIT, "frac_of_peak": w5.flop / (ms5 * 1e-3) / 1e12 / peaks["tflops"],
-                    "row_sum": float(out5.sum().item())}
+                    "row_sum_on_rank0": float(out5.sum().item())}
         del q5, k5
     assert fc.device_status() == 0
 

@@ -13,7 +13,7 @@ EXPORTED_SYMBOLS = (
     "fcs_version", "fcs_last_error", "fcs_workspace_bytes",
     "fcs_colsum_batched", "fcs_colsum_non_batched", "fcs_colsum_causal",
     "fcs_set_profiling", "fcs_last_pass_ms", "fcs_plan_info",
-    "fcs_colsum_batched_static_scratch",
+    "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate",
 )
 
 FCS_OK = 0
@@ -68,6 +68,8 @@ def load() -> ctypes.CDLL:
     lib.fcs_colsum_causal.restype = _i
     lib.fcs_colsum_causal.argtypes = [_p, _p, _p, _i, _i, _i, _i, _i] + [_i64] * 4 + \
         [_f, _i, _i, _p, _sz, _p, _p]
+    lib.fcs_colsum_causal_accumulate.restype = _i
+    lib.fcs_colsum_causal_accumulate.argtypes = lib.fcs_colsum_causal.argtypes
     lib.fcs_colsum_batched_static_scratch.restype = _i
     lib.fcs_colsum_batched_static_scratch.argtypes = [_p, _p, _p, _i64, _i, _i, _i, _i, _i] + [_i64] * 6 + \
         [_f, _i, _i, _p, _p]

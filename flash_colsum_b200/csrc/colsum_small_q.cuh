@@ -166,7 +166,7 @@ colsum_small_q_kernel(const SmallQParams p) {
 #pragma unroll
         for (int r = 0; r < SMALLQ_MAX_ROWS; ++r)
             if (r < p.R) v += sc[(size_t)r * p.Sk + k] * w[r];
-        atomicAdd(ob + k, v);
+        atomicAdd_system(ob + k, v);   // `out` may live on another GPU
     }
 }
 

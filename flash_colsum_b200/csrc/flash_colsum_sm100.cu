@@ -383,7 +383,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
         const float c = p.c;
         bool ok = true;
 
-        if constexpr (MODE == MODE_STATS) {
+        if (MODE == MODE_STATS && p.clear_out) {
             // the output is accumulated by the column pass: clear it here
             const long long n_out = (long long)p.B * p.Sk;
             for (long long idx = (long long)blockIdx.x * CONSUMER_THREADS + threadIdx.x; idx < n_out;
@@ -479,8 +479,9 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
                 if (it.flush()) {
                     const int k_abs = it.kt * TILE + row;
                     if (k_abs < p.Sk)
-                        atomicAdd(p.out + (long long)it.b * p.out_ld + k_abs,
-                                  (acc[0] + acc[1]) + (acc[2] + acc[3]));
+                        // system scope: `out` may live on another GPU and take adds from several
+                        atomicAdd_system(p.out + (long long)it.b * p.out_ld + k_abs,
+                                         (acc[0] + acc[1]) + (acc[2] + acc[3]));
                     acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
                 }
             }
@@ -650,9 +651,11 @@ static cudaError_t launch_small_q_t(const SmallQParams& sp, int grid, size_t sme
 
 static int launch_small_q(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int R, int Sk,
                           int D, int dtype, int64_t qsb, int64_t qsh, int64_t qss, int64_t ksb, int64_t ksh,
-                          int64_t kss, float scale, int causal, int k_past, int h_norm, cudaStream_t stream) {
-    cudaError_t e = cudaMemset2DAsync(out, (size_t)out_ld * sizeof(float), 0, (size_t)Sk * sizeof(float), (size_t)B,
-                                      stream);
+                          int64_t kss, float scale, int causal, int k_past, int h_norm, bool clear_out,
+                          cudaStream_t stream) {
+    cudaError_t e = cudaSuccess;
+    if (clear_out)
+        e = cudaMemset2DAsync(out, (size_t)out_ld * sizeof(float), 0, (size_t)Sk * sizeof(float), (size_t)B, stream);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "clearing the output failed: %s", cudaGetErrorString(e));
     SmallQParams sp;
     sp.q = q; sp.k = k; sp.out = out; sp.out_ld = out_ld;
@@ -676,7 +679,8 @@ static int launch_small_q(const void* q, const void* k, float* out, int64_t out_
 static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int Sq_full,
                        int Sk, int D, int dtype, int64_t qsb, int64_t qsh, int64_t qss, int64_t ksb,
                        int64_t ksh, int64_t kss, float scale, int causal, int k_past, int cls_n, int h_norm,
-                       void* workspace, size_t workspace_bytes, int* status, void* stream_v) {
+                       void* workspace, size_t workspace_bytes, int* status, void* stream_v,
+                       bool clear_out = true) {
     g_err[0] = 0;
     if (B <= 0 || H <= 0 || Sq_full <= 0 || Sk <= 0)
         return fail(FCS_ERR_INVALID_ARGUMENT, "sizes must be positive (B=%d H=%d Sq=%d Sk=%d)", B, H, Sq_full, Sk);
@@ -706,7 +710,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
             for (int i = 0; i < 3; ++i) cudaEventRecord(tms->ev[i], stream);
         }
         rc = launch_small_q(q, k, out, out_ld, B, H, Sq, Sk, D, dtype, qsb, qsh, qss, ksb, ksh, kss, scale,
-                            causal, k_past, h_norm, stream);
+                            causal, k_past, h_norm, clear_out, stream);
         if (rc == FCS_OK && tms) { cudaEventRecord(tms->ev[3], stream); tms->recorded = true; }
         return rc;
     }
@@ -725,6 +729,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     p.part = reinterpret_cast<uint8_t*>(workspace) + part_off;
     p.out = out;
     p.out_ld = out_ld;
+    p.clear_out = clear_out ? 1 : 0;
     p.status = status;
     p.c = fabsf(scale) * 1.4426950408889634f;
     p.log2_norm = log2f((float)h_norm * (float)Sq);
@@ -896,6 +901,15 @@ int fcs_colsum_batched_static_scratch(const void* q, const void* k, float* out, 
     return fcs::colsum_impl(q, k, out, out_ld, B, H, S, S, D, dtype, q_stride_b, q_stride_h, q_stride_s,
                             k_stride_b, k_stride_h, k_stride_s, scale, 0, 0, cls_n, h_norm, scratch,
                             (size_t)FCS_STATIC_SCRATCH_BYTES, status, stream);
+}
+
+int fcs_colsum_causal_accumulate(const void* q, const void* k, float* out, int H, int q_len, int k_len, int D,
+                                 int dtype, int64_t q_stride_h, int64_t q_stride_s, int64_t k_stride_h,
+                                 int64_t k_stride_s, float scale, int k_past, int h_norm, void* workspace,
+                                 size_t workspace_bytes, int* status, void* stream) {
+    return fcs::colsum_impl(q, k, out, k_len, 1, H, q_len, k_len, D, dtype, q_stride_h * H, q_stride_h,
+                            q_stride_s, k_stride_h * H, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm,
+                            workspace, workspace_bytes, status, stream, /*clear_out=*/false);
 }
 
 }  // extern "C"

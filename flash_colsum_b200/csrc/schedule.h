@@ -32,6 +32,7 @@ struct Problem {
     int NQB, NKB;       // 256-row query blocks / key blocks (streamed operands)
     int NKC;            // key tiles that hold at least one visible key (column pass)
     int causal, k_past; // key j is visible to query i iff j <= k_past + i
+    int clear_out;      // the statistics pass zeroes `out` before the column pass adds into it
     int nsplit;         // key ranges per (b, h, query tile) in the statistics pass
     int kreg;           // leading key tiles that every query block contributes to
     long long stats_items;

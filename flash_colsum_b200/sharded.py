@@ -11,6 +11,7 @@ flash_colsum/kernel_causal.py:94 and kernel_noncausal_batched.py:102.
 
 from __future__ import annotations
 
+import os
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -26,6 +27,41 @@ def shard_range(n: int, world_size: int, rank: int) -> Tuple[int, int]:
     base, extra = divmod(n, world_size)
     lo = rank * base + min(rank, extra)
     return lo, lo + base + (1 if rank < extra else 0)
+
+
+class PeerAccumulator:
+    """One fp32 ``(1, S_k)`` buffer per rank in symmetric (peer-mapped) memory.
+
+    Used to fold the reduce of the head-sharded causal call into the kernels: the
+    buffer of rank ``dst`` is cleared, every rank's column pass adds its per-key
+    sums straight into it over NVLink (plain system-scope atomic adds to a peer
+    address, no multicast), and a device-side barrier on each side of the
+    launches orders the clear, the adds and the read.  One process per GPU; the
+    constructor is a collective over ``group``.
+    """
+
+    def __init__(self, k_len: int, device: torch.device, group=None, dst: int = 0):
+        # peer mappings only: keep NVLink multicast objects out of it
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.k_len = int(k_len)
+        self.dst = int(dst)
+        self.rank = dist.get_rank(group)
+        self.local = symm_mem.empty((1, self.k_len), dtype=torch.float32, device=device)
+        self.handle = symm_mem.rendezvous(self.local, group)
+        self.target = self.handle.get_buffer(self.dst, (1, self.k_len), torch.float32)
+        self.local.zero_()
+
+    def reduce(self, launch: Callable[[torch.Tensor], None]) -> torch.Tensor:
+        """Run ``launch(target)`` on every rank between two barriers; rank ``dst``
+        gets the summed result (its local buffer), the others their stale buffer."""
+        if self.rank == self.dst:
+            self.local.zero_()
+        self.handle.barrier(channel=0)
+        launch(self.target)
+        self.handle.barrier(channel=1)
+        return self.local
 
 
 def _local_partial(query: torch.Tensor, key: torch.Tensor, scale: float, is_causal: bool,
@@ -49,6 +85,7 @@ def flash_colsum_head_sharded(
     group: Optional[dist.ProcessGroup] = None,
     dst: Optional[int] = None,
     local_fn: Callable = _local_partial,
+    peer: Optional[PeerAccumulator] = None,
 ) -> torch.Tensor:
     """Column means when each rank holds ``(B, H_local, S, D)`` of the heads.
 
@@ -56,6 +93,10 @@ def flash_colsum_head_sharded(
     rank returns the full result (all-reduce); otherwise only rank ``dst`` does
     (reduce) and the others return their partial.  A rank may hold zero heads
     (``H_local == 0``): it contributes zeros.
+
+    With ``peer`` (causal only) there is no collective at all: every rank's
+    kernels add into the buffer of rank ``peer.dst`` through peer memory, and only
+    that rank's return value is the result.
     """
     if query_shard.ndim != 4 or key_shard.ndim != 4:
         raise ValueError("Expected 4D tensors")
@@ -68,6 +109,17 @@ def flash_colsum_head_sharded(
         raise ValueError(f"shard has {h_local} heads but h_total is {h_total}")
     if scale is None:
         scale = 1.0 / (D ** 0.5)
+    if peer is not None:
+        if not is_causal:
+            raise ValueError("the peer-memory reduce is implemented for the causal call")
+        if peer.k_len != key_shard.shape[2]:
+            raise ValueError(f"peer buffer holds {peer.k_len} keys, the call has {key_shard.shape[2]}")
+
+        def launch(target: torch.Tensor) -> None:
+            if h_local > 0:
+                ops._flash_colsum_causal(query_shard, key_shard, scale, h_norm=h_total, accumulate_into=target)
+
+        return peer.reduce(launch)
     if h_local == 0:
         partial = torch.zeros(B, key_shard.shape[2], dtype=torch.float32, device=query_shard.device)
     else:
@@ -80,4 +132,4 @@ def flash_colsum_head_sharded(
     return partial
 
 
-__all__ = ["shard_range", "flash_colsum_head_sharded"]
+__all__ = ["shard_range", "flash_colsum_head_sharded", "PeerAccumulator"]

@@ -106,6 +106,25 @@ int fcs_colsum_causal(const void *q, const void *k, float *out,
                       void *workspace, size_t workspace_bytes, int *status, void *stream);
 
 /*
+ * Causal column mean ADDED into `out`: same arguments and arithmetic as
+ * fcs_colsum_causal, but `out` is not cleared first.  It exists for head-sharded
+ * calls that flush into one buffer: every shard passes the global head count as
+ * h_norm, the caller clears the buffer once, and each shard's column pass adds
+ * its fp32 per-key sums with system-scope atomics -- so `out` may be a
+ * peer-mapped address on another GPU of the node (the reduce over NVLink then
+ * happens inside the kernel, with no separate collective).  The caller orders
+ * the clear before, and the read after, all shards' calls.  No counterpart in
+ * the reference, which has no multi-GPU path (its single-GPU launcher is
+ * flash_colsum/kernel_causal.py:94).
+ */
+int fcs_colsum_causal_accumulate(const void *q, const void *k, float *out,
+                                 int H, int q_len, int k_len, int D, int dtype,
+                                 int64_t q_stride_h, int64_t q_stride_s,
+                                 int64_t k_stride_h, int64_t k_stride_s,
+                                 float scale, int k_past, int h_norm,
+                                 void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+/*
  * Batched non-causal column mean for callers that cannot give the library a
  * workspace.  It has no counterpart in the reference.
  *
