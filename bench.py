@@ -73,7 +73,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
@@ -172,15 +172,19 @@ def run_reference_arm(args):
     for _ in range(max(1, min(args.warmup, 2))):
         naive_colsum_torch(q, k)
     times = []
+    # one step = one batch entry on the host cores; bounded so that the run ends in minutes
+    t_stop = time.perf_counter() + 120.0
     for _ in range(args.steps):
         t0 = time.perf_counter()
         naive_colsum_torch(q, k)
         times.append(time.perf_counter() - t0)
+        if time.perf_counter() > t_stop:
+            break
     mean_s = sum(times) / len(times)
     value = sample.flop / mean_s / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean_s * 1e3,
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": mean_s * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
         "data": "synthetic",
         "config": {"workload": "c2: non-causal B=8 H=16 S=2048 D=64", "step": "one batch entry (B=1) per step",
@@ -239,8 +243,8 @@ def kernel_only(args, fc, _cabi, dev, flush_buf, peaks):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
     ap.add_argument("--skip-long-context", action="store_true")
@@ -315,7 +319,7 @@ def main():
     # per-kernel durations (events recorded by the library around each pass)
     _cabi.set_profiling(True)
     stats_ms, col_ms = [], []
-    for _ in range(max(5, min(args.steps, 20))):
+    for _ in range(max(5, min(args.steps, 50))):
         flush_buf.zero_()
         fc.flash_colsum(q, k)
         a, _, c = _cabi.last_pass_ms()
@@ -342,7 +346,7 @@ def main():
         return fc.flash_colsum(qd, kd).cpu()
 
     e2e_times = []
-    for i in range(3 + max(5, args.steps // 2)):
+    for i in range(3 + max(5, min(args.steps // 2, 30))):
         torch.cuda.synchronize()
         barrier()
         t0 = time.perf_counter()
@@ -384,7 +388,7 @@ def main():
         def long_step():
             return flash_colsum_head_sharded(q5, k5, w5.H, is_causal=True, peer=peer)
 
-        t5 = time_steps(long_step, max(5, args.steps // 2), 3, flush_buf, barrier)
+        t5 = time_steps(long_step, max(5, min(args.steps // 2, 30)), 3, flush_buf, barrier)
         ms5 = max_over_ranks(sum(t5) / len(t5))
         out5 = long_step()
         torch.cuda.synchronize()
