@@ -20,6 +20,7 @@
 #include "sm100_ptx.cuh"
 #include "schedule.h"
 #include "colsum_small_q.cuh"
+#include "colsum_math.cuh"
 
 #include <math.h>
 #include <stdarg.h>
@@ -32,15 +33,6 @@ namespace fcs {
 
 constexpr int NUM_TBUF = 2;        // accumulator buffers of 256 tensor-memory columns
 constexpr int TMEM_COLS = 512;
-// Of every 16 pairs of exps on fully visible tiles, this many are evaluated by
-// the polynomial on the FMA pipe instead of the special-function unit (which
-// issues 16 results per clock per SM and is the busiest unit of both passes).
-#ifndef FCS_POLY_PAIRS
-#define FCS_POLY_PAIRS 5
-#endif
-__host__ __device__ constexpr bool pair_uses_polynomial(int pair) {
-    return ((pair * FCS_POLY_PAIRS) % 16) < FCS_POLY_PAIRS;
-}
 constexpr int NUM_LSE = 4;         // per-query-block log-sum-exp vectors in flight (column pass)
 // Consumer warps come in groups of four (a group covers the 128 tensor-memory
 // lanes); every group takes an equal run of the columns of each accumulator.
@@ -53,18 +45,25 @@ constexpr int MMA_WARP = CONSUMER_WARPS + 1;
 constexpr int THREADS = 32 * (CONSUMER_WARPS + 2);
 static_assert(GROUP_COLS == 64, "a group consumes one 64-column block per step");
 
-template <int D>
+constexpr int EXT_K = 16;                        // extra contraction columns that carry -(lse)/c
+constexpr int EXT_ROW_BYTES = EXT_K * 2;
+constexpr int EXT_A_BYTES = TILE * EXT_ROW_BYTES;    // the constant key-side columns
+constexpr int EXT_B_BYTES = BLOCK * EXT_ROW_BYTES;   // the query-side columns of one block
+
+template <int D, bool EXT>
 struct Layout {
     static constexpr int SLABS = D / 64;              // 64-element (128-byte) column slabs
     static constexpr int A_SLAB_BYTES = TILE * 128;
     static constexpr int B_SLAB_BYTES = BLOCK * 128;
     static constexpr int A_BYTES = SLABS * A_SLAB_BYTES;
     static constexpr int B_BYTES = SLABS * B_SLAB_BYTES;
+    static constexpr int B_STAGE_BYTES = B_BYTES + (EXT ? EXT_B_BYTES : 0);   // block, then its extension
     static constexpr int NS = (D == 64) ? 4 : 2;      // streamed-operand stages
     static constexpr int A_OFF = 0;
     static constexpr int B_OFF = 2 * A_BYTES;
-    static constexpr int LSE_OFF = B_OFF + NS * B_BYTES;   // NUM_LSE slots of 256 floats
-    static constexpr int BAR_OFF = LSE_OFF + NUM_LSE * BLOCK * 4;
+    static constexpr int EXTA_OFF = B_OFF + NS * B_STAGE_BYTES;             // 128 rows of the constant
+    static constexpr int LSE_OFF = EXTA_OFF + (EXT ? EXT_A_BYTES : 0);      // NUM_LSE slots of 256 floats
+    static constexpr int BAR_OFF = LSE_OFF + (EXT ? 0 : NUM_LSE * BLOCK * 4);
     // barriers: a_full[2] a_empty[2] b_full[NS] b_empty[NS] t_full[2] t_empty[2] merge[2]
     //           l_full[NUM_LSE] l_empty[NUM_LSE]
     static constexpr int NUM_BARS = 4 + 2 * NS + 2 * NUM_TBUF + 2 + 2 * NUM_LSE;
@@ -72,139 +71,8 @@ struct Layout {
     static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // float2[2][groups-1][128]
     static constexpr int TOTAL = MERGE_OFF + 2 * (CONSUMER_GROUPS - 1) * TILE * 8;
     static constexpr int DYN_BYTES = TOTAL + 1024;    // slack to align the base to 1024
+    static_assert(DYN_BYTES <= 227 * 1024, "shared memory budget");
 };
-
-// ---------------------------------------------------------------------------
-// Consumer math
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float r;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
-}
-
-// Online (max, sum) update of one query row with 64 more scores (two 32-column
-// register blocks).  `last_valid`: columns 0..last_valid are visible (>= 63: all).
-template <bool MASKED>
-__device__ __forceinline__ void stats_block64(const uint32_t (&ra)[32], const uint32_t (&rb)[32],
-                                              int last_valid, float c, float& m, float& l) {
-    float s[64];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        s[j] = __uint_as_float(ra[j]);
-        s[32 + j] = __uint_as_float(rb[j]);
-    }
-    if (MASKED) {
-#pragma unroll
-        for (int j = 0; j < 64; ++j) s[j] = (j <= last_valid) ? s[j] : -INFINITY;
-    }
-    float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
-    float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
-#pragma unroll
-    for (int j = 12; j < 60; j += 8) {
-        m0 = max3(m0, s[j], s[j + 1]);
-        m1 = max3(m1, s[j + 2], s[j + 3]);
-        m2 = max3(m2, s[j + 4], s[j + 5]);
-        m3 = max3(m3, s[j + 6], s[j + 7]);
-    }
-    m0 = max3(m0, s[60], s[61]);
-    m1 = max3(m1, s[62], s[63]);
-    const float cm = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-    float m_safe;
-    if (MASKED) {   // a row may see nothing of this block (or nothing yet): keep -inf out of the arithmetic
-        const float scaled = (cm == -INFINITY) ? -INFINITY : cm * c;
-        const float m_new = fmaxf(m, scaled);
-        m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-        l *= ex2_approx(m - m_safe);
-        m = m_new;
-    } else {        // all 64 scores are finite
-        m_safe = fmaxf(m, cm * c);
-        l *= ex2_approx(m - m_safe);
-        m = m_safe;
-    }
-    if constexpr (!MASKED) {
-        // exp2(c*s - m) two at a time; a fixed share of the pairs avoids the special-function unit
-        const f32x2 c2 = pack2(c, c), nm2 = pack2(-m_safe, -m_safe);
-        f32x2 s0 = pack2(0.f, 0.f), s1 = s0;
-#pragma unroll
-        for (int pr = 0; pr < 32; ++pr) {
-            const f32x2 t = fma2(pack2(s[2 * pr], s[2 * pr + 1]), c2, nm2);
-            f32x2 e;
-            if (pair_uses_polynomial(pr & 15)) {
-                e = ex2_poly2(t);
-            } else {
-                float t0, t1;
-                unpack2(t, t0, t1);
-                e = pack2(ex2_approx(t0), ex2_approx(t1));
-            }
-            if (pr & 1) s1 = add2(s1, e); else s0 = add2(s0, e);
-        }
-        float x0, x1;
-        unpack2(add2(s0, s1), x0, x1);
-        l += x0 + x1;
-    } else {
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-    for (int j = 0; j < 64; j += 4) {
-        float t0 = fmaf(s[j], c, -m_safe), t1 = fmaf(s[j + 1], c, -m_safe);
-        float t2 = fmaf(s[j + 2], c, -m_safe), t3 = fmaf(s[j + 3], c, -m_safe);
-        if (MASKED) {   // c may be 0 and s -inf: select after the multiply
-            t0 = (j <= last_valid) ? t0 : -INFINITY;
-            t1 = (j + 1 <= last_valid) ? t1 : -INFINITY;
-            t2 = (j + 2 <= last_valid) ? t2 : -INFINITY;
-            t3 = (j + 3 <= last_valid) ? t3 : -INFINITY;
-        }
-        a0 += ex2_approx(t0); a1 += ex2_approx(t1);
-        a2 += ex2_approx(t2); a3 += ex2_approx(t3);
-    }
-    l += (a0 + a1) + (a2 + a3);
-    }
-}
-
-// Add exp2(c*s - lse[q]) of 32 query columns into a key's accumulators.  `nl`
-// points at the 32 values -(lse) of these columns in shared memory.  Columns
-// first_valid <= j < end_valid of this chunk are visible.
-template <bool MASKED>
-__device__ __forceinline__ void colsum_chunk(const uint32_t (&r)[32], const float4* nl, int first_valid,
-                                             int end_valid, float c, float (&acc)[4]) {
-    if constexpr (!MASKED) {
-        const f32x2 c2 = pack2(c, c);
-        f32x2 a01 = pack2(acc[0], acc[1]), a23 = pack2(acc[2], acc[3]);
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-            const float4 n = nl[j >> 2];
-            const f32x2 ta = fma2(pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), c2, pack2(n.x, n.y));
-            const f32x2 tb = fma2(pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), c2, pack2(n.z, n.w));
-            f32x2 ea, eb;
-            float u0, u1;
-            if (pair_uses_polynomial((j >> 1) & 15)) { ea = ex2_poly2(ta); }
-            else { unpack2(ta, u0, u1); ea = pack2(ex2_approx(u0), ex2_approx(u1)); }
-            if (pair_uses_polynomial(((j >> 1) + 1) & 15)) { eb = ex2_poly2(tb); }
-            else { unpack2(tb, u0, u1); eb = pack2(ex2_approx(u0), ex2_approx(u1)); }
-            a01 = add2(a01, ea);
-            a23 = add2(a23, eb);
-        }
-        unpack2(a01, acc[0], acc[1]);
-        unpack2(a23, acc[2], acc[3]);
-    } else {
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-        const float4 n = nl[j >> 2];
-        float t0 = fmaf(__uint_as_float(r[j]), c, n.x);
-        float t1 = fmaf(__uint_as_float(r[j + 1]), c, n.y);
-        float t2 = fmaf(__uint_as_float(r[j + 2]), c, n.z);
-        float t3 = fmaf(__uint_as_float(r[j + 3]), c, n.w);
-        if (MASKED) {
-            t0 = (j >= first_valid && j < end_valid) ? t0 : -INFINITY;
-            t1 = (j + 1 >= first_valid && j + 1 < end_valid) ? t1 : -INFINITY;
-            t2 = (j + 2 >= first_valid && j + 2 < end_valid) ? t2 : -INFINITY;
-            t3 = (j + 3 >= first_valid && j + 3 < end_valid) ? t3 : -INFINITY;
-        }
-        acc[0] += ex2_approx(t0); acc[1] += ex2_approx(t1);
-        acc[2] += ex2_approx(t2); acc[3] += ex2_approx(t3);
-    }
-    }
-}
 
 // A group's 64 columns of one accumulator.  `taddr`, `lim`, `thr`, `end` and
 // `nl` are relative to the group's first column.
@@ -229,15 +97,28 @@ __device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, in
     colsum_chunk<MASKED>(r, nl + 8, thr - 32, end - 32, c, acc);
 }
 
+template <bool MASKED>
+__device__ __forceinline__ void colsum_tile_ext(uint32_t taddr, int thr, int end, float c, float (&acc)[4]) {
+    uint32_t r[32];
+    tmem_ld_x32(taddr, r);
+    tmem_ld_wait(r);
+    colsum_chunk_ext<MASKED>(r, thr, end, c, acc);
+    tmem_ld_x32(taddr + 32, r);
+    tmem_ld_wait(r);
+    colsum_chunk_ext<MASKED>(r, thr - 32, end - 32, c, acc);
+}
+
 // ---------------------------------------------------------------------------
 // The streaming kernel.  tm_a: resident operand (box of 128 rows), tm_b:
-// streamed operand (box of 256 rows).
+// streamed operand (box of 256 rows), tm_ext: the 16 extension columns of the
+// query blocks (MODE_COLSUM_EXT only).
 // ---------------------------------------------------------------------------
 template <int D, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
-colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
-                     const __grid_constant__ CUtensorMap tm_b, const Problem p) {
-    using L = Layout<D>;
+colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                     const __grid_constant__ CUtensorMap tm_ext, const Problem p) {
+    constexpr bool EXT = (MODE == MODE_COLSUM_EXT);
+    using L = Layout<D, EXT>;
     using Items = typename ItemsOf<MODE>::type;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -272,9 +153,19 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
         *abort_flag = 0;
         mbar_fence_init();
     }
+    if constexpr (EXT) {
+        // the key-side constant of the extension: every 16-byte piece is (k, k, k, 0, 0, 0, 0, 0),
+        // which reads the same under any swizzle of the pieces
+        const uint32_t k16 = p.ext_bf16 ? 0x3F80u : 0x5C00u;   // bf16 1.0 / fp16 256.0
+        uint4* ones = reinterpret_cast<uint4*>(smem + L::EXTA_OFF);
+        for (int i = threadIdx.x; i < EXT_A_BYTES / 16; i += THREADS)
+            ones[i] = make_uint4(k16 | (k16 << 16), k16, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     if (warp == PRODUCER_WARP && lane == 0) {
         prefetch_tensormap(&tm_a);
         prefetch_tensormap(&tm_b);
+        if constexpr (EXT) prefetch_tensormap(&tm_ext);
     }
     if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -314,14 +205,18 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
                 const float* lse_src = nullptr;
                 if constexpr (MODE == MODE_COLSUM)
                     lse_src = p.neg_lse + ((long long)it.b * p.H + it.h) * p.lse_rows;
+                const int bh = it.b * p.H + it.h;
                 for (int st = it.s0; st < it.s1; ++st, ++n) {
                     if (!wait_all(b_empty(stage), phase ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
                     if (elect_one_sync()) {
-                        mbar_arrive_expect_tx(b_full(stage), L::B_BYTES);
+                        mbar_arrive_expect_tx(b_full(stage), L::B_STAGE_BYTES);
 #pragma unroll
                         for (int sl = 0; sl < L::SLABS; ++sl)
-                            tma_load_4d(b_smem + stage * L::B_BYTES + sl * L::B_SLAB_BYTES, &tm_b,
+                            tma_load_4d(b_smem + stage * L::B_STAGE_BYTES + sl * L::B_SLAB_BYTES, &tm_b,
                                         b_full(stage), sl * 64, it.b_row(st), it.h, it.b);
+                        if constexpr (EXT)
+                            tma_load_3d(b_smem + stage * L::B_STAGE_BYTES + L::B_BYTES, &tm_ext, b_full(stage),
+                                        0, it.b_row(st), bh);
                     }
                     if constexpr (MODE == MODE_COLSUM) {
                         // -(lse) of the 256 queries of this block, for the consumers
@@ -355,7 +250,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
                     const int buf = n & (NUM_TBUF - 1);
                     if (!wait_all(t_empty(buf), ((n >> 1) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t db = umma_desc_k_sw128(b_smem + stage * L::B_BYTES);
+                    const uint64_t db = umma_desc_k_sw128(b_smem + stage * L::B_STAGE_BYTES);
                     const uint32_t d_tmem = tmem_base + buf * BLOCK;
                     if (elect_one_sync()) {
 #pragma unroll
@@ -365,6 +260,9 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
                             const uint64_t ob = (uint64_t)(((ks >> 2) * L::B_SLAB_BYTES + (ks & 3) * 32) >> 4);
                             umma_f16(d_tmem, da + oa, db + ob, p.idesc, ks > 0 ? 1u : 0u);
                         }
+                        if constexpr (EXT)   // + (key-side constant) x (-(lse)/c parts of the queries)
+                            umma_f16(d_tmem, umma_desc_k_sw32(smem_base + L::EXTA_OFF),
+                                     umma_desc_k_sw32(b_smem + stage * L::B_STAGE_BYTES + L::B_BYTES), p.idesc, 1u);
                         umma_commit(b_empty(stage));
                         umma_commit(t_full(buf));
                         if (st + 1 == it.s1) umma_commit(a_empty(ab));
@@ -420,6 +318,17 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
                         const int lim_last_row = stats_last_visible(p, it.qt, st, TILE - 1) - col0;
                         if (lim_last_row >= 0) stats_tile<true>(taddr, lim, c, m_run, l_run);
                     }
+                } else if constexpr (EXT) {
+                    // the accumulator already holds s - lse/c
+                    if (full) {
+                        colsum_tile_ext<false>(taddr, 0, GROUP_COLS, c, acc);
+                    } else {
+                        const int thr = colsum_first_visible(p, it.kt, st, row) - col0;
+                        const int end = colsum_end_visible(p, st) - col0;
+                        // skip the block when no key of the tile is seen by any of its queries
+                        const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - col0;
+                        if (end > 0 && thr_first_row < GROUP_COLS) colsum_tile_ext<true>(taddr, thr, end, c, acc);
+                    }
                 } else {
                     const int ls = n & (NUM_LSE - 1);
                     ok = mbar_wait(l_full(ls), (n / NUM_LSE) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
@@ -466,8 +375,13 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a,
                     const long long bh = (long long)it.b * p.H + it.h;
                     const int q_abs = it.qt * TILE + row;
                     if (p.nsplit == 1) {
-                        p.neg_lse[bh * p.lse_rows + q_abs] =
-                            (q_abs < p.Sq) ? -(mm + log2f(ll) + p.log2_norm) : -INFINITY;
+                        const float nlv = (q_abs < p.Sq) ? -(mm + log2f(ll) + p.log2_norm) : -INFINITY;
+                        p.neg_lse[bh * p.lse_rows + q_abs] = nlv;
+                        uint4 e0, e1;
+                        make_ext_row(nlv, p.inv_c, p.ext_bf16 != 0, e0, e1);
+                        uint4* er = reinterpret_cast<uint4*>(p.ext) + (bh * p.lse_rows + q_abs) * 2;
+                        er[0] = e0;
+                        er[1] = e1;
                     } else {
                         const long long rows = (long long)p.NQ * TILE;
                         reinterpret_cast<float2*>(p.part)[((long long)it.sp * p.B * p.H + bh) * rows + q_abs] =
@@ -520,6 +434,11 @@ __global__ void merge_stats_kernel(const Problem p) {
             v = -(mm + log2f(ll) + p.log2_norm);
         }
         p.neg_lse[bh * p.lse_rows + q_abs] = v;
+        uint4 e0, e1;
+        make_ext_row(v, p.inv_c, p.ext_bf16 != 0, e0, e1);
+        uint4* er = reinterpret_cast<uint4*>(p.ext) + (bh * p.lse_rows + q_abs) * 2;
+        er[0] = e0;
+        er[1] = e1;
     }
 }
 
@@ -605,20 +524,38 @@ static PassTimers* timers_for_current_device() {
     return &t;
 }
 
+// (16, rows, planes) view of the [planes][rows][16] extension columns: boxes of 256
+// rows x 16 elements (32 bytes), 32-byte swizzle.
+static int make_ext_tensor_map(CUtensorMap* m, const void* base, int dtype, long long planes, long long rows) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(FCS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {(cuuint64_t)EXT_K, (cuuint64_t)rows, (cuuint64_t)planes};
+    cuuint64_t strides[2] = {(cuuint64_t)EXT_ROW_BYTES, (cuuint64_t)rows * EXT_ROW_BYTES};
+    cuuint32_t box[3] = {(cuuint32_t)EXT_K, (cuuint32_t)BLOCK, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(m, dtype == FCS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                     3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FCS_ERR_CUDA, "cuTensorMapEncodeTiled (extension) failed with CUresult %d", (int)r);
+    return FCS_OK;
+}
+
 template <int D, int MODE>
-static cudaError_t launch_stream(const CUtensorMap& ta, const CUtensorMap& tb, const Problem& p, int grid,
-                                 cudaStream_t stream) {
+static cudaError_t launch_stream(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& text,
+                                 const Problem& p, int grid, cudaStream_t stream) {
+    using LayoutT = Layout<D, MODE == MODE_COLSUM_EXT>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     auto kern = colsum_stream_kernel<D, MODE>;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             Layout<D>::DYN_BYTES);
+                                             LayoutT::DYN_BYTES);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    kern<<<grid, THREADS, Layout<D>::DYN_BYTES, stream>>>(ta, tb, p);
+    kern<<<grid, THREADS, LayoutT::DYN_BYTES, stream>>>(ta, tb, text, p);
     return cudaGetLastError();
 }
 
@@ -719,19 +656,25 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     Problem p;
     memset(&p, 0, sizeof(p));
     plan(p, B, H, Sq, Sk, causal, k_past, sms);
-    size_t part_off = 0;
-    const size_t need = workspace_layout(p, &part_off);
+    size_t part_off = 0, ext_off = 0;
+    const size_t need = workspace_layout(p, &part_off, &ext_off);
     if (!workspace || workspace_bytes < need)
         return fail(FCS_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
     if (reinterpret_cast<uintptr_t>(workspace) % 256)
         return fail(FCS_ERR_WORKSPACE, "workspace must be 256-byte aligned");
     p.neg_lse = reinterpret_cast<float*>(workspace);
     p.part = reinterpret_cast<uint8_t*>(workspace) + part_off;
+    p.ext = reinterpret_cast<uint8_t*>(workspace) + ext_off;
+    p.ext_bf16 = dtype == FCS_DTYPE_BF16 ? 1 : 0;
     p.out = out;
     p.out_ld = out_ld;
     p.clear_out = clear_out ? 1 : 0;
     p.status = status;
     p.c = fabsf(scale) * 1.4426950408889634f;
+    // -(lse) rides in the MMA of the column pass unless the scale is so small that
+    // -(lse)/c leaves the range of its 16-bit parts
+    const bool use_ext = p.c >= 1e-4f;
+    p.inv_c = use_ext ? (scale < 0.f ? -1.0f : 1.0f) / p.c : 0.f;
     p.log2_norm = log2f((float)h_norm * (float)Sq);
     const uint32_t fmt = dtype == FCS_DTYPE_BF16 ? 1u : 0u;
     // fp32 accumulate, K-major A and B, M = 128, N = 256; a negative scale negates A
@@ -745,14 +688,16 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if ((rc = make_tensor_map(&tq_b, q, dtype, B, H, Sq, D, qsb, qsh, qss, BLOCK)) != FCS_OK) return rc;
     if ((rc = make_tensor_map(&tk_a, k, dtype, B, H, Sk, D, ksb, ksh, kss, TILE)) != FCS_OK) return rc;
     if ((rc = make_tensor_map(&tk_b, k, dtype, B, H, Sk, D, ksb, ksh, kss, BLOCK)) != FCS_OK) return rc;
+    CUtensorMap text = tq_b;   // placeholder when the extension is not used
+    if (use_ext && (rc = make_ext_tensor_map(&text, p.ext, dtype, (long long)B * H, p.lse_rows)) != FCS_OK) return rc;
 
     const int grid1 = (int)(p.stats_items < sms ? p.stats_items : sms);
     const int grid2 = (int)(p.steps_total < sms ? p.steps_total : sms);
     PassTimers* tm = g_profiling ? timers_for_current_device() : nullptr;
     if (tm) { tm->recorded = false; cudaEventRecord(tm->ev[0], stream); }
     cudaError_t e;
-    e = (D == 64) ? launch_stream<64, MODE_STATS>(tq_a, tk_b, p, grid1, stream)
-                  : launch_stream<128, MODE_STATS>(tq_a, tk_b, p, grid1, stream);
+    e = (D == 64) ? launch_stream<64, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream)
+                  : launch_stream<128, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics pass launch failed: %s", cudaGetErrorString(e));
     if (tm) cudaEventRecord(tm->ev[1], stream);
     if (p.nsplit > 1) {
@@ -764,8 +709,12 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
         if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics merge launch failed: %s", cudaGetErrorString(e));
     }
     if (tm) cudaEventRecord(tm->ev[2], stream);
-    e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tk_a, tq_b, p, grid2, stream)
-                  : launch_stream<128, MODE_COLSUM>(tk_a, tq_b, p, grid2, stream);
+    if (use_ext)
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream)
+                      : launch_stream<128, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream);
+    else
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream)
+                      : launch_stream<128, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "column pass launch failed: %s", cudaGetErrorString(e));
     if (tm) { cudaEventRecord(tm->ev[3], stream); tm->recorded = true; }
     return FCS_OK;

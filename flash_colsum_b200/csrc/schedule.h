@@ -24,7 +24,7 @@ constexpr int TILE = 128;      // rows of the resident operand tile (MMA M)
 constexpr int BLOCK = 256;     // rows of the streamed operand block (MMA N)
 constexpr int MAX_SPLIT = 64;  // most key ranges a query tile is split into
 
-enum : int { MODE_STATS = 0, MODE_COLSUM = 1 };
+enum : int { MODE_STATS = 0, MODE_COLSUM = 1, MODE_COLSUM_EXT = 2 };
 
 struct Problem {
     int B, H, Sq, Sk;   // Sq: query rows that enter the mean
@@ -42,6 +42,9 @@ struct Problem {
     float c;            // |scale| * log2(e)
     float log2_norm;    // log2(h_norm * R)
     float* neg_lse;     // [B*H][lse_rows]   -(lse2 + log2_norm)
+    void* ext;          // [B*H][lse_rows][16] 16-bit: neg_lse / c split into three parts (see make_ext_row)
+    float inv_c;        // 1 / c
+    int ext_bf16;       // element type of `ext` (that of the inputs)
     void* part;         // float2 [nsplit][B*H][NQ*128]   (max, sum) per key range
     float* out;
     long long out_ld;
@@ -229,6 +232,7 @@ struct ColsumItems {
 template <int MODE> struct ItemsOf;
 template <> struct ItemsOf<MODE_STATS> { typedef StatsItems type; };
 template <> struct ItemsOf<MODE_COLSUM> { typedef ColsumItems type; };
+template <> struct ItemsOf<MODE_COLSUM_EXT> { typedef ColsumItems type; };
 
 // ---------------------------------------------------------------------------
 // Planning (host): fills the shape-derived fields of `p`.
@@ -280,9 +284,11 @@ inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_pas
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// Scratch layout: [neg_lse | part]; returns the total and the offset of `part`.
-inline size_t workspace_layout(const Problem& p, size_t* part_off) {
+// Scratch layout: [neg_lse | ext | part]; returns the total and the offsets.
+inline size_t workspace_layout(const Problem& p, size_t* part_off, size_t* ext_off = nullptr) {
     size_t off = align_up((size_t)p.B * p.H * (size_t)p.lse_rows * sizeof(float), 256);
+    if (ext_off) *ext_off = off;
+    off += align_up((size_t)p.B * p.H * (size_t)p.lse_rows * 32, 256);
     if (part_off) *part_off = off;
     if (p.nsplit > 1) off += align_up((size_t)p.B * p.H * p.NQ * TILE * 2 * sizeof(float) * p.nsplit, 256);
     return off;

@@ -107,6 +107,16 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
         : "memory");
 }
 
+// One [box_rows x 16-element] slab of a (16, rows, planes) tensor into shared memory.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar,
+                                            int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
 // `bytes` (multiple of 16) from 16-byte-aligned global memory into shared memory.
 __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
     asm volatile(
@@ -162,6 +172,14 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
     return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
+// Same for a K-major tile stored as rows of 32 bytes (16 16-bit elements) with
+// the 32-byte swizzle: 8-row groups are 256 bytes apart; layout type 6.
+__device__ __forceinline__ uint64_t umma_desc_k_sw32(uint32_t smem_addr) {
+    const uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | (1u << 16);
+    const uint32_t hi = 16u | (1u << 14) | (6u << 29);
+    return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane
 // (32 * (warp % 4) + i), registers are the columns.
 __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -206,6 +224,11 @@ __device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
 __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     f32x2 r;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
 __device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {

@@ -26,10 +26,11 @@ def test_library_builds_and_exports_every_declared_symbol():
 
 def test_workspace_query_is_pure_host_arithmetic():
     lib = _cabi.load()
-    # B*H*ceil(S/128)*128 fp32 rows, no key split for the batched headline shape
-    assert lib.fcs_workspace_bytes(8, 16, 2048, 2048, 64, 0) == 8 * 16 * 2048 * 4
-    assert lib.fcs_workspace_bytes(32, 16, 1, 577, 64, 0) >= 32 * 16 * 128 * 4   # one padded query tile
-    assert lib.fcs_workspace_bytes(1, 32, 512, 131072, 128, 1) > 32 * 512 * 4   # key ranges split
+    # per query row (padded to 256): 4 bytes of -(lse) and 32 bytes of its MMA-ready form;
+    # no key split for the batched headline shape
+    assert lib.fcs_workspace_bytes(8, 16, 2048, 2048, 64, 0) == 8 * 16 * 2048 * (4 + 32)
+    assert lib.fcs_workspace_bytes(32, 16, 1, 577, 64, 0) >= 32 * 16 * 256 * 4   # one padded query block
+    assert lib.fcs_workspace_bytes(1, 32, 512, 131072, 128, 1) > 32 * 512 * 36   # key ranges split
     assert lib.fcs_workspace_bytes(1, 1, 1, 1, 96, 0) == 0
     assert lib.fcs_workspace_bytes(0, 1, 1, 1, 64, 0) == 0
 

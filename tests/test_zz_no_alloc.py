@@ -72,9 +72,9 @@ def test_static_scratch_entry_refuses_problems_beyond_its_limit():
         pytest.fail("the gpu-marked tests need a CUDA device")
     from flash_colsum_b200 import _cabi
     lib = _cabi.load()
-    B, H, S, D = 16, 16, 4096, 64          # 16*16*4096 rows * 4 bytes = 4 MiB ... plus nothing: at the limit
+    B, H, S, D = 28, 16, 256, 64           # 28*16*256 rows * 36 bytes: just under the 4 MiB limit
     assert lib.fcs_workspace_bytes(B, H, S, S, D, 0) <= (4 << 20)
-    B = 17
+    B = 29
     assert lib.fcs_workspace_bytes(B, H, S, S, D, 0) > (4 << 20)
     q = torch.empty(1, dtype=torch.float16, device="cuda")     # never dereferenced: the call is refused first
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
