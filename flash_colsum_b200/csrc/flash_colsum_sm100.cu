@@ -33,6 +33,9 @@ namespace fcs {
 
 constexpr int NUM_TBUF = 2;        // accumulator buffers of 256 tensor-memory columns
 constexpr int TMEM_COLS = 512;
+#ifndef FCS_STATS_BLOCK
+#define FCS_STATS_BLOCK 32
+#endif
 constexpr int NUM_LSE = 4;         // per-query-block log-sum-exp vectors in flight (column pass)
 // Consumer warps come in groups of four (a group covers the 128 tensor-memory
 // lanes); every group takes an equal run of the columns of each accumulator.
@@ -45,13 +48,18 @@ constexpr int MMA_WARP = CONSUMER_WARPS + 1;
 constexpr int THREADS = 32 * (CONSUMER_WARPS + 2);
 static_assert(GROUP_COLS == 64, "a group consumes one 64-column block per step");
 
+// Item-end partials of the statistics pass wait in one of these slots until a group
+// combines them; consumer groups are never more than two steps apart, so four
+// slots cannot be overrun.
+constexpr int MERGE_SLOTS = 4;
 constexpr int EXT_K = 16;                        // extra contraction columns that carry -(lse)/c
 constexpr int EXT_ROW_BYTES = EXT_K * 2;
 constexpr int EXT_A_BYTES = TILE * EXT_ROW_BYTES;    // the constant key-side columns
 constexpr int EXT_B_BYTES = BLOCK * EXT_ROW_BYTES;   // the query-side columns of one block
 
-template <int D, bool EXT>
+template <int D, int MODE>
 struct Layout {
+    static constexpr bool EXT = (MODE == MODE_COLSUM_EXT);
     static constexpr int SLABS = D / 64;              // 64-element (128-byte) column slabs
     static constexpr int A_SLAB_BYTES = TILE * 128;
     static constexpr int B_SLAB_BYTES = BLOCK * 128;
@@ -63,13 +71,13 @@ struct Layout {
     static constexpr int B_OFF = 2 * A_BYTES;
     static constexpr int EXTA_OFF = B_OFF + NS * B_STAGE_BYTES;             // 128 rows of the constant
     static constexpr int LSE_OFF = EXTA_OFF + (EXT ? EXT_A_BYTES : 0);      // NUM_LSE slots of 256 floats
-    static constexpr int BAR_OFF = LSE_OFF + (EXT ? 0 : NUM_LSE * BLOCK * 4);
-    // barriers: a_full[2] a_empty[2] b_full[NS] b_empty[NS] t_full[2] t_empty[2] merge[2]
+    static constexpr int BAR_OFF = LSE_OFF + (MODE == MODE_COLSUM ? NUM_LSE * BLOCK * 4 : 0);
+    // barriers: a_full[2] a_empty[2] b_full[NS] b_empty[NS] t_full[2] t_empty[2] merge[MERGE_SLOTS]
     //           l_full[NUM_LSE] l_empty[NUM_LSE]
-    static constexpr int NUM_BARS = 4 + 2 * NS + 2 * NUM_TBUF + 2 + 2 * NUM_LSE;
+    static constexpr int NUM_BARS = 4 + 2 * NS + 2 * NUM_TBUF + MERGE_SLOTS + 2 * NUM_LSE;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;        // tmem address, abort flag
-    static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // float2[2][groups-1][128]
-    static constexpr int TOTAL = MERGE_OFF + 2 * (CONSUMER_GROUPS - 1) * TILE * 8;
+    static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // float2[MERGE_SLOTS][groups][128]
+    static constexpr int TOTAL = MERGE_OFF + (MODE == MODE_STATS ? MERGE_SLOTS * CONSUMER_GROUPS * TILE * 8 : 0);
     static constexpr int DYN_BYTES = TOTAL + 1024;    // slack to align the base to 1024
     static_assert(DYN_BYTES <= 227 * 1024, "shared memory budget");
 };
@@ -78,12 +86,22 @@ struct Layout {
 // `nl` are relative to the group's first column.
 template <bool MASKED>
 __device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, float& m, float& l) {
+#if FCS_STATS_BLOCK == 64
     uint32_t ra[32], rb[32];
     tmem_ld_x32(taddr, ra);
     tmem_ld_x32(taddr + 32, rb);
     tmem_ld_wait(ra);
     tmem_ld_wait(rb);
     stats_block64<MASKED>(ra, rb, lim, c, m, l);
+#else
+    uint32_t r[32];
+    tmem_ld_x32(taddr, r);
+    tmem_ld_wait(r);
+    stats_block32<MASKED>(r, lim, c, m, l);
+    tmem_ld_x32(taddr + 32, r);
+    tmem_ld_wait(r);
+    stats_block32<MASKED>(r, lim - 32, c, m, l);
+#endif
 }
 template <bool MASKED>
 __device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, int thr, int end, float c,
@@ -118,7 +136,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ CUtensorMap tm_ext, const Problem p) {
     constexpr bool EXT = (MODE == MODE_COLSUM_EXT);
-    using L = Layout<D, EXT>;
+    using L = Layout<D, MODE>;
     using Items = typename ItemsOf<MODE>::type;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -135,8 +153,8 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     auto t_full = [&](int i) { return bars + 8u * (4 + 2 * L::NS + i); };
     auto t_empty = [&](int i) { return bars + 8u * (4 + 2 * L::NS + NUM_TBUF + i); };
     auto merge_bar = [&](int i) { return bars + 8u * (4 + 2 * L::NS + 2 * NUM_TBUF + i); };
-    auto l_full = [&](int i) { return bars + 8u * (6 + 2 * L::NS + 2 * NUM_TBUF + i); };
-    auto l_empty = [&](int i) { return bars + 8u * (6 + 2 * L::NS + 2 * NUM_TBUF + NUM_LSE + i); };
+    auto l_full = [&](int i) { return bars + 8u * (4 + MERGE_SLOTS + 2 * L::NS + 2 * NUM_TBUF + i); };
+    auto l_empty = [&](int i) { return bars + 8u * (4 + MERGE_SLOTS + 2 * L::NS + 2 * NUM_TBUF + NUM_LSE + i); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFF + 4);
     float2* merge_buf = reinterpret_cast<float2*>(smem + L::MERGE_OFF);
@@ -148,7 +166,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), 1); }
         for (int i = 0; i < L::NS; ++i) { mbar_init(b_full(i), 1); mbar_init(b_empty(i), 1); }
         for (int i = 0; i < NUM_TBUF; ++i) { mbar_init(t_full(i), 1); mbar_init(t_empty(i), CONSUMER_THREADS); }
-        for (int i = 0; i < 2; ++i) mbar_init(merge_bar(i), 128 * (CONSUMER_GROUPS - 1));
+        for (int i = 0; i < MERGE_SLOTS; ++i) mbar_init(merge_bar(i), CONSUMER_THREADS);
         for (int i = 0; i < NUM_LSE; ++i) { mbar_init(l_full(i), 1); mbar_init(l_empty(i), CONSUMER_THREADS); }
         *abort_flag = 0;
         mbar_fence_init();
@@ -296,6 +314,44 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         float m_run = -INFINITY, l_run = 0.f;      // statistics pass state
         float acc[4] = {0.f, 0.f, 0.f, 0.f};       // column pass state
         int item_cnt = 0, n = 0;
+        // statistics pass: the item whose partials this group still has to combine
+        bool pending = false;
+        int pend_cnt = 0, pend_b = 0, pend_h = 0, pend_qt = 0, pend_sp = 0;
+        auto finish_item = [&]() -> bool {
+            const int slot = pend_cnt & (MERGE_SLOTS - 1);
+            bool good = mbar_wait(merge_bar(slot), (pend_cnt / MERGE_SLOTS) & 1, abort_flag, p.status,
+                                  FCS_STATUS_WAIT_CONSUMER);
+            good = __all_sync(0xffffffffu, good);
+            pending = false;
+            if (!good) return false;
+            const float2* mb = merge_buf + slot * CONSUMER_GROUPS * TILE;
+            float mm = -INFINITY;
+#pragma unroll
+            for (int g = 0; g < CONSUMER_GROUPS; ++g) mm = fmaxf(mm, mb[g * TILE + row].x);
+            const float ms = (mm == -INFINITY) ? 0.f : mm;
+            float ll = 0.f;
+#pragma unroll
+            for (int g = 0; g < CONSUMER_GROUPS; ++g) {
+                const float2 o = mb[g * TILE + row];
+                ll += o.y * exp2f(o.x - ms);
+            }
+            const long long bh = (long long)pend_b * p.H + pend_h;
+            const int q_abs = pend_qt * TILE + row;
+            if (p.nsplit == 1) {
+                const float nlv = (q_abs < p.Sq) ? -(mm + log2f(ll) + p.log2_norm) : -INFINITY;
+                p.neg_lse[bh * p.lse_rows + q_abs] = nlv;
+                uint4 e0, e1;
+                make_ext_row(nlv, p.inv_c, p.ext_bf16 != 0, e0, e1);
+                uint4* er = reinterpret_cast<uint4*>(p.ext) + (bh * p.lse_rows + q_abs) * 2;
+                er[0] = e0;
+                er[1] = e1;
+            } else {
+                const long long rows = (long long)p.NQ * TILE;
+                reinterpret_cast<float2*>(p.part)[((long long)pend_sp * p.B * p.H + bh) * rows + q_abs] =
+                    make_float2(mm, ll);
+            }
+            return true;
+        };
         for (; ok && !it.done; it.next(p), ++item_cnt) {
             // steps f_lo <= st < f_hi need no masks: their per-step work is kept minimal
             int f_lo, f_hi;
@@ -348,45 +404,22 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 }
                 tc_fence_before();
                 mbar_arrive(t_empty(buf));
+                if constexpr (MODE == MODE_STATS) {
+                    if (pending) { ok = finish_item(); if (!ok) break; }
+                }
             }
             if (!ok) break;
             if constexpr (MODE == MODE_STATS) {
-                // combine the consumer groups' partial (max, sum) in group 0 and store
-                const int slot = item_cnt & 1;
-                float2* mb = merge_buf + slot * (CONSUMER_GROUPS - 1) * TILE;
-                if (wg != 0) {
-                    mb[(wg - 1) * TILE + row] = make_float2(m_run, l_run);
-                    mbar_arrive(merge_bar(slot));
-                } else {
-                    ok = mbar_wait(merge_bar(slot), (item_cnt >> 1) & 1, abort_flag, p.status,
-                                   FCS_STATUS_WAIT_CONSUMER);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    float mm = m_run;
-#pragma unroll
-                    for (int g = 0; g < CONSUMER_GROUPS - 1; ++g) mm = fmaxf(mm, mb[g * TILE + row].x);
-                    const float ms = (mm == -INFINITY) ? 0.f : mm;
-                    float ll = l_run * exp2f(m_run - ms);
-#pragma unroll
-                    for (int g = 0; g < CONSUMER_GROUPS - 1; ++g) {
-                        const float2 o = mb[g * TILE + row];
-                        ll += o.y * exp2f(o.x - ms);
-                    }
-                    const long long bh = (long long)it.b * p.H + it.h;
-                    const int q_abs = it.qt * TILE + row;
-                    if (p.nsplit == 1) {
-                        const float nlv = (q_abs < p.Sq) ? -(mm + log2f(ll) + p.log2_norm) : -INFINITY;
-                        p.neg_lse[bh * p.lse_rows + q_abs] = nlv;
-                        uint4 e0, e1;
-                        make_ext_row(nlv, p.inv_c, p.ext_bf16 != 0, e0, e1);
-                        uint4* er = reinterpret_cast<uint4*>(p.ext) + (bh * p.lse_rows + q_abs) * 2;
-                        er[0] = e0;
-                        er[1] = e1;
-                    } else {
-                        const long long rows = (long long)p.NQ * TILE;
-                        reinterpret_cast<float2*>(p.part)[((long long)it.sp * p.B * p.H + bh) * rows + q_abs] =
-                            make_float2(mm, ll);
-                    }
+                // post this group's partial (max, sum); one group, a different one every
+                // item, combines the four partials after its next step, when the others
+                // have long since posted -- nobody stands waiting at the end of an item
+                if (pending) { ok = finish_item(); if (!ok) break; }
+                const int slot = item_cnt & (MERGE_SLOTS - 1);
+                merge_buf[(slot * CONSUMER_GROUPS + wg) * TILE + row] = make_float2(m_run, l_run);
+                mbar_arrive(merge_bar(slot));
+                if ((item_cnt % CONSUMER_GROUPS) == wg) {
+                    pending = true;
+                    pend_cnt = item_cnt; pend_b = it.b; pend_h = it.h; pend_qt = it.qt; pend_sp = it.sp;
                 }
                 m_run = -INFINITY; l_run = 0.f;
             } else {
@@ -399,6 +432,9 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
                 }
             }
+        }
+        if constexpr (MODE == MODE_STATS) {
+            if (ok && pending) finish_item();
         }
     }
 
@@ -544,7 +580,7 @@ static int make_ext_tensor_map(CUtensorMap* m, const void* base, int dtype, long
 template <int D, int MODE>
 static cudaError_t launch_stream(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& text,
                                  const Problem& p, int grid, cudaStream_t stream) {
-    using LayoutT = Layout<D, MODE == MODE_COLSUM_EXT>;
+    using LayoutT = Layout<D, MODE>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
