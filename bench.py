@@ -200,8 +200,9 @@ def run_reference_arm(args):
 def kernel_only(args, fc, _cabi, dev, flush_buf, peaks):
     """Device passes of one workload, per-pass durations; one JSON line."""
     w = WORKLOADS[args.workload]
-    if args.batch > 0:
-        w = Workload(w.name, args.batch, w.H, w.Sq, w.Sk, w.D, w.dtype, w.is_causal, w.cls_len,
+    if args.batch > 0 or args.keys > 0:
+        w = Workload(w.name, args.batch or w.B, w.H, w.Sq if w.is_causal or not args.keys else args.keys,
+                     args.keys or w.Sk, w.D, w.dtype, w.is_causal, w.cls_len,
                      w.key_outliers, w.key_is_query, w.seed)
     g = torch.Generator(device=dev).manual_seed(w.seed)
     q = torch.randn(w.B, w.H, w.Sq, w.D, generator=g, device=dev).to(w.torch_dtype)
@@ -217,7 +218,8 @@ def kernel_only(args, fc, _cabi, dev, flush_buf, peaks):
     torch.cuda.synchronize()
     rows = []
     for _ in range(args.steps):
-        flush_buf.zero_()
+        if not args.no_l2_flush:
+            flush_buf.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         call()
@@ -254,6 +256,9 @@ def main():
                     help="time only the device passes of --workload (used for ncu captures)")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (kernel-only mode)")
+    ap.add_argument("--keys", type=int, default=0, help="override the key length (kernel-only mode)")
+    ap.add_argument("--no-l2-flush", action="store_true",
+                    help="kernel-only mode: do not write the 256 MiB buffer between calls (inputs stay in L2)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
