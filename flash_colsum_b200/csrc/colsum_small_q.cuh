@@ -69,8 +69,10 @@ __device__ __forceinline__ void block_reduce(float (&v)[SMALLQ_MAX_ROWS], int R,
     __syncthreads();
 }
 
-template <int D, bool BF16>
-__global__ void __launch_bounds__(SMALLQ_THREADS)
+// RMAX: compile-time bound on the query rows (1, 2 or 4); fewer rows need fewer
+// registers, so that four CTAs fit on an SM and a 512-CTA grid runs as one wave.
+template <int D, bool BF16, int RMAX>
+__global__ void __launch_bounds__(SMALLQ_THREADS, 4)
 colsum_small_q_kernel(const SmallQParams p) {
     extern __shared__ float smallq_smem[];
     float* qs = smallq_smem;                       // [R][D], scaled by c
@@ -97,9 +99,9 @@ colsum_small_q_kernel(const SmallQParams p) {
     constexpr int UNROLL = 4;             // independent loads in flight per lane
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int piece = lane % LPR, sub = lane / LPR;
-    float qreg[SMALLQ_MAX_ROWS][8];
+    float qreg[RMAX][8];
 #pragma unroll
-    for (int r = 0; r < SMALLQ_MAX_ROWS; ++r)
+    for (int r = 0; r < RMAX; ++r)
 #pragma unroll
         for (int e = 0; e < 8; ++e) qreg[r][e] = (r < p.R) ? qs[r * D + piece * 8 + e] : 0.f;
     float vmax[SMALLQ_MAX_ROWS];
@@ -120,7 +122,7 @@ colsum_small_q_kernel(const SmallQParams p) {
             const float2 f0 = unpack16x2<BF16>(raw[u].x), f1 = unpack16x2<BF16>(raw[u].y);
             const float2 f2 = unpack16x2<BF16>(raw[u].z), f3 = unpack16x2<BF16>(raw[u].w);
 #pragma unroll
-            for (int r = 0; r < SMALLQ_MAX_ROWS; ++r) {
+            for (int r = 0; r < RMAX; ++r) {
                 if (r < p.R) {      // uniform across the CTA
                     float d = f0.x * qreg[r][0] + f0.y * qreg[r][1] + f1.x * qreg[r][2] + f1.y * qreg[r][3] +
                               f2.x * qreg[r][4] + f2.y * qreg[r][5] + f3.x * qreg[r][6] + f3.y * qreg[r][7];

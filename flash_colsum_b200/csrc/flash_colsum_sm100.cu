@@ -607,12 +607,12 @@ static int check_operand(const char* name, const void* ptr, int64_t sb, int64_t 
 }
 
 // Few query rows: the matrix-vector kernel (memset of the output, then one launch).
-template <int D, bool BF16>
-static cudaError_t launch_small_q_t(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream) {
+template <int D, bool BF16, int RMAX>
+static cudaError_t launch_small_q_r(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream) {
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kern = colsum_small_q_kernel<D, BF16>;
+    auto kern = colsum_small_q_kernel<D, BF16, RMAX>;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMALLQ_MAX_SMEM);
         if (e != cudaSuccess) return e;
@@ -620,6 +620,13 @@ static cudaError_t launch_small_q_t(const SmallQParams& sp, int grid, size_t sme
     }
     kern<<<grid, SMALLQ_THREADS, smem, stream>>>(sp);
     return cudaGetLastError();
+}
+
+template <int D, bool BF16>
+static cudaError_t launch_small_q_t(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream) {
+    if (sp.R == 1) return launch_small_q_r<D, BF16, 1>(sp, grid, smem, stream);
+    if (sp.R == 2) return launch_small_q_r<D, BF16, 2>(sp, grid, smem, stream);
+    return launch_small_q_r<D, BF16, 4>(sp, grid, smem, stream);
 }
 
 static int launch_small_q(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int R, int Sk,
