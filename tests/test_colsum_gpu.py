@@ -208,6 +208,42 @@ def test_headline_workloads_full_size(fc, name, chunk):
         torch.backends.cuda.matmul.allow_tf32 = prev
 
 
+REFERENCE_TEST_SHAPES = [
+    # the shapes of the reference's own GPU tests that are not already above at full size
+    Workload("ref_non_batched", 1, 16, 8192, 8192, 64, "fp16", seed=0),                 # test_core.py:39-53
+    Workload("ref_non_batched_cls2", 1, 16, 4096, 4096, 64, "fp16", cls_len=2, seed=0),  # test_core.py:76-91
+    Workload("ref_causal", 1, 16, 128, 16384, 128, "fp16", is_causal=True, seed=0),      # test_core.py:95-109
+]
+
+
+@pytest.mark.parametrize("w", REFERENCE_TEST_SHAPES, ids=lambda w: w.name)
+def test_reference_test_shapes_full_size(fc, w):
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        q, k = make_inputs(w)
+        qc, kc = q.cuda(), k.cuda()
+        got = run_gpu(fc, w, qc, kc)
+        want = _torch_fp32_reference(qc, kc, w.is_causal, w.cls_len, 2)
+        assert_parity(got, want, w.name)
+        # what the reference's test asserts, on the dtype its kernels return
+        half = fc.flash_colsum(qc, kc, is_causal=w.is_causal, cls_len=w.cls_len, out_dtype=torch.float16)
+        assert torch.allclose(torch.from_numpy(want).half(), half.cpu(), atol=1e-3, rtol=1e-3)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def test_large_scores_and_peaked_rows(fc):
+    """Inputs three times the usual magnitude: scores of several tens, nearly one-hot rows."""
+    for w in (Workload("big_noncausal", 2, 4, 640, 640, 64, "fp16", seed=61),
+              Workload("big_causal", 1, 4, 256, 2048, 128, "bf16", is_causal=True, seed=62)):
+        q, k = make_inputs(w)
+        q, k = (q.float() * 3).to(w.torch_dtype), (k.float() * 3).to(w.torch_dtype)
+        got = run_gpu(fc, w, q, k)
+        want = c_oracle.colsum_c(q, k, is_causal=w.is_causal)
+        assert_parity(got, want, w.name)
+
+
 def test_c5_long_context_properties_and_sampled_parity(fc):
     """131072 keys, 512 suffix queries, outlier keys, bf16: rows sum to one, the
     last key is seen by the last query only, and a 4-head slice matches the
