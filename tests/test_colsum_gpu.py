@@ -147,6 +147,29 @@ def test_repeated_calls_reuse_scratch_safely(fc):
     assert fc.device_status() == 0
 
 
+def test_calls_can_be_captured_in_a_cuda_graph(fc):
+    """The library neither synchronises nor allocates, so a call replays from a graph."""
+    w = Workload("graph", 1, 8, 128, 4096, 128, "fp16", is_causal=True, seed=81)
+    q, k = (t.cuda() for t in make_inputs(w))
+    fc.flash_colsum(q, k, is_causal=True)            # first call outside capture (one-time set-up)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fc.flash_colsum(q, k, is_causal=True)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = fc.flash_colsum(q, k, is_causal=True)
+    want = c_oracle.colsum_c(q.cpu(), k.cpu(), is_causal=True)
+    for _ in range(3):
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert_parity(out.cpu().numpy(), want, "graph replay")
+    assert fc.device_status() == 0
+
+
 def test_error_handling(fc):
     """The reference's error cases (tests/test_core.py:112-134), same messages."""
     dev, dt = torch.device("cuda"), torch.float16
