@@ -25,84 +25,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return r;
 }
 
-// Online (max, sum) update of one query row with 64 more scores (two 32-column
-// register blocks).  `last_valid`: columns 0..last_valid are visible (>= 63: all).
-template <bool MASKED>
-__device__ __forceinline__ void stats_block64(const uint32_t (&ra)[32], const uint32_t (&rb)[32],
-                                              int last_valid, float c, float& m, float& l) {
-    float s[64];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        s[j] = __uint_as_float(ra[j]);
-        s[32 + j] = __uint_as_float(rb[j]);
-    }
-    if (MASKED) {
-#pragma unroll
-        for (int j = 0; j < 64; ++j) s[j] = (j <= last_valid) ? s[j] : -INFINITY;
-    }
-    float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
-    float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
-#pragma unroll
-    for (int j = 12; j < 60; j += 8) {
-        m0 = max3(m0, s[j], s[j + 1]);
-        m1 = max3(m1, s[j + 2], s[j + 3]);
-        m2 = max3(m2, s[j + 4], s[j + 5]);
-        m3 = max3(m3, s[j + 6], s[j + 7]);
-    }
-    m0 = max3(m0, s[60], s[61]);
-    m1 = max3(m1, s[62], s[63]);
-    const float cm = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-    float m_safe;
-    if (MASKED) {   // a row may see nothing of this block (or nothing yet): keep -inf out of the arithmetic
-        const float scaled = (cm == -INFINITY) ? -INFINITY : cm * c;
-        const float m_new = fmaxf(m, scaled);
-        m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-        l *= ex2_approx(m - m_safe);
-        m = m_new;
-    } else {        // all 64 scores are finite
-        m_safe = fmaxf(m, cm * c);
-        l *= ex2_approx(m - m_safe);
-        m = m_safe;
-    }
-    if constexpr (!MASKED) {
-        // exp2(c*s - m) two at a time; a fixed share of the pairs avoids the special-function unit
-        const f32x2 c2 = pack2(c, c), nm2 = pack2(-m_safe, -m_safe);
-        f32x2 s0 = pack2(0.f, 0.f), s1 = s0;
-#pragma unroll
-        for (int pr = 0; pr < 32; ++pr) {
-            const f32x2 t = fma2(pack2(s[2 * pr], s[2 * pr + 1]), c2, nm2);
-            f32x2 e;
-            if (pair_uses_polynomial(pr & 15)) {
-                e = ex2_poly2(t);
-            } else {
-                float t0, t1;
-                unpack2(t, t0, t1);
-                e = pack2(ex2_approx(t0), ex2_approx(t1));
-            }
-            if (pr & 1) s1 = add2(s1, e); else s0 = add2(s0, e);
-        }
-        float x0, x1;
-        unpack2(add2(s0, s1), x0, x1);
-        l += x0 + x1;
-    } else {
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-    for (int j = 0; j < 64; j += 4) {
-        float t0 = fmaf(s[j], c, -m_safe), t1 = fmaf(s[j + 1], c, -m_safe);
-        float t2 = fmaf(s[j + 2], c, -m_safe), t3 = fmaf(s[j + 3], c, -m_safe);
-        if (MASKED) {   // c may be 0 and s -inf: select after the multiply
-            t0 = (j <= last_valid) ? t0 : -INFINITY;
-            t1 = (j + 1 <= last_valid) ? t1 : -INFINITY;
-            t2 = (j + 2 <= last_valid) ? t2 : -INFINITY;
-            t3 = (j + 3 <= last_valid) ? t3 : -INFINITY;
-        }
-        a0 += ex2_approx(t0); a1 += ex2_approx(t1);
-        a2 += ex2_approx(t2); a3 += ex2_approx(t3);
-    }
-    l += (a0 + a1) + (a2 + a3);
-    }
-}
-
 // Online (max, sum) update of one query row with 32 more scores.
 // `last_valid`: columns 0..last_valid are visible (>= 31: all).
 template <bool MASKED>

@@ -12,11 +12,15 @@
 //                    down the query axis stays inside one thread as well.  It
 //                    adds exp2(c*s - lse) into a per-key fp32 accumulator and
 //                    flushes that with one atomic add per (key tile, CTA range).
+//                    -lse/c reaches the accumulator through 16 extra contraction
+//                    columns (MODE_COLSUM_EXT); for tiny scales it is staged
+//                    through shared memory instead (MODE_COLSUM).
 //
 // Both operands are row tiles with the head dimension contiguous, so the same
 // shared-memory layout serves as A (128 resident rows) or B (256 streamed rows)
 // of the MMA; one step is a 128 x 256 x D MMA into one of two accumulator
-// buffers of 256 tensor-memory columns.
+// buffers of 256 tensor-memory columns.  Calls with at most four query rows
+// take the matrix-vector kernel of colsum_small_q.cuh instead.
 #include "sm100_ptx.cuh"
 #include "schedule.h"
 #include "colsum_small_q.cuh"
@@ -33,9 +37,6 @@ namespace fcs {
 
 constexpr int NUM_TBUF = 2;        // accumulator buffers of 256 tensor-memory columns
 constexpr int TMEM_COLS = 512;
-#ifndef FCS_STATS_BLOCK
-#define FCS_STATS_BLOCK 32
-#endif
 constexpr int NUM_LSE = 4;         // per-query-block log-sum-exp vectors in flight (column pass)
 // Consumer warps come in groups of four (a group covers the 128 tensor-memory
 // lanes); every group takes an equal run of the columns of each accumulator.
@@ -86,14 +87,6 @@ struct Layout {
 // `nl` are relative to the group's first column.
 template <bool MASKED>
 __device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, float& m, float& l) {
-#if FCS_STATS_BLOCK == 64
-    uint32_t ra[32], rb[32];
-    tmem_ld_x32(taddr, ra);
-    tmem_ld_x32(taddr + 32, rb);
-    tmem_ld_wait(ra);
-    tmem_ld_wait(rb);
-    stats_block64<MASKED>(ra, rb, lim, c, m, l);
-#else
     uint32_t r[32];
     tmem_ld_x32(taddr, r);
     tmem_ld_wait(r);
@@ -101,7 +94,6 @@ __device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, flo
     tmem_ld_x32(taddr + 32, r);
     tmem_ld_wait(r);
     stats_block32<MASKED>(r, lim - 32, c, m, l);
-#endif
 }
 template <bool MASKED>
 __device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, int thr, int end, float c,
