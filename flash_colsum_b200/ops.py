@@ -208,4 +208,61 @@ def flash_colsum(
     return out
 
 
-__all__ = ["flash_colsum", "device_status"]
+_copy_streams: Dict[int, torch.cuda.Stream] = {}
+
+
+def flash_colsum_host(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    scale: Optional[float] = None,
+    is_causal: bool = False,
+    cls_len: Optional[int] = None,
+    *,
+    device: Optional[torch.device] = None,
+    batch_chunk: int = 1,
+) -> torch.Tensor:
+    """``flash_colsum`` for inputs that live in host memory; returns a host tensor.
+
+    Same arguments as :func:`flash_colsum`, but ``query`` and ``key`` are CPU
+    tensors (pinned memory makes the copies asynchronous).  A batched call is cut
+    along the batch into chunks of ``batch_chunk`` entries whose host-to-device
+    copies run on a second stream while the previous chunk is being computed, so
+    the call costs about the copy time of the inputs plus one chunk of compute.
+    Causal and single-sample calls are copied in one piece.
+    """
+    if query.ndim != 4 or key.ndim != 4:
+        raise ValueError(f"Expected 4D tensors, got query.ndim={query.ndim}, key.ndim={key.ndim}")
+    if query.device.type != "cpu" or key.device.type != "cpu":
+        raise ValueError("flash_colsum_host takes host tensors; use flash_colsum for CUDA tensors")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    B = query.shape[0]
+    if is_causal or B == 1 or key.shape[0] != B:
+        out = flash_colsum(query.to(dev, non_blocking=True), key.to(dev, non_blocking=True), scale,
+                           is_causal, cls_len)
+        return out.cpu()
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(dev):
+        copy_stream = _copy_streams.get(idx)
+        if copy_stream is None:
+            copy_stream = _copy_streams[idx] = torch.cuda.Stream(device=dev)
+        main = torch.cuda.current_stream(dev)
+        out = torch.empty((B, key.shape[2]), dtype=torch.float32, device=dev)
+        copy_stream.wait_stream(main)
+        staged = []
+        for b0 in range(0, B, batch_chunk):
+            with torch.cuda.stream(copy_stream):
+                qd = query[b0:b0 + batch_chunk].to(dev, non_blocking=True)
+                kd = key[b0:b0 + batch_chunk].to(dev, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(copy_stream)
+            staged.append((b0, qd, kd, ready))
+        for b0, qd, kd, ready in staged:
+            main.wait_event(ready)
+            # a one-entry chunk takes the single-sample entry point, a longer one the batched one
+            out[b0:b0 + qd.shape[0]] = flash_colsum(qd, kd, scale, False, cls_len)
+            qd.record_stream(main)
+            kd.record_stream(main)
+        return out.cpu()
+
+
+__all__ = ["flash_colsum", "flash_colsum_host", "device_status"]

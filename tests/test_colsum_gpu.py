@@ -147,6 +147,24 @@ def test_repeated_calls_reuse_scratch_safely(fc):
     assert fc.device_status() == 0
 
 
+def test_host_entry_matches_device_entry(fc):
+    w = Workload("host", 5, 4, 300, 300, 64, "fp16", seed=91)
+    q, k = make_inputs(w)
+    want = fc.flash_colsum(q.cuda(), k.cuda()).cpu()
+    for qh, kh in ((q, k), (q.pin_memory(), k.pin_memory())):
+        for chunk in (1, 2, 8):
+            got = fc.flash_colsum_host(qh, kh, batch_chunk=chunk)
+            assert got.device.type == "cpu"
+            torch.testing.assert_close(got, want, rtol=2e-5, atol=1e-9)   # summation order differs with the chunking
+    wc = Workload("host_causal", 1, 4, 64, 900, 128, "bf16", is_causal=True, seed=92)
+    q, k = make_inputs(wc)
+    torch.testing.assert_close(fc.flash_colsum_host(q, k, is_causal=True),
+                               fc.flash_colsum(q.cuda(), k.cuda(), is_causal=True).cpu(), rtol=2e-5, atol=1e-9)
+    with pytest.raises(ValueError, match="host tensors"):
+        fc.flash_colsum_host(q.cuda(), k.cuda())
+    assert fc.device_status() == 0
+
+
 def test_calls_can_be_captured_in_a_cuda_graph(fc):
     """The library neither synchronises nor allocates, so a call replays from a graph."""
     w = Workload("graph", 1, 8, 128, 4096, 128, "fp16", is_causal=True, seed=81)
