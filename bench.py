@@ -139,6 +139,7 @@ def time_steps(fn, steps, warmup, flush_buf, barrier=None):
 def cpu_port_tflops(w: Workload, budget_s: float, batch_entries: int):
     """The CPU restatement of the reference on a bounded sample of `w`."""
     from oracle.naive_colsum import naive_colsum_torch
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     sample = Workload(w.name + "_sample", min(batch_entries, w.B), w.H, w.Sq, w.Sk, w.D, w.dtype,
                       w.is_causal, w.cls_len, w.key_outliers, w.key_is_query, w.seed)
     q, k = make_inputs(sample)
@@ -166,6 +167,8 @@ def run_reference_arm(args):
         return
     w = WORKLOADS["c2"]
     from oracle.naive_colsum import naive_colsum_torch
+    # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1 to its ranks)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     sample = Workload("c2_sample", 1, w.H, w.Sq, w.Sk, w.D, w.dtype, seed=w.seed)
     q, k = make_inputs(sample)
     q, k = q.float(), k.float()
