@@ -14,6 +14,7 @@ EXPORTED_SYMBOLS = (
     "fcs_colsum_batched", "fcs_colsum_non_batched", "fcs_colsum_causal",
     "fcs_set_profiling", "fcs_last_pass_ms", "fcs_plan_info",
     "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate",
+    "fcs_set_single_pass", "fcs_single_pass_info",
 )
 
 FCS_OK = 0
@@ -75,6 +76,10 @@ def load() -> ctypes.CDLL:
         [_f, _i, _i, _p, _p]
     lib.fcs_set_profiling.restype = _i
     lib.fcs_set_profiling.argtypes = [_i]
+    lib.fcs_set_single_pass.restype = _i
+    lib.fcs_set_single_pass.argtypes = [_i]
+    lib.fcs_single_pass_info.restype = _i
+    lib.fcs_single_pass_info.argtypes = [_i, ctypes.POINTER(_i), ctypes.POINTER(_i)]
     lib.fcs_last_pass_ms.restype = _i
     lib.fcs_last_pass_ms.argtypes = [_p, _p, _p]
     lib.fcs_plan_info.restype = _i
@@ -89,6 +94,23 @@ def last_error() -> str:
 
 def set_profiling(enabled: bool) -> None:
     load().fcs_set_profiling(int(bool(enabled)))
+
+
+def single_pass_info(sk: int):
+    """(CTAs per cluster, clusters resident at once) of the single-pass kernel for `sk` keys."""
+    cl, n = _i(0), _i(0)
+    if load().fcs_single_pass_info(int(sk), ctypes.byref(cl), ctypes.byref(n)) != FCS_OK:
+        raise ValueError(f"the single-pass kernel does not cover {sk} keys")
+    return cl.value, n.value
+
+
+SINGLE_PASS_AUTO, SINGLE_PASS_NEVER, SINGLE_PASS_ALWAYS = 0, 1, 2
+
+
+def set_single_pass(mode: int) -> None:
+    """Kernel choice for short non-causal calls (`fcs_set_single_pass`)."""
+    if load().fcs_set_single_pass(int(mode)) != FCS_OK:
+        raise ValueError(f"single-pass mode must be 0, 1 or 2, got {mode}")
 
 
 def last_pass_ms():

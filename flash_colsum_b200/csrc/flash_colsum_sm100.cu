@@ -33,6 +33,8 @@
 
 #include "../../include/flash_colsum_b200.h"
 
+#include "colsum_single_pass.cuh"
+
 namespace fcs {
 
 constexpr int NUM_TBUF = 2;        // accumulator buffers of 256 tensor-memory columns
@@ -647,6 +649,99 @@ static int launch_small_q(const void* q, const void* k, float* out, int64_t out_
     return FCS_OK;
 }
 
+// Short key axes (non-causal, head dimension 64, S_k <= 2048): the single-pass
+// cluster kernel.  g_single_pass: 0 = when the shape fills enough of the device,
+// 1 = never, 2 = whenever the shape allows.
+static int g_single_pass = 1;
+
+static int single_pass_cluster_size(int Sk) {
+    const int slices = (Sk + 255) / 256;
+    int cl = 1;
+    while (cl < slices) cl *= 2;
+    return cl;
+}
+
+static bool single_pass_applies(int B, int H, int Sk, int D, int causal) {
+    if (g_single_pass == 1 || causal || D != 64 || Sk > 256 * sp::MAX_CL) return false;
+    if (g_single_pass == 2) return true;
+    return (long long)B * H * single_pass_cluster_size(Sk) >= 32;
+}
+
+// Clusters of `cl` CTAs that can be resident at once (0 if the query fails).
+static int single_pass_max_clusters(int cl) {
+    static int cached[64][4] = {{0}};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    int idx = 0;
+    while ((1 << idx) < cl) ++idx;
+    if (cached[dev][idx] == 0) {
+        if (cudaFuncSetAttribute(colsum_single_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 sp::DYN_BYTES) != cudaSuccess)
+            return 0;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)(cl * 64));
+        cfg.blockDim = dim3(sp::THREADS);
+        cfg.dynamicSmemBytes = sp::DYN_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = (unsigned)cl;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, colsum_single_pass_kernel, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            return 0;
+        }
+        cached[dev][idx] = n;
+    }
+    return cached[dev][idx];
+}
+
+static int launch_single_pass(const CUtensorMap& tq, const CUtensorMap& tk, float* out, int64_t out_ld, int B,
+                              int H, int Sq, int Sk, float scale, int h_norm, int dtype, bool clear_out,
+                              int max_clusters, int* status, cudaStream_t stream) {
+    cudaError_t e = cudaSuccess;
+    if (clear_out)
+        e = cudaMemset2DAsync(out, (size_t)out_ld * sizeof(float), 0, (size_t)Sk * sizeof(float), (size_t)B, stream);
+    if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "clearing the output failed: %s", cudaGetErrorString(e));
+    SinglePassParams sp_;
+    memset(&sp_, 0, sizeof(sp_));
+    sp_.B = B; sp_.H = H; sp_.Sq = Sq; sp_.Sk = Sk;
+    sp_.NQ = (Sq + TILE - 1) / TILE;
+    sp_.CL = single_pass_cluster_size(Sk);
+    sp_.units = B * H;
+    sp_.clusters = sp_.units < max_clusters ? sp_.units : max_clusters;
+    sp_.c = fabsf(scale) * 1.4426950408889634f;
+    sp_.out_scale = 1.0f / ((float)h_norm * (float)Sq * 1024.0f);
+    sp_.out = out;
+    sp_.out_ld = out_ld;
+    sp_.status = status;
+    const uint32_t fmt = dtype == FCS_DTYPE_BF16 ? 1u : 0u;
+    sp_.idesc_scores = (1u << 4) | (fmt << 7) | (fmt << 10) | ((scale < 0.f ? 1u : 0u) << 13) |
+                       ((uint32_t)(BLOCK >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
+    // fp16 x fp16 -> fp32, A stored with the M index contiguous, B K-major, M = 128, N = 16
+    sp_.idesc_colsum = (1u << 4) | (1u << 15) | ((uint32_t)(sp::W_N >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(sp_.clusters * sp_.CL));
+    cfg.blockDim = dim3(sp::THREADS);
+    cfg.dynamicSmemBytes = sp::DYN_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = (unsigned)sp_.CL;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, colsum_single_pass_kernel, tq, tk, sp_);
+    if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "single-pass kernel launch failed: %s", cudaGetErrorString(e));
+    return FCS_OK;
+}
+
 // The one implementation behind the three entry points.
 static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int Sq_full,
                        int Sk, int D, int dtype, int64_t qsb, int64_t qsh, int64_t qss, int64_t ksb,
@@ -723,6 +818,21 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if ((rc = make_tensor_map(&tq_b, q, dtype, B, H, Sq, D, qsb, qsh, qss, BLOCK)) != FCS_OK) return rc;
     if ((rc = make_tensor_map(&tk_a, k, dtype, B, H, Sk, D, ksb, ksh, kss, TILE)) != FCS_OK) return rc;
     if ((rc = make_tensor_map(&tk_b, k, dtype, B, H, Sk, D, ksb, ksh, kss, BLOCK)) != FCS_OK) return rc;
+    if (single_pass_applies(B, H, Sk, D, causal)) {
+        const int max_clusters = single_pass_max_clusters(single_pass_cluster_size(Sk));
+        if (max_clusters > 0) {
+            // reported as a call whose statistics and merge passes take no time
+            PassTimers* tms = g_profiling ? timers_for_current_device() : nullptr;
+            if (tms) {
+                tms->recorded = false;
+                for (int i = 0; i < 3; ++i) cudaEventRecord(tms->ev[i], stream);
+            }
+            rc = launch_single_pass(tq_a, tk_b, out, out_ld, B, H, Sq, Sk, scale, h_norm, dtype, clear_out,
+                                    max_clusters, status, stream);
+            if (rc == FCS_OK && tms) { cudaEventRecord(tms->ev[3], stream); tms->recorded = true; }
+            return rc;
+        }
+    }
     CUtensorMap text = tq_b;   // placeholder when the extension is not used
     if (use_ext && (rc = make_ext_tensor_map(&text, p.ext, dtype, (long long)B * H, p.lse_rows)) != FCS_OK) return rc;
 
@@ -793,6 +903,20 @@ const char* fcs_last_error(void) { return fcs::g_err; }
 
 int fcs_set_profiling(int enabled) {
     fcs::g_profiling = enabled != 0;
+    return FCS_OK;
+}
+
+int fcs_set_single_pass(int mode) {
+    if (mode < 0 || mode > 2) return FCS_ERR_INVALID_ARGUMENT;
+    fcs::g_single_pass = mode;
+    return FCS_OK;
+}
+
+int fcs_single_pass_info(int Sk, int* cluster_size, int* max_clusters) {
+    if (Sk <= 0 || Sk > 256 * fcs::sp::MAX_CL) return FCS_ERR_UNSUPPORTED;
+    const int cl = fcs::single_pass_cluster_size(Sk);
+    if (cluster_size) *cluster_size = cl;
+    if (max_clusters) *max_clusters = fcs::single_pass_max_clusters(cl);
     return FCS_OK;
 }
 

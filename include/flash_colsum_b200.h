@@ -173,6 +173,20 @@ int fcs_set_profiling(int enabled);
 int fcs_last_pass_ms(float *stats_ms, float *merge_ms, float *colsum_ms);
 
 /*
+ * Kernel choice for non-causal calls with head dimension 64 and at most 2048
+ * keys, which can run as one pass on thread-block clusters instead of the two
+ * streaming passes.  No counterpart in the reference.  mode 0: the single pass
+ * when the call has enough (batch, head) pairs to fill the device; 1 (default):
+ * never; 2: whenever the shape allows.  Process-wide; not thread-safe.  A
+ * single-pass call reports its whole duration as the column pass in
+ * fcs_last_pass_ms().
+ */
+int fcs_set_single_pass(int mode);
+/* CTAs per cluster the single pass uses for `Sk` keys (one per 256 keys, rounded up
+ * to a power of two) and how many such clusters the current device runs at once. */
+int fcs_single_pass_info(int Sk, int *cluster_size, int *max_clusters);
+
+/*
  * How a call with these sizes is decomposed on the current device: key ranges
  * per query tile in the statistics pass, its work items, the 128x128 score
  * tiles of the column pass, and the SM count used for planning.  Host
