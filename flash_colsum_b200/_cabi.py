@@ -14,7 +14,7 @@ EXPORTED_SYMBOLS = (
     "fcs_colsum_batched", "fcs_colsum_non_batched", "fcs_colsum_causal",
     "fcs_set_profiling", "fcs_last_pass_ms", "fcs_plan_info",
     "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate",
-    "fcs_set_single_pass", "fcs_single_pass_info",
+    "fcs_set_single_pass", "fcs_single_pass_info", "fcs_single_pass_applies",
 )
 
 FCS_OK = 0
@@ -78,6 +78,8 @@ def load() -> ctypes.CDLL:
     lib.fcs_set_profiling.argtypes = [_i]
     lib.fcs_set_single_pass.restype = _i
     lib.fcs_set_single_pass.argtypes = [_i]
+    lib.fcs_single_pass_applies.restype = _i
+    lib.fcs_single_pass_applies.argtypes = [_i, _i, _i, _i, _i]
     lib.fcs_single_pass_info.restype = _i
     lib.fcs_single_pass_info.argtypes = [_i, ctypes.POINTER(_i), ctypes.POINTER(_i)]
     lib.fcs_last_pass_ms.restype = _i
@@ -94,6 +96,11 @@ def last_error() -> str:
 
 def set_profiling(enabled: bool) -> None:
     load().fcs_set_profiling(int(bool(enabled)))
+
+
+def single_pass_applies(B: int, H: int, sk: int, D: int = 64, is_causal: bool = False) -> bool:
+    """Whether a call with these sizes takes the single-pass kernel under the current mode."""
+    return bool(load().fcs_single_pass_applies(B, H, sk, D, int(is_causal)))
 
 
 def single_pass_info(sk: int):

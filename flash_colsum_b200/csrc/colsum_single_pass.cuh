@@ -1,13 +1,15 @@
 // Single-pass attention column mean for short key axes (S_k <= 2048, head
-// dimension 64, non-causal), one thread-block cluster per (batch, head) stream.
+// dimension 64, non-causal), one thread-block cluster per stream of (batch, head)
+// pairs.
 //
 // The two-pass kernels evaluate every score and every exp twice.  When the whole
 // key axis fits a cluster of up to eight CTAs (256 keys each), one pass is enough:
 //
-//   S      = Q_tile K_slice^T            tcgen05 MMA, 128 queries x 256 keys, fp32 in tensor memory
+//   S      = Q_tile K_slice^T            tcgen05 MMA, 128 queries x 2 x 128 keys, fp32 in tensor memory
 //   P~     = exp2(c*S - m_g)             per thread (= query row) and 64-key group g, fp16 -> shared memory
 //   (m, l) exchange                      per row: 4 groups in the CTA, then all CTAs of the cluster
-//                                        through distributed shared memory
+//                                        through distributed shared memory (st.async + mbarrier
+//                                        byte counts: nobody waits for a store to land)
 //   w_g    = exp2(m_g - M) / L           the factor that turns P~ into softmax probabilities
 //   D2    += P~^T W                      second MMA: contraction over the 128 query rows; W holds
 //                                        w_g as two fp16 parts (hi + lo) in columns of a 16-wide
@@ -15,30 +17,19 @@
 //                                        sums of the keys of 64-key group a of a key tile
 //
 // D2 lives in tensor memory across all query tiles and heads of a batch entry and
-// is added to the output once per (cluster, batch entry).
+// is added to the output once per (cluster, batch entry).  P~ is double-buffered:
+// the column-sum MMA of tile i runs while the consumers work on tiles i+1 and i+2,
+// which is the time the statistics of tile i have to go around the cluster.
 //
-// Pipeline per CTA (i = running tile number):
-//   MMA warp   : scores(i) as soon as the consumers have read scores(i-1) out of
-//                tensor memory; column sums(i-1) once its P~ and W are in shared memory.
-//   consumers  : read scores(i), write P~(i) and their (max, sum); finish tile i-1
-//                (read the cluster's statistics, write W(i-1)); one group, a
-//                different one every tile, combines the CTA's four partials and posts
-//                them to every CTA of the cluster.
-// Because tile i-1 is finished a whole tile after its statistics were posted, the
-// exchange latency is off the critical path.
+// Measured against the two-pass kernels (fp16, H = 16): 1.67x at S = 256, 1.43x at
+// 512, 1.12-1.15x at 1024, 0.87x at 2048 (15 resident clusters of 8 use 120 of the
+// 148 SMs, and eight CTAs advance in step); key lengths that fill less than ~85 %
+// of their cluster's slices lose to the padding.  The host side picks accordingly.
 #pragma once
 
 #include "colsum_math.cuh"
 #include "sm100_ptx.cuh"
 
-#ifndef FCS_SP_X
-#define FCS_SP_X 0
-#endif
-#ifdef FCS_SP_TIMING
-#define TICK(k) { const long long now_ = clock64(); tacc[k] += now_ - tlast; tlast = now_; }
-#else
-#define TICK(k)
-#endif
 namespace fcs {
 
 struct SinglePassParams {
@@ -52,7 +43,7 @@ struct SinglePassParams {
     float* out;
     long long out_ld;
     int* status;
-    uint32_t idesc_scores;  // 128 x 256 x 16, K-major operands
+    uint32_t idesc_scores;  // 128 x 128 x 16, K-major operands
     uint32_t idesc_colsum;  // 128 x 16 x 16, A = P~ (M-major), B = W (K-major), fp16
 };
 
@@ -61,9 +52,14 @@ namespace sp {
 constexpr int CONSUMER_GROUPS = 4;
 constexpr int CONSUMER_WARPS = 16;
 constexpr int CONSUMER_THREADS = 512;
+constexpr int HALF_THREADS = 256;          // consumers of one half (two groups)
 constexpr int PRODUCER_WARP = 16;
 constexpr int MMA_WARP = 17;
-constexpr int THREADS = 576;
+constexpr int XCHG_WARP = 19;
+constexpr int XCHG_WARPS = 2;
+constexpr int XCHG_ROWS_PER_WARP = 128 / XCHG_WARPS;
+constexpr int XCHG_ROWS_PER_LANE = XCHG_ROWS_PER_WARP / 32;
+constexpr int THREADS = 32 * (XCHG_WARP + XCHG_WARPS);
 constexpr int MAX_CL = 8;
 constexpr int TMEM_COLS = 512;
 constexpr int D2_COL = 256;            // tensor-memory column of the column-sum accumulators
@@ -81,12 +77,12 @@ constexpr int K_OFF = 0;
 constexpr int Q_OFF = K_OFF + K_BYTES;             // two buffers
 constexpr int P_OFF = Q_OFF + 2 * Q_BYTES;         // two buffers
 constexpr int W_OFF = P_OFF + 2 * P_BYTES;         // one buffer: [2 key tiles][W_TILE_BYTES]
-constexpr int XCHG_OFF = W_OFF + 2 * W_TILE_BYTES; // float2 [2][MAX_CL][128]
+constexpr int XCHG_OFF = W_OFF + 2 * W_TILE_BYTES; // float2 [2][MAX_CL][128]: every CTA's (max, sum) per row
 constexpr int LST_OFF = XCHG_OFF + 2 * MAX_CL * 128 * 8;   // float2 [2][groups][128]
 constexpr int BAR_OFF = LST_OFF + 2 * CONSUMER_GROUPS * 128 * 8;
-constexpr int NUM_BARS = 16;
+constexpr int NUM_BARS = 28;
 constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-constexpr int TOTAL = MISC_OFF + 16 + 32;   // tensor-memory address, abort flag, post counters
+constexpr int TOTAL = MISC_OFF + 16;               // tensor-memory address, abort flag
 constexpr int DYN_BYTES = TOTAL + 1024;
 static_assert(DYN_BYTES <= 227 * 1024, "shared memory budget");
 
@@ -144,6 +140,25 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
             }
         }
     }
+}
+
+// 32 lanes x 16 consecutive fp32 columns.
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                   "+r"(r[15])
+                 :
+                 : "memory");
 }
 
 // Shared-memory descriptor of an M-major operand tile (the M index is contiguous in
@@ -214,6 +229,18 @@ __device__ __forceinline__ void exp8_packed(int pair0, const uint32_t* s, f32x2 
 // tm_q: boxes of 128 query rows, tm_k: boxes of 256 key rows (both 64 elements
 // wide, 128-byte swizzle).  Grid = clusters * CL CTAs, launched with cluster
 // dimension CL; CTA `rank` of a cluster owns keys [256*rank, 256*rank + 256).
+//
+// Roles in a CTA (21 warps):
+//   16 consumer warps  four groups of 128 threads (thread = query row of the tile, group =
+//                      64 key columns).  Groups 0,1 and groups 2,3 form two "halves" (the two
+//                      128-key tiles of the slice) with their own score accumulator, P~
+//                      buffers, column-sum accumulator and barriers, so that one half computes
+//                      while the other waits for its next scores.
+//   1 TMA warp         key slice per (batch, head), query tile per step.
+//   2 MMA warps        one per half: scores(i), column sums(i-2), scores(i+1), ...
+//   2 exchange warps   64 rows each: combine the four groups' (max, sum) of a row, post the
+//                      result to every CTA of the cluster, and when all CTAs' values are in,
+//                      write the weights W of the four groups.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(sp::THREADS, 1)
 colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -229,17 +256,21 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const uint32_t w_smem = smem_base + W_OFF;
     const uint32_t xchg_smem = smem_base + XCHG_OFF;
     const uint32_t bars = smem_base + BAR_OFF;
+    // barriers; `hf` is the half (key tile of the slice), `s` a P~ / statistics slot
     const uint32_t k_full = bars, k_empty = bars + 8;
-    auto q_full = [&](int i) { return bars + 8u * (2 + i); };
-    auto q_empty = [&](int i) { return bars + 8u * (4 + i); };
-    const uint32_t s_full = bars + 8 * 6, s_empty = bars + 8 * 7;
-    auto xchg_bar = [&](int i) { return bars + 8u * (8 + i); };
-    auto pw_ready = [&](int i) { return bars + 8u * (10 + i); };
-    auto pw_free = [&](int i) { return bars + 8u * (12 + i); };
-    const uint32_t d2_full = bars + 8 * 14, d2_empty = bars + 8 * 15;
+    auto q_full = [&](int s) { return bars + 8u * (2 + s); };
+    auto q_empty = [&](int s) { return bars + 8u * (4 + s); };
+    auto s_full = [&](int hf) { return bars + 8u * (6 + hf); };
+    auto s_empty = [&](int hf) { return bars + 8u * (8 + hf); };
+    auto stats_bar = [&](int s) { return bars + 8u * (10 + s); };
+    auto xchg_bar = [&](int s) { return bars + 8u * (12 + s); };
+    auto w_ready = [&](int s) { return bars + 8u * (14 + s); };
+    auto p_ready = [&](int s, int hf) { return bars + 8u * (16 + 2 * s + hf); };
+    auto pw_free = [&](int s, int hf) { return bars + 8u * (20 + 2 * s + hf); };
+    auto d2_full = [&](int hf) { return bars + 8u * (24 + hf); };
+    auto d2_empty = [&](int hf) { return bars + 8u * (26 + hf); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + MISC_OFF);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + MISC_OFF + 4);
-    int* post_count = reinterpret_cast<int*>(smem + MISC_OFF + 16);   // [2 slots][4 row blocks]
     float2* lstats = reinterpret_cast<float2*>(smem + LST_OFF);
     const float2* xchg = reinterpret_cast<const float2*>(smem + XCHG_OFF);
 
@@ -250,18 +281,22 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const int cluster_id = blockIdx.x / CL;
     const int u0 = (int)((long long)p.units * cluster_id / p.clusters);
     const int u1 = (int)((long long)p.units * (cluster_id + 1) / p.clusters);
+    const int NQ = p.NQ;
 
     if (threadIdx.x == 0) {
-        mbar_init(k_full, 1); mbar_init(k_empty, 1);
+        mbar_init(k_full, 1); mbar_init(k_empty, 2);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(q_full(i), 1); mbar_init(q_empty(i), 1);
-            mbar_init(xchg_bar(i), 4);   // this CTA's four posting warps; the data counts as bytes
-            mbar_init(pw_ready(i), CONSUMER_THREADS);
-            mbar_init(pw_free(i), 1);
+            mbar_init(q_full(i), 1); mbar_init(q_empty(i), 2);   // released by both halves' score MMAs
+            mbar_init(s_full(i), 1); mbar_init(s_empty(i), HALF_THREADS);
+            mbar_init(stats_bar(i), CONSUMER_THREADS);
+            mbar_init(xchg_bar(i), XCHG_WARPS);   // this CTA's exchange warps; the data counts as bytes
+            mbar_init(w_ready(i), XCHG_WARPS * 32);
+            for (int hf = 0; hf < 2; ++hf) {
+                mbar_init(p_ready(i, hf), HALF_THREADS);
+                mbar_init(pw_free(i, hf), 1);
+            }
+            mbar_init(d2_full(i), 1); mbar_init(d2_empty(i), HALF_THREADS);
         }
-        mbar_init(s_full, 1); mbar_init(s_empty, CONSUMER_THREADS);
-        mbar_init(d2_full, 1); mbar_init(d2_empty, CONSUMER_THREADS);
-        for (int i = 0; i < 8; ++i) post_count[i] = 0;
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -302,7 +337,7 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 tma_load_4d(k_smem, &tm_k, k_full, 0, 256 * (int)rank, h, b);
             }
             __syncwarp();
-            for (int t = 0; t < p.NQ; ++t, ++i) {
+            for (int t = 0; t < NQ; ++t, ++i) {
                 const int qs = i & 1;
                 if (!wait_all(q_empty(qs), ((i >> 1) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
                 if (elect_one_sync()) {
@@ -312,75 +347,128 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 __syncwarp();
             }
         }
-    } else if (warp == MMA_WARP) {
-        // ------------------------------------------------ MMA issuer
+    } else if (warp >= XCHG_WARP) {
+        // ------------------------------------------------ statistics exchange and weights
+        const int xw = warp - XCHG_WARP;
+        const int total = (u1 - u0) * NQ;
+        for (int i = 0; i < total; ++i) {
+            const int slot = i & 1;
+            const int t = i % NQ;
+            // (1) the four groups' (max, sum) of this CTA -> one pair per row, posted to every CTA
+            if (!wait_all(stats_bar(slot), (i >> 1) & 1, FCS_STATUS_WAIT_CONSUMER)) break;
+            float mg[XCHG_ROWS_PER_LANE][CONSUMER_GROUPS];
+#pragma unroll
+            for (int rr = 0; rr < XCHG_ROWS_PER_LANE; ++rr) {
+                const int row = xw * XCHG_ROWS_PER_WARP + rr * 32 + lane;
+                const float2* ls = lstats + slot * CONSUMER_GROUPS * 128 + row;
+                float2 o[CONSUMER_GROUPS];
+#pragma unroll
+                for (int g = 0; g < CONSUMER_GROUPS; ++g) { o[g] = ls[g * 128]; mg[rr][g] = o[g].x; }
+                const float mm = fmaxf(fmaxf(o[0].x, o[1].x), fmaxf(o[2].x, o[3].x));
+                const float ms = (mm == -INFINITY) ? 0.f : mm;
+                float ll = 0.f;
+#pragma unroll
+                for (int g = 0; g < CONSUMER_GROUPS; ++g) ll = fmaf(o[g].y, ex2_approx(o[g].x - ms), ll);
+                const uint32_t dst = xchg_smem + (uint32_t)(((slot * MAX_CL + (int)rank) * 128 + row) * 8);
+                for (int r = 0; r < CL; ++r)
+                    st_async_f32x2(map_to_cta(dst, (uint32_t)r), mm, ll, map_to_cta(xchg_bar(slot), (uint32_t)r));
+            }
+            // what this CTA's own barrier will receive for this warp's rows: 8 bytes per row and CTA
+            if (lane == 0) mbar_arrive_expect_tx(xchg_bar(slot), (uint32_t)(CL * XCHG_ROWS_PER_WARP * 8));
+
+            // (2) every CTA's pair of the row -> the weights of this CTA's four groups
+            bool good = mbar_wait_cluster(xchg_bar(slot), (i >> 1) & 1, abort_flag, p.status,
+                                          FCS_STATUS_WAIT_CONSUMER);
+            if (good && i > 0) {   // the MMAs that read W(i-1) must be done before W is rewritten
+                good = mbar_wait(pw_free((i - 1) & 1, 0), ((i - 1) >> 1) & 1, abort_flag, p.status,
+                                 FCS_STATUS_WAIT_CONSUMER) &&
+                       mbar_wait(pw_free((i - 1) & 1, 1), ((i - 1) >> 1) & 1, abort_flag, p.status,
+                                 FCS_STATUS_WAIT_CONSUMER);
+            }
+            if (!__all_sync(0xffffffffu, good)) break;
+#pragma unroll
+            for (int rr = 0; rr < XCHG_ROWS_PER_LANE; ++rr) {
+                const int row = xw * XCHG_ROWS_PER_WARP + rr * 32 + lane;
+                const float2* xs = xchg + slot * MAX_CL * 128 + row;
+                float2 o[MAX_CL];
+#pragma unroll
+                for (int r = 0; r < MAX_CL; ++r) o[r] = (r < CL) ? xs[r * 128] : make_float2(-INFINITY, 0.f);
+                const float M = fmaxf(fmaxf(fmaxf(o[0].x, o[1].x), fmaxf(o[2].x, o[3].x)),
+                                      fmaxf(fmaxf(o[4].x, o[5].x), fmaxf(o[6].x, o[7].x)));
+                float L = 0.f;
+#pragma unroll
+                for (int r = 0; r < MAX_CL; ++r) L = fmaf(o[r].y, ex2_approx(o[r].x - M), L);
+                const float base = W_SCALE_LOG2 - M - __log2f(L);
+                const bool live = t * 128 + row < p.Sq;   // rows past the end of the query axis weigh nothing
+                // columns 2a (hi), 2a + 1 (lo) of half hf's operand belong to group 2*hf + a
+                const uint32_t w_row = w_smem + (row >> 4) * 512 + (row & 15) * 2;
+#pragma unroll
+                for (int g = 0; g < CONSUMER_GROUPS; ++g) {
+                    const float w = live ? ex2_approx(mg[rr][g] + base) : 0.f;
+                    const __half w_hi = __float2half_rn(w);
+                    const __half w_lo = __float2half_rn(w - __half2float(w_hi));
+                    const uint32_t a = w_row + (g >> 1) * W_TILE_BYTES + (2 * (g & 1)) * 32;
+                    st_shared_u16(a, __half_as_ushort(w_hi));
+                    st_shared_u16(a + 32, __half_as_ushort(w_lo));
+                }
+            }
+            mbar_arrive(w_ready(slot));   // (the MMA warps fence before the tensor core reads W)
+        }
+    } else if (warp >= MMA_WARP) {
+        // ------------------------------------------------ MMA issuers, one warp per half
         // Issue order: scores(i), column sums(i-2), scores(i+1), ... -- the order in which
-        // their inputs become ready (scores(i+1) when the consumers have read scores(i),
-        // column sums(i-1) only when the consumers are through with tile i).
+        // their inputs become ready: scores(i+1) when the half's consumers have read
+        // scores(i) out of tensor memory, column sums(i-1) only after the statistics of
+        // tile i-1 have gone around the cluster.
+        const int hf = warp - MMA_WARP;
         int i = 0, uc = 0, fc = 0;
         int first = 0;                // first tile of the current batch entry on this CTA
-        bool ok = true, d2_fresh = true;
-#ifdef FCS_SP_TIMING
-        long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tlast = clock64();
-#endif
-        // column sums of tile j: D2[kt] (+)= P~(j, kt)^T W(j, kt)
+        bool ok = true, fresh = true; // fresh: the next column-sum MMA starts a new accumulation
+        // column sums of tile j: D2_hf (+)= P~(j)^T W(j)
         auto colsum_mma = [&](int j, bool last) -> bool {
             const int slot = j & 1;
-            TICK(7)
-            if (!wait_all(pw_ready(slot), (j >> 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
-            TICK(4)
-            if (d2_fresh && fc > 0) {   // the previous batch entry's sums have been read out
-                if (!wait_all(d2_empty, (fc - 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
+            if (!wait_all(p_ready(slot, hf), (j >> 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
+            if (!wait_all(w_ready(slot), (j >> 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
+            if (fresh && fc > 0) {   // the previous batch entry's sums have been read out
+                if (!wait_all(d2_empty(hf), (fc - 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
             }
+            // P~ and W were written with ordinary stores by threads this warp has just
+            // synchronised with; the fence orders them before the tensor core's reads
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_after();
+            const uint64_t da = umma_desc_mn_sw128(p_smem + slot * P_BYTES + hf * P_TILE_BYTES);
+            const uint64_t db = umma_desc_k_sw32(w_smem + hf * W_TILE_BYTES);
             if (elect_one_sync()) {
 #pragma unroll
-                for (int kt = 0; kt < 2; ++kt) {
-                    const uint64_t da = umma_desc_mn_sw128(p_smem + slot * P_BYTES + kt * P_TILE_BYTES);
-                    const uint64_t db = umma_desc_k_sw32(w_smem + kt * W_TILE_BYTES);
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)   // 16 query rows per instruction
-                        if (!(FCS_SP_X & 1)) umma_f16(tmem_base + D2_COL + W_N * kt, da + (uint64_t)((ks * 2048) >> 4),
-                                 db + (uint64_t)((ks * 512) >> 4), p.idesc_colsum,
-                                 (d2_fresh && ks == 0) ? 0u : 1u);
-                }
-                umma_commit(pw_free(slot));
-                if (last) umma_commit(d2_full);
+                for (int ks = 0; ks < 8; ++ks)   // 16 query rows per instruction
+                    umma_f16(tmem_base + D2_COL + W_N * hf, da + (uint64_t)((ks * 2048) >> 4),
+                             db + (uint64_t)((ks * 512) >> 4), p.idesc_colsum, (fresh && ks == 0) ? 0u : 1u);
+                umma_commit(pw_free(slot, hf));
+                if (last) umma_commit(d2_full(hf));
             }
             __syncwarp();
-            TICK(5)
-#ifdef FCS_SP_TIME_MMA2
-            wait_all(pw_free(slot), (j >> 1) & 1, FCS_STATUS_WAIT_MMA);
-            TICK(6)
-#endif
-            d2_fresh = false;
+            fresh = false;
             return true;
         };
+        const uint64_t dk = umma_desc_k_sw128(k_smem + hf * (K_BYTES / 2));
         for (int u = u0; ok && u < u1; ++u, ++uc) {
-            TICK(7)
             if (!wait_all(k_full, uc & 1, FCS_STATUS_WAIT_MMA)) break;
-            TICK(0)
-            const uint64_t dk = umma_desc_k_sw128(k_smem);
-            for (int t = 0; t < p.NQ; ++t, ++i) {
+            for (int t = 0; t < NQ; ++t, ++i) {
                 const int qs = i & 1;
-                TICK(7)
                 if (!wait_all(q_full(qs), (i >> 1) & 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
-                TICK(1)
-                if (!wait_all(s_empty, (i & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
-                TICK(2)
+                if (!wait_all(s_empty(hf), (i & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t dq = umma_desc_k_sw128(q_smem + qs * Q_BYTES);
                 if (elect_one_sync()) {
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks)
-                        umma_f16(tmem_base, dq + (uint64_t)((ks * 32) >> 4), dk + (uint64_t)((ks * 32) >> 4),
+                        umma_f16(tmem_base + 128 * hf, dq + (uint64_t)((ks * 32) >> 4), dk + (uint64_t)((ks * 32) >> 4),
                                  p.idesc_scores, ks > 0 ? 1u : 0u);
-                    umma_commit(s_full);
+                    umma_commit(s_full(hf));
                     umma_commit(q_empty(qs));
-                    if (t + 1 == p.NQ) umma_commit(k_empty);
+                    if (t + 1 == NQ) umma_commit(k_empty);
                 }
                 __syncwarp();
-                TICK(3)
                 if (i - first >= 2) {
                     if (!colsum_mma(i - 2, false)) { ok = false; break; }
                 }
@@ -391,81 +479,33 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 if (i - first >= 2 && !colsum_mma(i - 2, false)) break;
                 if (!colsum_mma(i - 1, true)) break;
                 first = i;
-                d2_fresh = true;
+                fresh = true;
                 ++fc;
             }
         }
-#ifdef FCS_SP_TIMING
-        if (blockIdx.x == 0 && lane == 0)
-            printf("mma tiles %d: k_full %lld q_full %lld s_empty %lld issue1 %lld pw_ready %lld issue2 %lld mma2-exec %lld other %lld\n",
-                   i, tacc[0], tacc[1], tacc[2], tacc[3], tacc[4], tacc[5], tacc[6], tacc[7]);
-#endif
     } else {
         // ------------------------------------------------ consumers
         const int wg = warp >> 2;                  // group: columns 64*wg .. 64*wg+63 of the scores
+        const int hf = wg >> 1;                    // half = key tile of the slice
+        const int half64 = wg & 1;                 // 64-key half of that key tile
         const int w4 = warp & 3;                   // 32-row block of the tile
         const int row = (w4 << 5) | lane;          // tensor-memory lane = query row of the tile
         const uint32_t lane_base = tmem_base + ((uint32_t)(w4 << 5) << 16);
         const float c = p.c;
-        const int kt = wg >> 1;                    // key tile of the slice, and 64-key half of it
-        const int half64 = wg & 1;
         const int keys_valid = p.Sk - (256 * (int)rank + 64 * wg);   // >= 64: the whole group is real keys
         // this thread's 128-byte line of P~ (one line per query row and 64-key group)
-        const uint32_t p_line = (uint32_t)(kt * P_TILE_BYTES + half64 * P_ATOM_COL_BYTES + (row >> 3) * 1024 +
+        const uint32_t p_line = (uint32_t)(hf * P_TILE_BYTES + half64 * P_ATOM_COL_BYTES + (row >> 3) * 1024 +
                                            (row & 7) * 128);
         const uint32_t sw = (uint32_t)(row & 7);
-        // this thread's two weight elements: columns 2*half64 (hi), 2*half64 + 1 (lo)
-        const uint32_t w_addr = w_smem + kt * W_TILE_BYTES + (row >> 4) * 512 + (2 * half64) * 32 + (row & 15) * 2;
         int i = 0, fc = 0;
-        bool ok = true, have_prev = false;
-#ifdef FCS_SP_TIMING
-        long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tlast = clock64();
-#endif
-        float m_prev = 0.f;
-        int t_prev = 0;
-
-        // Finish tile j: all CTAs' (max, sum) of the row -> this group's weight.
-        auto finish_tile = [&](int j) -> bool {
-            const int slot = j & 1;
-            bool good = (FCS_SP_X & 2) ? true : mbar_wait_cluster(xchg_bar(slot), (j >> 1) & 1, abort_flag, p.status,
-                                          FCS_STATUS_WAIT_CONSUMER);
-            // the MMA that read W(j-1) must be done before W is rewritten
-            if (good && j > 0)
-                good = mbar_wait(pw_free((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, p.status,
-                                 FCS_STATUS_WAIT_CONSUMER);
-            good = __all_sync(0xffffffffu, good);
-            if (!good) return false;
-            TICK(5)
-            const float2* xs = xchg + slot * MAX_CL * 128 + row;
-            float2 o[MAX_CL];
-#pragma unroll
-            for (int r = 0; r < MAX_CL; ++r) o[r] = (r < CL) ? xs[r * 128] : make_float2(-INFINITY, 0.f);
-            float M = fmaxf(fmaxf(fmaxf(o[0].x, o[1].x), fmaxf(o[2].x, o[3].x)),
-                            fmaxf(fmaxf(o[4].x, o[5].x), fmaxf(o[6].x, o[7].x)));
-            float L = 0.f;
-#pragma unroll
-            for (int r = 0; r < MAX_CL; ++r) L = fmaf(o[r].y, ex2_approx(o[r].x - M), L);
-            float w = ex2_approx(m_prev - M - __log2f(L) + W_SCALE_LOG2);
-            if (t_prev * 128 + row >= p.Sq) w = 0.f;   // rows past the end of the query axis
-            const __half w_hi = __float2half_rn(w);
-            const __half w_lo = __float2half_rn(w - __half2float(w_hi));
-            st_shared_u16(w_addr, __half_as_ushort(w_hi));
-            st_shared_u16(w_addr + 32, __half_as_ushort(w_lo));
-            TICK(6)
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P~ and W -> the MMA's view
-            mbar_arrive(pw_ready(slot));
-            TICK(7)
-            return true;
-        };
-
+        bool ok = true;
         for (int u = u0; ok && u < u1; ++u) {
-            for (int t = 0; t < p.NQ; ++t, ++i) {
+            for (int t = 0; t < NQ; ++t, ++i) {
                 const int slot = i & 1;
                 // ---- scores of this thread's row and group
-                ok = mbar_wait(s_full, i & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+                ok = mbar_wait(s_full(hf), i & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                TICK(0)
                 tc_fence_after();
                 uint32_t sa[32], sb[32];   // columns 0..31 and 32..63 of the group
                 tmem_ld_x32(lane_base + 64 * wg, sa);
@@ -473,10 +513,9 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 tmem_ld_wait(sa);
                 tmem_ld_wait(sb);
                 tc_fence_before();
-                mbar_arrive(s_empty);
-                TICK(1)
+                mbar_arrive(s_empty(hf));
 
-                // ---- P~ = exp2(c*s - m_g) as packed fp16, kept in registers until its buffer is free
+                // ---- P~ = exp2(c*s - m_g) as packed fp16
                 uint32_t h[32];
                 float m_g, l_g;
                 if (keys_valid >= 64) {
@@ -516,90 +555,47 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                     }
                     l_g = acc;
                 }
-                TICK(2)
-                // ---- finish the previous tile, whose statistics were posted a tile ago
-                if (have_prev) { ok = finish_tile(i - 1); if (!ok) break; }
-
-                // ---- this group's (max, sum); the last of the four groups to get here for a
-                // block of 32 rows combines them and posts the result to every CTA of the cluster
-                lstats[(slot * CONSUMER_GROUPS + wg) * 128 + row] = make_float2(m_g, l_g);
-                __threadfence_block();
-                __syncwarp();
-                int arrived = 0;
-                if (lane == 0) arrived = atomicAdd(&post_count[slot * 4 + w4], 1);
-                arrived = __shfl_sync(0xffffffffu, arrived, 0);
-                if (!(FCS_SP_X & 8) && arrived == CONSUMER_GROUPS - 1) {
-                    if (lane == 0) post_count[slot * 4 + w4] = 0;
-                    __threadfence_block();
-                    const float2* ls = lstats + slot * CONSUMER_GROUPS * 128 + row;
-                    float mm = -INFINITY;
-#pragma unroll
-                    for (int g = 0; g < CONSUMER_GROUPS; ++g) mm = fmaxf(mm, ls[g * 128].x);
-                    const float ms = (mm == -INFINITY) ? 0.f : mm;
-                    float ll = 0.f;
-#pragma unroll
-                    for (int g = 0; g < CONSUMER_GROUPS; ++g) {
-                        const float2 o = ls[g * 128];
-                        ll += o.y * ex2_approx(o.x - ms);
-                    }
-                    const uint32_t dst = xchg_smem + (uint32_t)(((slot * MAX_CL + (int)rank) * 128 + row) * 8);
-                    for (int r = 0; r < CL; ++r)
-                        st_async_f32x2(map_to_cta(dst, (uint32_t)r), mm, ll, map_to_cta(xchg_bar(slot), (uint32_t)r));
-                    // what this CTA's own barrier will receive for these 32 rows: 8 bytes per row and CTA
-                    if (lane == 0) mbar_arrive_expect_tx(xchg_bar(slot), (uint32_t)CL * 32u * 8u);
-                }
-                // ---- P~(i) may overwrite P~(i-2) once the MMA that read it is done
-                ok = mbar_wait(pw_free(slot), ((i >> 1) & 1) ^ 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+                // ---- tile i-2 is through: its column-sum MMA has read P~(i-2), and (before that)
+                // the exchange warps have read its statistics -- both slots are free
+                ok = mbar_wait(pw_free(slot, hf), ((i >> 1) & 1) ^ 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                TICK(3)
+                // ---- this group's (max, sum), for the exchange warps
+                lstats[(slot * CONSUMER_GROUPS + wg) * 128 + row] = make_float2(m_g, l_g);
+                mbar_arrive(stats_bar(slot));
                 {
                     const uint32_t line = p_smem + slot * P_BYTES + p_line;
 #pragma unroll
                     for (int j8 = 0; j8 < 8; ++j8)
-                        if (!(FCS_SP_X & 4)) st_shared_v4(line + ((((uint32_t)j8) ^ sw) << 4), h[4 * j8], h[4 * j8 + 1], h[4 * j8 + 2],
+                        st_shared_v4(line + ((((uint32_t)j8) ^ sw) << 4), h[4 * j8], h[4 * j8 + 1], h[4 * j8 + 2],
                                      h[4 * j8 + 3]);
                 }
-                TICK(4)
-                m_prev = m_g;
-                t_prev = t;
-                have_prev = true;
+                // (the MMA warp makes these stores visible to the tensor core: it fences after its wait)
+                mbar_arrive(p_ready(slot, hf));
             }
             if (!ok) break;
             if (last_of_batch(u)) {
-                ok = finish_tile(i - 1);
-                if (!ok) break;
-                have_prev = false;
                 // ---- column sums of this batch entry -> output
-                ok = mbar_wait(d2_full, fc & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+                ok = mbar_wait(d2_full(hf), fc & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                if (wg == 0) {
-                    uint32_t d[32];
-                    tmem_ld_x32(lane_base + D2_COL, d);
-                    tmem_ld_wait(d);
+                if (half64 == 0) {
+                    uint32_t d[16];
+                    tmem_ld_x16(lane_base + D2_COL + W_N * hf, d);
+                    tmem_ld_wait16(d);
                     const int b = u / p.H;
-                    const int a = row >> 6;   // 64-key half of the tile this lane's key belongs to
-#pragma unroll
-                    for (int kk = 0; kk < 2; ++kk) {
-                        const float v0 = __uint_as_float(d[W_N * kk]) + __uint_as_float(d[W_N * kk + 1]);
-                        const float v1 = __uint_as_float(d[W_N * kk + 2]) + __uint_as_float(d[W_N * kk + 3]);
-                        const int key = 256 * (int)rank + 128 * kk + row;
-                        if (key < p.Sk)
-                            atomicAdd_system(p.out + (long long)b * p.out_ld + key, (a ? v1 : v0) * p.out_scale);
-                    }
+                    // lanes 0..63 hold keys of the first 64-key group (columns 0, 1), the rest columns 2, 3
+                    const float v = (row >> 6) ? __uint_as_float(d[2]) + __uint_as_float(d[3])
+                                               : __uint_as_float(d[0]) + __uint_as_float(d[1]);
+                    const int key = 256 * (int)rank + 128 * hf + row;
+                    if (key < p.Sk) atomicAdd_system(p.out + (long long)b * p.out_ld + key, v * p.out_scale);
                 }
                 tc_fence_before();
-                mbar_arrive(d2_empty);
+                mbar_arrive(d2_empty(hf));
                 ++fc;
             }
         }
-#ifdef FCS_SP_TIMING
-        if (blockIdx.x == 0 && lane == 0 && (warp & 3) == 0)
-            printf("grp %d tiles %d: s_full %lld ld %lld math %lld post+pw_free %lld store %lld xchg-wait %lld weights %lld fence+arrive %lld\n",
-                   wg, i, tacc[0], tacc[1], tacc[2], tacc[3], tacc[4], tacc[5], tacc[6], tacc[7]);
-#endif
     }
 
     // ---------------------------------------------------- teardown

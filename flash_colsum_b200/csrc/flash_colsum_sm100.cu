@@ -650,9 +650,10 @@ static int launch_small_q(const void* q, const void* k, float* out, int64_t out_
 }
 
 // Short key axes (non-causal, head dimension 64, S_k <= 2048): the single-pass
-// cluster kernel.  g_single_pass: 0 = when the shape fills enough of the device,
-// 1 = never, 2 = whenever the shape allows.
-static int g_single_pass = 1;
+// cluster kernel.  g_single_pass: 0 = where it is the faster of the two (measured:
+// up to 1024 keys, when the keys fill their 256-key slices well and there are enough
+// (batch, head) pairs to occupy the device), 1 = never, 2 = whenever the shape allows.
+static int g_single_pass = 0;
 
 static int single_pass_cluster_size(int Sk) {
     const int slices = (Sk + 255) / 256;
@@ -664,7 +665,10 @@ static int single_pass_cluster_size(int Sk) {
 static bool single_pass_applies(int B, int H, int Sk, int D, int causal) {
     if (g_single_pass == 1 || causal || D != 64 || Sk > 256 * sp::MAX_CL) return false;
     if (g_single_pass == 2) return true;
-    return (long long)B * H * single_pass_cluster_size(Sk) >= 32;
+    const int cl = single_pass_cluster_size(Sk);
+    if (cl > 4) return false;                                  // 2048 keys: the two passes are faster
+    if ((long long)Sk * 100 < (long long)cl * 256 * 85) return false;   // too much padding
+    return (long long)B * H * cl >= 32;
 }
 
 // Clusters of `cl` CTAs that can be resident at once (0 if the query fails).
@@ -720,8 +724,9 @@ static int launch_single_pass(const CUtensorMap& tq, const CUtensorMap& tk, floa
     sp_.out_ld = out_ld;
     sp_.status = status;
     const uint32_t fmt = dtype == FCS_DTYPE_BF16 ? 1u : 0u;
+    // one score MMA covers the 128 keys of a half: M = 128, N = 128
     sp_.idesc_scores = (1u << 4) | (fmt << 7) | (fmt << 10) | ((scale < 0.f ? 1u : 0u) << 13) |
-                       ((uint32_t)(BLOCK >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
+                       ((uint32_t)(TILE >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
     // fp16 x fp16 -> fp32, A stored with the M index contiguous, B K-major, M = 128, N = 16
     sp_.idesc_colsum = (1u << 4) | (1u << 15) | ((uint32_t)(sp::W_N >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
     cudaLaunchConfig_t cfg;
@@ -910,6 +915,11 @@ int fcs_set_single_pass(int mode) {
     if (mode < 0 || mode > 2) return FCS_ERR_INVALID_ARGUMENT;
     fcs::g_single_pass = mode;
     return FCS_OK;
+}
+
+int fcs_single_pass_applies(int B, int H, int Sk, int D, int is_causal) {
+    if (B <= 0 || H <= 0 || Sk <= 0) return 0;
+    return fcs::single_pass_applies(B, H, Sk, D, is_causal ? 1 : 0) ? 1 : 0;
 }
 
 int fcs_single_pass_info(int Sk, int* cluster_size, int* max_clusters) {

@@ -64,3 +64,30 @@ def test_no_cpu_fallback_in_the_product_package():
             if fn.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, fn)).read()
                 assert "oracle" not in text, os.path.join(dirpath, fn)
+
+
+def test_kernel_choice_rule_is_host_arithmetic():
+    """Which calls take the single-pass cluster kernel: short, well-filled, non-causal, head
+    dimension 64, enough (batch, head) pairs; the setter overrides in both directions."""
+    from flash_colsum_b200 import _cabi
+    try:
+        _cabi.set_single_pass(_cabi.SINGLE_PASS_AUTO)
+        assert _cabi.single_pass_applies(8, 16, 256)
+        assert _cabi.single_pass_applies(8, 16, 512)
+        assert _cabi.single_pass_applies(8, 16, 1024)
+        assert _cabi.single_pass_applies(8, 16, 900)           # 88 % of four slices
+        assert not _cabi.single_pass_applies(8, 16, 577)       # 56 % of four slices
+        assert not _cabi.single_pass_applies(8, 16, 2048)      # eight-CTA clusters lose to two passes
+        assert not _cabi.single_pass_applies(8, 16, 4096)      # does not fit a cluster
+        assert not _cabi.single_pass_applies(1, 2, 512)        # too few pairs to occupy the device
+        assert not _cabi.single_pass_applies(8, 16, 512, D=128)
+        assert not _cabi.single_pass_applies(8, 16, 512, is_causal=True)
+        _cabi.set_single_pass(_cabi.SINGLE_PASS_ALWAYS)
+        assert _cabi.single_pass_applies(1, 1, 2048) and _cabi.single_pass_applies(8, 16, 577)
+        assert not _cabi.single_pass_applies(8, 16, 4096)
+        _cabi.set_single_pass(_cabi.SINGLE_PASS_NEVER)
+        assert not _cabi.single_pass_applies(8, 16, 512)
+        with pytest.raises(ValueError):
+            _cabi.set_single_pass(7)
+    finally:
+        _cabi.set_single_pass(_cabi.SINGLE_PASS_AUTO)
