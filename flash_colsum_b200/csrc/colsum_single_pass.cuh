@@ -38,6 +38,7 @@ struct SinglePassParams {
     int CL;                 // CTAs per cluster = 256-key slices (1, 2, 4 or 8)
     int units;              // B * H
     int clusters;           // gridDim.x / CL
+    int flush_units;        // most (batch, head) pairs accumulated in tensor memory before a flush
     float c;                // |scale| * log2(e)
     float out_scale;        // 1 / (h_norm * R * 2^10): the weights are stored times 2^10
     float* out;
@@ -323,7 +324,13 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         const bool ok = mbar_wait(bar, parity, abort_flag, p.status, code);
         return __all_sync(0xffffffffu, ok);
     };
-    auto last_of_batch = [&](int u) { return (u + 1 == u1) || ((u + 1) / p.H != u / p.H); };
+    // The column sums leave tensor memory at the end of a batch entry, of this cluster's range,
+    // and every `flush_units` pairs: the tensor core truncates when it adds into its fp32
+    // accumulator (about half a unit in the last place lost per accumulation), and the bound
+    // keeps that bias below ~1e-4 of a column sum however many heads there are.
+    auto last_of_batch = [&](int u) {
+        return (u + 1 == u1) || ((u + 1) / p.H != u / p.H) || ((u + 1 - u0) % p.flush_units == 0);
+    };
 
     if (warp == PRODUCER_WARP) {
         // ------------------------------------------------ TMA producer

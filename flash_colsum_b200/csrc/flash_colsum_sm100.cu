@@ -718,6 +718,8 @@ static int launch_single_pass(const CUtensorMap& tq, const CUtensorMap& tk, floa
     sp_.CL = single_pass_cluster_size(Sk);
     sp_.units = B * H;
     sp_.clusters = sp_.units < max_clusters ? sp_.units : max_clusters;
+    // at most ~1024 accumulations (16 query rows each) per flush
+    sp_.flush_units = 128 / sp_.NQ > 1 ? 128 / sp_.NQ : 1;
     sp_.c = fabsf(scale) * 1.4426950408889634f;
     sp_.out_scale = 1.0f / ((float)h_norm * (float)Sq * 1024.0f);
     sp_.out = out;

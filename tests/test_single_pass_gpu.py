@@ -59,6 +59,7 @@ SHAPES = [
     (3, 4, 577, "fp16", 5),          # cls_len: five query rows (more than the few-row kernel takes)
     (3, 4, 577, "fp16", 200),        # cls_len: ragged second query tile
     (40, 4, 256, "fp16", None),      # more (batch, head) pairs than resident clusters: several per cluster
+    (2, 64, 512, "fp16", None),      # many heads: intermediate flushes of the tensor-memory accumulator
 ]
 
 
