@@ -56,7 +56,7 @@ constexpr int CONSUMER_THREADS = 512;
 constexpr int HALF_THREADS = 256;          // consumers of one half (two groups)
 constexpr int PRODUCER_WARP = 16;
 constexpr int MMA_WARP = 17;
-constexpr int XCHG_WARP = 19;
+constexpr int XCHG_WARP = 18;
 constexpr int XCHG_WARPS = 2;
 constexpr int XCHG_ROWS_PER_WARP = 128 / XCHG_WARPS;
 constexpr int XCHG_ROWS_PER_LANE = XCHG_ROWS_PER_WARP / 32;
@@ -231,14 +231,14 @@ __device__ __forceinline__ void exp8_packed(int pair0, const uint32_t* s, f32x2 
 // wide, 128-byte swizzle).  Grid = clusters * CL CTAs, launched with cluster
 // dimension CL; CTA `rank` of a cluster owns keys [256*rank, 256*rank + 256).
 //
-// Roles in a CTA (21 warps):
+// Roles in a CTA (20 warps):
 //   16 consumer warps  four groups of 128 threads (thread = query row of the tile, group =
 //                      64 key columns).  Groups 0,1 and groups 2,3 form two "halves" (the two
 //                      128-key tiles of the slice) with their own score accumulator, P~
 //                      buffers, column-sum accumulator and barriers, so that one half computes
 //                      while the other waits for its next scores.
 //   1 TMA warp         key slice per (batch, head), query tile per step.
-//   2 MMA warps        one per half: scores(i), column sums(i-2), scores(i+1), ...
+//   1 MMA warp         scores(i) of both halves, column sums(i-2) of both halves, scores(i+1), ...
 //   2 exchange warps   64 rows each: combine the four groups' (max, sum) of a row, post the
 //                      result to every CTA of the cluster, and when all CTAs' values are in,
 //                      write the weights W of the four groups.
@@ -421,61 +421,67 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             }
             mbar_arrive(w_ready(slot));   // (the MMA warps fence before the tensor core reads W)
         }
-    } else if (warp >= MMA_WARP) {
-        // ------------------------------------------------ MMA issuers, one warp per half
-        // Issue order: scores(i), column sums(i-2), scores(i+1), ... -- the order in which
-        // their inputs become ready: scores(i+1) when the half's consumers have read
-        // scores(i) out of tensor memory, column sums(i-1) only after the statistics of
-        // tile i-1 have gone around the cluster.
-        const int hf = warp - MMA_WARP;
+    } else if (warp == MMA_WARP) {
+        // ------------------------------------------------ MMA issuer
+        // Issue order: scores(i) of both halves, column sums(i-2) of both halves, scores(i+1),
+        // ... -- the order in which their inputs become ready: scores(i+1) when the consumers
+        // have read scores(i) out of tensor memory, column sums(i-1) only after the statistics
+        // of tile i-1 have gone around the cluster.
         int i = 0, uc = 0, fc = 0;
         int first = 0;                // first tile of the current batch entry on this CTA
-        bool ok = true, fresh = true; // fresh: the next column-sum MMA starts a new accumulation
-        // column sums of tile j: D2_hf (+)= P~(j)^T W(j)
+        bool ok = true, fresh = true; // fresh: the next column-sum MMAs start a new accumulation
+        // column sums of tile j: D2_hf (+)= P~_hf(j)^T W_hf(j)
         auto colsum_mma = [&](int j, bool last) -> bool {
             const int slot = j & 1;
-            if (!wait_all(p_ready(slot, hf), (j >> 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
             if (!wait_all(w_ready(slot), (j >> 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
-            if (fresh && fc > 0) {   // the previous batch entry's sums have been read out
-                if (!wait_all(d2_empty(hf), (fc - 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
-            }
-            // P~ and W were written with ordinary stores by threads this warp has just
-            // synchronised with; the fence orders them before the tensor core's reads
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_after();
-            const uint64_t da = umma_desc_mn_sw128(p_smem + slot * P_BYTES + hf * P_TILE_BYTES);
-            const uint64_t db = umma_desc_k_sw32(w_smem + hf * W_TILE_BYTES);
-            if (elect_one_sync()) {
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)   // 16 query rows per instruction
-                    umma_f16(tmem_base + D2_COL + W_N * hf, da + (uint64_t)((ks * 2048) >> 4),
-                             db + (uint64_t)((ks * 512) >> 4), p.idesc_colsum, (fresh && ks == 0) ? 0u : 1u);
-                umma_commit(pw_free(slot, hf));
-                if (last) umma_commit(d2_full(hf));
+            for (int hf = 0; hf < 2; ++hf) {
+                if (!wait_all(p_ready(slot, hf), (j >> 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
+                if (fresh && fc > 0) {   // the previous sums have been read out
+                    if (!wait_all(d2_empty(hf), (fc - 1) & 1, FCS_STATUS_WAIT_MMA)) return false;
+                }
+                // P~ and W were written with ordinary stores by threads this warp has just
+                // synchronised with; the fence orders them before the tensor core's reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc_fence_after();
+                const uint64_t da = umma_desc_mn_sw128(p_smem + slot * P_BYTES + hf * P_TILE_BYTES);
+                const uint64_t db = umma_desc_k_sw32(w_smem + hf * W_TILE_BYTES);
+                if (elect_one_sync()) {
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)   // 16 query rows per instruction
+                        umma_f16(tmem_base + D2_COL + W_N * hf, da + (uint64_t)((ks * 2048) >> 4),
+                                 db + (uint64_t)((ks * 512) >> 4), p.idesc_colsum, (fresh && ks == 0) ? 0u : 1u);
+                    umma_commit(pw_free(slot, hf));
+                    if (last) umma_commit(d2_full(hf));
+                }
+                __syncwarp();
             }
-            __syncwarp();
             fresh = false;
             return true;
         };
-        const uint64_t dk = umma_desc_k_sw128(k_smem + hf * (K_BYTES / 2));
         for (int u = u0; ok && u < u1; ++u, ++uc) {
             if (!wait_all(k_full, uc & 1, FCS_STATUS_WAIT_MMA)) break;
             for (int t = 0; t < NQ; ++t, ++i) {
                 const int qs = i & 1;
                 if (!wait_all(q_full(qs), (i >> 1) & 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
-                if (!wait_all(s_empty(hf), (i & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
-                tc_fence_after();
                 const uint64_t dq = umma_desc_k_sw128(q_smem + qs * Q_BYTES);
-                if (elect_one_sync()) {
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)
-                        umma_f16(tmem_base + 128 * hf, dq + (uint64_t)((ks * 32) >> 4), dk + (uint64_t)((ks * 32) >> 4),
-                                 p.idesc_scores, ks > 0 ? 1u : 0u);
-                    umma_commit(s_full(hf));
-                    umma_commit(q_empty(qs));
-                    if (t + 1 == NQ) umma_commit(k_empty);
+                for (int hf = 0; hf < 2; ++hf) {
+                    if (!wait_all(s_empty(hf), (i & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t dk = umma_desc_k_sw128(k_smem + hf * (K_BYTES / 2));
+                    if (elect_one_sync()) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks)
+                            umma_f16(tmem_base + 128 * hf, dq + (uint64_t)((ks * 32) >> 4),
+                                     dk + (uint64_t)((ks * 32) >> 4), p.idesc_scores, ks > 0 ? 1u : 0u);
+                        umma_commit(s_full(hf));
+                        umma_commit(q_empty(qs));
+                        if (t + 1 == NQ) umma_commit(k_empty);
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
+                if (!ok) break;
                 if (i - first >= 2) {
                     if (!colsum_mma(i - 2, false)) { ok = false; break; }
                 }

@@ -58,7 +58,9 @@ def load_reference(root: str):
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of the reference project>")
+    root = sys.argv[1]
     naive_colsum = load_reference(root)
     arrays, manifest = {}, []
     for w in CASES:
