@@ -1000,6 +1000,16 @@ int fcs_colsum_causal(const void* q, const void* k, float* out, int H, int q_len
                             workspace, workspace_bytes, status, stream);
 }
 
+int fcs_colsum_causal_batched(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int q_len,
+                              int k_len, int D, int dtype, int64_t q_stride_b, int64_t q_stride_h,
+                              int64_t q_stride_s, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                              float scale, int k_past, int h_norm, void* workspace, size_t workspace_bytes,
+                              int* status, void* stream) {
+    return fcs::colsum_impl(q, k, out, out_ld, B, H, q_len, k_len, D, dtype, q_stride_b, q_stride_h, q_stride_s,
+                            k_stride_b, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm, workspace,
+                            workspace_bytes, status, stream);
+}
+
 int fcs_colsum_batched_static_scratch(const void* q, const void* k, float* out, int64_t out_ld, int B, int H,
                                       int S, int D, int dtype, int64_t q_stride_b, int64_t q_stride_h,
                                       int64_t q_stride_s, int64_t k_stride_b, int64_t k_stride_h,

@@ -208,6 +208,57 @@ def flash_colsum(
     return out
 
 
+def flash_colsum_causal(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    scale: Optional[float] = None,
+    *,
+    k_past: Optional[int] = None,
+    out_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """Causal column means for any batch size, with the launcher's ``K_past`` exposed.
+
+    What the reference defines but does not offer through ``flash_colsum``: its
+    operator refuses ``B > 1`` (flash_colsum/ops.py:79-82) and never passes
+    ``K_past`` (ops.py:89; kernel_causal.py:94-113), while ``naive_colsum`` computes
+    batched causal column means (baselines.py:45-63) including ``K_len < Q_len``
+    (baselines.py:58-62).
+
+    Args:
+        query: (B, H, Q_len, D), key: (B, H, K_len, D); fp16 or bf16, CUDA.
+        k_past: keys every query sees before its own position -- key j is visible to
+            query i iff ``j <= k_past + i``; default ``max(0, K_len - Q_len)``.
+    Returns:
+        (B, K_len), fp32 unless ``out_dtype`` says otherwise.
+    """
+    if query.ndim != 4 or key.ndim != 4:
+        raise ValueError(f"Expected 4D tensors, got query.ndim={query.ndim}, key.ndim={key.ndim}")
+    if query.device.type != 'cuda':
+        raise ValueError(f"Flash attention only supports CUDA tensors, got {query.device}")
+    B, H, Q_len, D = query.shape
+    if key.shape[0] != B or key.shape[1] != H or key.shape[3] != D:
+        raise ValueError(
+            f"Query and key must have same batch, heads and head_dim, got query: {query.shape}, key: {key.shape}")
+    if k_past is not None and k_past < 0:
+        raise ValueError(f"k_past must be non-negative, got {k_past}")
+    if scale is None:
+        scale = 1.0 / (D ** 0.5)
+    lib = _cabi.load()
+    Q, K, code = _prepare(query, key)
+    K_len = K.shape[2]
+    with torch.cuda.device(Q.device):
+        out = torch.empty((B, K_len), device=Q.device, dtype=torch.float32)
+        ws = _workspace(lib, Q.device, B, H, Q_len, K_len, D, True)
+        _check(lib.fcs_colsum_causal_batched(
+            Q.data_ptr(), K.data_ptr(), out.data_ptr(), K_len, B, H, Q_len, K_len, D, code,
+            Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
+            float(scale), -1 if k_past is None else int(k_past), 0, ws.data_ptr(), ws.numel(),
+            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+    if out_dtype is not None and out_dtype != out.dtype:
+        out = out.to(out_dtype)
+    return out
+
+
 _copy_streams: Dict[int, torch.cuda.Stream] = {}
 
 
@@ -265,4 +316,4 @@ def flash_colsum_host(
         return out.cpu()
 
 
-__all__ = ["flash_colsum", "flash_colsum_host", "device_status"]
+__all__ = ["flash_colsum", "flash_colsum_causal", "flash_colsum_host", "device_status"]

@@ -106,6 +106,23 @@ int fcs_colsum_causal(const void *q, const void *k, float *out,
                       void *workspace, size_t workspace_bytes, int *status, void *stream);
 
 /*
+ * Causal column mean of a batch: q [B, H, q_len, D], k [B, H, k_len, D], out (B, k_len)
+ * with row stride out_ld.  The reference's operator refuses causal calls with B > 1
+ * (flash_colsum/ops.py:79-82) although its naive_colsum defines them
+ * (flash_colsum/baselines.py:45-63, which this entry follows), and never passes the
+ * launcher's K_past (flash_colsum/kernel_causal.py:94-113; ops.py:89): here k_past >= 0
+ * sets the number of keys every query sees before its own position (key j is visible to
+ * query i iff j <= k_past + i, clipped to the key axis), k_past < 0 infers
+ * max(0, k_len - q_len) -- which also covers k_len < q_len (baselines.py:58-62).
+ */
+int fcs_colsum_causal_batched(const void *q, const void *k, float *out, int64_t out_ld,
+                              int B, int H, int q_len, int k_len, int D, int dtype,
+                              int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                              int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                              float scale, int k_past, int h_norm,
+                              void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+/*
  * Causal column mean ADDED into `out`: same arguments and arithmetic as
  * fcs_colsum_causal, but `out` is not cleared first.  It exists for head-sharded
  * calls that flush into one buffer: every shard passes the global head count as

@@ -79,8 +79,12 @@ def naive_colsum_torch(query: torch.Tensor, key: torch.Tensor,
 
 
 def naive_colsum_f64(query, key, scale: Optional[float] = None,
-                     is_causal: bool = False, cls_len: Optional[int] = None) -> np.ndarray:
-    """numpy float64 evaluation of the same definition, (b, h) at a time."""
+                     is_causal: bool = False, cls_len: Optional[int] = None,
+                     k_past: Optional[int] = None) -> np.ndarray:
+    """numpy float64 evaluation of the same definition, (b, h) at a time.
+
+    ``k_past`` replaces the inferred ``max(0, S_k - S_q)`` of the causal rule, as the
+    reference's causal launcher allows (flash_colsum/kernel_causal.py:94-113)."""
     q = np.asarray(query.detach().to(torch.float64).numpy() if isinstance(query, torch.Tensor) else query,
                    dtype=np.float64)
     k = np.asarray(key.detach().to(torch.float64).numpy() if isinstance(key, torch.Tensor) else key,
@@ -93,7 +97,7 @@ def naive_colsum_f64(query, key, scale: Optional[float] = None,
     out = np.zeros((B, S_k), dtype=np.float64)
     limit = None
     if is_causal:
-        limit = causal_k_past(S_q, S_k) + np.arange(S_q)[:, None]
+        limit = (causal_k_past(S_q, S_k) if k_past is None else int(k_past)) + np.arange(S_q)[:, None]
     kk = np.arange(S_k)[None, :]
     for b in range(B):
         for h in range(H):

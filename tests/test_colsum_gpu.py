@@ -306,3 +306,40 @@ def test_c5_long_context_properties_and_sampled_parity(fc):
         assert_parity(got4, want4, "c5 heads 8..11")
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def test_batched_causal_and_explicit_k_past(fc):
+    """Causal column means for B > 1, for fewer keys than queries, and with the launcher's
+    K_past given explicitly -- what the reference's naive_colsum and causal launcher define
+    but its operator does not offer."""
+    from oracle.naive_colsum import naive_colsum_f64
+    # batch of three, ragged sizes, both head dimensions
+    for (B, H, Sq, Sk, D, dtype) in [(3, 2, 200, 500, 64, "bf16"), (2, 3, 128, 1024, 128, "fp16")]:
+        w = Workload("bc", B, H, Sq, Sk, D, dtype, is_causal=True, seed=Sq + Sk)
+        q, k = make_inputs(w)
+        got = fc.flash_colsum_causal(q.cuda(), k.cuda()).cpu().numpy()
+        assert fc.device_status() == 0
+        assert got.shape == (B, Sk)
+        assert_parity(got, c_oracle.colsum_c(q, k, is_causal=True), f"batched causal {B}x{H}x{Sq}x{Sk}")
+    # the operator itself keeps the reference's refusal
+    with pytest.raises(ValueError, match="batch size 1"):
+        fc.flash_colsum(q.cuda(), k.cuda(), is_causal=True)
+    # fewer keys than queries: every query sees keys up to its own index
+    w = Workload("short_keys", 2, 2, 300, 120, 64, "fp16", is_causal=True, seed=4)
+    q, k = make_inputs(w)
+    got = fc.flash_colsum_causal(q.cuda(), k.cuda()).cpu().numpy()
+    assert_parity(got, c_oracle.colsum_c(q, k, is_causal=True), "k_len < q_len")
+    # explicit K_past, below / at / above the inferred value (300), and beyond the key axis
+    w = Workload("k_past", 1, 4, 100, 400, 128, "fp16", is_causal=True, seed=8)
+    q, k = make_inputs(w)
+    for k_past in (0, 50, 300, 350, 1000):
+        got = fc.flash_colsum_causal(q.cuda(), k.cuda(), k_past=k_past).cpu().numpy()
+        assert fc.device_status() == 0
+        assert_parity(got, naive_colsum_f64(q, k, is_causal=True, k_past=k_past), f"k_past {k_past}")
+        np.testing.assert_allclose(got.sum(axis=1), 1.0, rtol=1e-4)
+    default = fc.flash_colsum_causal(q.cuda(), k.cuda())
+    # same kernels, same masks; only the order of the atomic adds differs between calls
+    torch.testing.assert_close(default, fc.flash_colsum_causal(q.cuda(), k.cuda(), k_past=300), rtol=1e-5, atol=0)
+    torch.testing.assert_close(default, fc.flash_colsum(q.cuda(), k.cuda(), is_causal=True), rtol=1e-5, atol=0)
+    with pytest.raises(ValueError, match="non-negative"):
+        fc.flash_colsum_causal(q.cuda(), k.cuda(), k_past=-2)

@@ -102,3 +102,19 @@ def test_headline_workload_table():
     assert w.flop == pytest.approx(1.374e11, rel=1e-3)
     assert WORKLOADS["c5"].flop == pytest.approx(1.0995e12, rel=1e-3)
     assert WORKLOADS["c3"].rows_averaged == 1
+
+
+def test_f64_evaluation_takes_an_explicit_k_past():
+    """The causal launcher's K_past: the inferred value reproduces the default, a smaller one
+    hides keys (their column means are zero), rows still sum to one."""
+    from oracle.naive_colsum import naive_colsum_f64
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(2, 2, 6, 8, generator=g)
+    k = torch.randn(2, 2, 10, 8, generator=g)
+    default = naive_colsum_f64(q, k, is_causal=True)
+    np.testing.assert_array_equal(default, naive_colsum_f64(q, k, is_causal=True, k_past=4))
+    fewer = naive_colsum_f64(q, k, is_causal=True, k_past=1)
+    assert (fewer[:, 7:] == 0).all() and (fewer[:, :7] > 0).all()
+    np.testing.assert_allclose(fewer.sum(axis=1), 1.0, rtol=1e-12)
+    everything = naive_colsum_f64(q, k, is_causal=True, k_past=100)
+    np.testing.assert_allclose(everything, naive_colsum_f64(q, k, is_causal=False), rtol=1e-12)
