@@ -15,7 +15,7 @@ EXPORTED_SYMBOLS = (
     "fcs_set_profiling", "fcs_last_pass_ms", "fcs_plan_info",
     "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate",
     "fcs_set_single_pass", "fcs_single_pass_info", "fcs_single_pass_applies",
-    "fcs_colsum_causal_batched",
+    "fcs_colsum_causal_batched", "fcs_select_topk",
 )
 
 FCS_OK = 0
@@ -73,6 +73,8 @@ def load() -> ctypes.CDLL:
     lib.fcs_colsum_causal_batched.restype = _i
     lib.fcs_colsum_causal_batched.argtypes = [_p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64,
                                               _i64, _f, _i, _i, _p, _sz, _p, _p]
+    lib.fcs_select_topk.restype = _i
+    lib.fcs_select_topk.argtypes = [_p, _i64, _i, _i, _i, _p, _p, _p]
     lib.fcs_colsum_causal_accumulate.restype = _i
     lib.fcs_colsum_causal_accumulate.argtypes = lib.fcs_colsum_causal.argtypes
     lib.fcs_colsum_batched_static_scratch.restype = _i

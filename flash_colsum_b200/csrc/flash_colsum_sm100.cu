@@ -34,6 +34,7 @@
 #include "../../include/flash_colsum_b200.h"
 
 #include "colsum_single_pass.cuh"
+#include "select_topk.cuh"
 
 namespace fcs {
 
@@ -1008,6 +1009,20 @@ int fcs_colsum_causal_batched(const void* q, const void* k, float* out, int64_t 
     return fcs::colsum_impl(q, k, out, out_ld, B, H, q_len, k_len, D, dtype, q_stride_b, q_stride_h, q_stride_s,
                             k_stride_b, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm, workspace,
                             workspace_bytes, status, stream);
+}
+
+int fcs_select_topk(const float* colsum, int64_t ld, int B, int S, int k, int* indices, float* values,
+                    void* stream) {
+    fcs::g_err[0] = 0;
+    if (!colsum || !indices) return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "colsum and indices must not be NULL");
+    if (B <= 0 || S <= 0 || ld < S)
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "bad sizes (B=%d S=%d ld=%lld)", B, S, (long long)ld);
+    if (k <= 0 || k > S) return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "k must be in 1..S, got %d (S=%d)", k, S);
+    fcs::select_topk_kernel<<<B, fcs::TOPK_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        colsum, (long long)ld, S, k, indices, values);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fcs::fail(FCS_ERR_CUDA, "top-k selection launch failed: %s", cudaGetErrorString(e));
+    return FCS_OK;
 }
 
 int fcs_colsum_batched_static_scratch(const void* q, const void* k, float* out, int64_t out_ld, int B, int H,

@@ -259,6 +259,31 @@ def flash_colsum_causal(
     return out
 
 
+def topk_columns(colsum: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The ``k`` most-attended key positions of every row of a column-mean tensor.
+
+    ``colsum``: (B, S) fp32 CUDA tensor (what :func:`flash_colsum` returns).  Returns
+    ``(values, indices)``, both (B, k), positions ascending (the kept tokens stay in
+    order; ties go to the lower position), ``indices`` int32.  Runs on the current
+    stream without synchronising -- the pruning step of the reference's use case,
+    which the reference leaves to the caller.
+    """
+    if colsum.ndim != 2 or colsum.dtype != torch.float32 or colsum.device.type != "cuda":
+        raise ValueError("topk_columns takes a 2-D fp32 CUDA tensor")
+    B, S = colsum.shape
+    if not 1 <= k <= S:
+        raise ValueError(f"k must be in 1..{S}, got {k}")
+    if colsum.stride(1) != 1:
+        colsum = colsum.contiguous()
+    lib = _cabi.load()
+    with torch.cuda.device(colsum.device):
+        idx = torch.empty((B, k), dtype=torch.int32, device=colsum.device)
+        val = torch.empty((B, k), dtype=torch.float32, device=colsum.device)
+        _check(lib.fcs_select_topk(colsum.data_ptr(), colsum.stride(0), B, S, int(k), idx.data_ptr(),
+                                   val.data_ptr(), torch.cuda.current_stream(colsum.device).cuda_stream))
+    return val, idx
+
+
 _copy_streams: Dict[int, torch.cuda.Stream] = {}
 
 
@@ -316,4 +341,4 @@ def flash_colsum_host(
         return out.cpu()
 
 
-__all__ = ["flash_colsum", "flash_colsum_causal", "flash_colsum_host", "device_status"]
+__all__ = ["flash_colsum", "flash_colsum_causal", "flash_colsum_host", "topk_columns", "device_status"]

@@ -177,6 +177,18 @@ int fcs_colsum_batched_static_scratch(const void *q, const void *k, float *out, 
                                       int *status, void *stream);
 
 /*
+ * Token pruning on top of the column means (the operator's use in the reference's
+ * README: keep the most-attended visual tokens): for each of the B rows of `colsum`
+ * (fp32, S valid entries, row stride ld) the k positions with the largest value, written
+ * to indices[B][k] in ascending position order (ties go to the lower position) and, if
+ * `values` is not NULL, their values in the same order.  Runs on `stream`, after the
+ * call that produced `colsum`; no host synchronisation, no allocation.  No counterpart in
+ * the reference, which leaves the selection to its callers.
+ */
+int fcs_select_topk(const float *colsum, int64_t ld, int B, int S, int k,
+                    int *indices, float *values, void *stream);
+
+/*
  * Measurement aids.  No counterpart in the reference, which times whole calls
  * with a host clock (benchmarks/benchmark_colsum.py:42-56).
  *

@@ -111,6 +111,17 @@ def naive_colsum_f64(query, key, scale: Optional[float] = None,
     return out / float(H * rows)
 
 
+def topk_positions(colsum, k: int) -> np.ndarray:
+    """Per row, the k positions with the largest value, ascending; ties go to the lower
+    position.  The checker for the pruning step (plain sort)."""
+    v = np.asarray(colsum)
+    out = np.empty((v.shape[0], k), dtype=np.int64)
+    for b in range(v.shape[0]):
+        order = np.lexsort((np.arange(v.shape[1]), -v[b].astype(np.float64)))
+        out[b] = np.sort(order[:k])
+    return out
+
+
 def parity_errors(got, want):
     """(rel-L2, max-abs / max column mean) of fp32/fp64 arrays."""
     g = np.asarray(got, dtype=np.float64)

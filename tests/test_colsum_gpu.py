@@ -343,3 +343,34 @@ def test_batched_causal_and_explicit_k_past(fc):
     torch.testing.assert_close(default, fc.flash_colsum(q.cuda(), k.cuda(), is_causal=True), rtol=1e-5, atol=0)
     with pytest.raises(ValueError, match="non-negative"):
         fc.flash_colsum_causal(q.cuda(), k.cuda(), k_past=-2)
+
+
+def test_topk_columns_matches_a_plain_sort(fc):
+    """The pruning step: exact top-k positions per row, ascending, ties to the lower position."""
+    from oracle.naive_colsum import topk_positions
+    w = Workload("topk", 3, 4, 577, 577, 64, "fp16", seed=12)
+    q, k = make_inputs(w)
+    col = fc.flash_colsum(q.cuda(), k.cuda())
+    for kk in (1, 7, 144, 576, 577):
+        val, idx = fc.topk_columns(col, kk)
+        want = topk_positions(col.cpu().numpy(), kk)
+        np.testing.assert_array_equal(idx.cpu().numpy(), want)
+        np.testing.assert_array_equal(val.cpu().numpy(), np.take_along_axis(col.cpu().numpy(), want, axis=1))
+    # heavy ties, zeros, a long row, a padded row stride
+    g = torch.Generator().manual_seed(0)
+    x = torch.randint(0, 5, (2, 70000), generator=g).float() * 0.25
+    x[0, 100:200] = 0.0
+    xp = torch.zeros(2, 70016)
+    xp[:, :70000] = x
+    view = xp.cuda()[:, :70000]
+    for kk in (1, 1000, 35000, 70000):
+        val, idx = fc.topk_columns(view, kk)
+        np.testing.assert_array_equal(idx.cpu().numpy(), topk_positions(x.numpy(), kk))
+    # negative values order correctly too
+    y = torch.randn(4, 333, generator=g)
+    val, idx = fc.topk_columns(y.cuda(), 50)
+    np.testing.assert_array_equal(idx.cpu().numpy(), topk_positions(y.numpy(), 50))
+    with pytest.raises(ValueError):
+        fc.topk_columns(col, 0)
+    with pytest.raises(ValueError):
+        fc.topk_columns(col, 578)

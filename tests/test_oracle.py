@@ -118,3 +118,12 @@ def test_f64_evaluation_takes_an_explicit_k_past():
     np.testing.assert_allclose(fewer.sum(axis=1), 1.0, rtol=1e-12)
     everything = naive_colsum_f64(q, k, is_causal=True, k_past=100)
     np.testing.assert_allclose(everything, naive_colsum_f64(q, k, is_causal=False), rtol=1e-12)
+
+
+def test_topk_positions_checker():
+    from oracle.naive_colsum import topk_positions
+    v = np.array([[0.1, 0.5, 0.5, 0.0, 0.5, 0.2]])
+    np.testing.assert_array_equal(topk_positions(v, 1), [[1]])
+    np.testing.assert_array_equal(topk_positions(v, 2), [[1, 2]])
+    np.testing.assert_array_equal(topk_positions(v, 4), [[1, 2, 4, 5]])
+    np.testing.assert_array_equal(topk_positions(v, 6), [[0, 1, 2, 3, 4, 5]])
