@@ -205,6 +205,13 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             int a_cnt = 0, stage = 0, n = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // which streamed block every stage holds: when a (batch, head) has no more blocks
+            // than there are stages (short query axes in the column pass, short key axes in the
+            // statistics pass), the next item finds its blocks still in shared memory and the
+            // stage is handed to the MMA warp again without a copy
+            long long held[L::NS];
+#pragma unroll
+            for (int i = 0; i < L::NS; ++i) held[i] = -1;
             for (; ok && !it.done; it.next(p), ++a_cnt) {
                 const int ab = a_cnt & 1;
                 if (!wait_all(a_empty(ab), ((a_cnt >> 1) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
@@ -221,7 +228,14 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 const int bh = it.b * p.H + it.h;
                 for (int st = it.s0; st < it.s1; ++st, ++n) {
                     if (!wait_all(b_empty(stage), phase ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
-                    if (elect_one_sync()) {
+                    const long long block_id = ((long long)bh << 32) | (unsigned)st;
+                    bool reuse = false;
+#pragma unroll
+                    for (int i = 0; i < L::NS; ++i)
+                        if (i == stage) { reuse = held[i] == block_id; held[i] = block_id; }
+                    if (reuse) {
+                        if (elect_one_sync()) mbar_arrive(b_full(stage));
+                    } else if (elect_one_sync()) {
                         mbar_arrive_expect_tx(b_full(stage), L::B_STAGE_BYTES);
 #pragma unroll
                         for (int sl = 0; sl < L::SLABS; ++sl)

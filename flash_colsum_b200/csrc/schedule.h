@@ -35,6 +35,8 @@ struct Problem {
     int clear_out;      // the statistics pass zeroes `out` before the column pass adds into it
     int nsplit;         // key ranges per (b, h, query tile) in the statistics pass
     int kreg;           // leading key tiles that every query block contributes to
+    int col_interleave; // column pass: (b, h, key tile) chunks dealt round-robin instead of one contiguous range per CTA
+    int col_parts;      // ... each cut into this many query-block ranges
     long long stats_items;
     long long steps_per_batch;  // column pass: steps of one batch entry
     long long steps_total;
@@ -163,14 +165,42 @@ struct StatsItems {
     FCS_HD bool flush() const { return false; }
 };
 
-// Column pass: steps ordered (b, key tile, h, query block); a CTA takes one
-// contiguous range of them, cut into items at (b, key tile, h) boundaries.
-// `flush` marks the item after which the per-key accumulators are added into
-// the output (the CTA leaves the (b, key tile) group or ends).
+// Column pass, two ways of dealing out the steps.
+// Contiguous (short inputs): steps ordered (b, key tile, h, query block); a CTA takes
+// one contiguous range of them, cut into items at (b, key tile, h) boundaries --
+// perfect balance, and the per-key accumulators stay in registers across the heads
+// of a key tile.  `flush` marks the item after which they are added into the output
+// (the CTA leaves the (b, key tile) group or ends).
+// Interleaved (inputs far larger than the L2): chunks ordered (b, h, key tile, part of
+// the query blocks) are dealt round-robin, so that at any moment the CTAs work on
+// neighbouring key tiles of the same one or two heads and stream the same query blocks
+// -- with contiguous ranges every CTA is in a different place and the working set is
+// all heads at once (measured at B=1 H=16 S=32768: 4.3 GB read from DRAM for 134 MB of
+// inputs).  Every chunk flushes.
 struct ColsumItems {
     bool done, flush_;
     int b, h, kt, s0, s1, qlo;        // steps = query blocks s0..s1-1
     long long s, s_end;
+    long long chunk;                  // interleaved mode: current chunk and the stride to the next
+    int stride;
+
+    FCS_HD void load_chunk(const Problem& p) {
+        const long long total = (long long)p.B * p.H * p.NKC * p.col_parts;
+        for (; chunk < total; chunk += stride) {
+            const int part = (int)(chunk % p.col_parts);
+            long long item = chunk / p.col_parts;
+            kt = (int)(item % p.NKC);
+            item /= p.NKC;
+            h = (int)(item % p.H);
+            b = (int)(item / p.H);
+            qlo = colsum_first_q_block(p, kt);
+            const long long n = p.NQB - qlo;
+            s0 = qlo + (int)(n * part / p.col_parts);
+            s1 = qlo + (int)(n * (part + 1) / p.col_parts);
+            if (s1 > s0) { flush_ = true; return; }   // (a part of a short item may be empty)
+        }
+        done = true;
+    }
 
     FCS_HD void cut(const Problem& p) {
         long long n = p.NQB - s0;
@@ -180,11 +210,19 @@ struct ColsumItems {
         flush_ = ((s1 >= p.NQB) && (h + 1 >= p.H)) || end;
     }
     FCS_HD void init(const Problem& p, int cta, int grid) {
+        b = h = kt = s0 = s1 = qlo = 0;
+        flush_ = false;
+        s = s_end = 0;
+        chunk = cta;
+        stride = grid;
+        if (p.col_interleave) {
+            done = false;
+            load_chunk(p);
+            return;
+        }
         s = p.steps_total * cta / grid;
         s_end = p.steps_total * (cta + 1) / grid;
         done = (s >= s_end);
-        flush_ = false;
-        b = h = kt = s0 = s1 = qlo = 0;
         if (done) return;
         b = (int)(s / p.steps_per_batch);
         long long r = s % p.steps_per_batch;
@@ -212,6 +250,11 @@ struct ColsumItems {
         cut(p);
     }
     FCS_HD void next(const Problem& p) {
+        if (p.col_interleave) {
+            chunk += stride;
+            load_chunk(p);
+            return;
+        }
         s += s1 - s0;
         if (s >= s_end) { done = true; return; }
         if (h + 1 < p.H) {
@@ -237,7 +280,13 @@ template <> struct ItemsOf<MODE_COLSUM_EXT> { typedef ColsumItems type; };
 // ---------------------------------------------------------------------------
 // Planning (host): fills the shape-derived fields of `p`.
 // ---------------------------------------------------------------------------
-inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_past, int sms) {
+// Query rows (B * H * Sq) beyond which the column pass deals its work out interleaved:
+// the rows and their extension columns (up to 288 bytes each) then exceed what the L2
+// keeps for data that every SM reads.
+constexpr long long COL_INTERLEAVE_MIN_ROWS = 300000;
+
+inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_past, int sms,
+                 long long interleave_min_rows = COL_INTERLEAVE_MIN_ROWS) {
     p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk;
     p.NQ = ceil_div(Sq, TILE);
     p.NKT = ceil_div(Sk, TILE);
@@ -280,6 +329,13 @@ inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_pas
     for (int kt = p.kreg; kt < p.NKC; ++kt) steps += (long long)H * (p.NQB - colsum_first_q_block(p, kt));
     p.steps_per_batch = steps;
     p.steps_total = steps * B;
+    p.col_interleave = ((long long)B * H * Sq >= interleave_min_rows) ? 1 : 0;
+    // enough chunks for a balanced deal: about eight per CTA, by cutting the query blocks
+    // of an item into parts when the (b, h, key tile) items alone are too few
+    const long long items = (long long)B * H * p.NKC;
+    long long parts = items >= 8ll * sms ? 1 : (8ll * sms + items - 1) / items;
+    if (parts > p.NQB) parts = p.NQB;
+    p.col_parts = (int)parts;
 }
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }

@@ -25,14 +25,14 @@ static float dot(const float* a, const float* b, int D) {
 
 extern "C" int emulate_colsum(const float* q, const float* k, float* out, int B, int H, int Sq_full, int Sk,
                               int D, float scale, int causal, int k_past, int cls_n, int h_norm, int sms,
-                              int* nsplit_out, long long* steps_out) {
+                              long long interleave_min_rows, int* nsplit_out, long long* steps_out) {
     int Sq = Sq_full;
     if (!causal && cls_n > 0 && cls_n < Sq_full) Sq = cls_n;
     if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
     if (h_norm <= 0) h_norm = H;
     Problem p;
     memset(&p, 0, sizeof(p));
-    plan(p, B, H, Sq, Sk, causal, k_past, sms);
+    plan(p, B, H, Sq, Sk, causal, k_past, sms, interleave_min_rows);
     if (nsplit_out) *nsplit_out = p.nsplit;
     if (steps_out) *steps_out = p.steps_total;
     const float c = fabsf(scale) * 1.4426950408889634f;

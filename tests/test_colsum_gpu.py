@@ -249,6 +249,28 @@ def test_headline_workloads_full_size(fc, name, chunk):
         torch.backends.cuda.matmul.allow_tf32 = prev
 
 
+def test_long_inputs_take_the_interleaved_column_schedule(fc):
+    """More than 300 000 query rows: the column pass deals (b, h, key tile) chunks round-robin.
+    Non-causal with ragged sizes, and causal with more than one batch entry."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        w = Workload("long_rows", 2, 16, 10200, 10200, 64, "fp16", seed=21)
+        q, k = make_inputs(w)
+        qc, kc = q.cuda(), k.cuda()
+        got = run_gpu(fc, w, qc, kc)
+        assert_parity(got, _torch_fp32_reference(qc, kc, False, None, 2), w.name)
+        np.testing.assert_allclose(got.sum(axis=1), 1.0, atol=1e-3)
+        w = Workload("long_rows_causal", 2, 8, 20000, 20100, 128, "bf16", is_causal=True, seed=22)
+        q, k = make_inputs(w)
+        qc, kc = q.cuda(), k.cuda()
+        got = fc.flash_colsum_causal(qc, kc).cpu().numpy()
+        assert fc.device_status() == 0
+        assert_parity(got, _torch_fp32_reference(qc, kc, True, None, 1), w.name)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
 REFERENCE_TEST_SHAPES = [
     # the shapes of the reference's own GPU tests that are not already above at full size
     Workload("ref_non_batched", 1, 16, 8192, 8192, 64, "fp16", seed=0),                 # test_core.py:39-53

@@ -27,11 +27,15 @@ def emu():
     lib = ctypes.CDLL(LIB)
     lib.emulate_colsum.restype = ctypes.c_int
     lib.emulate_colsum.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 5 + [ctypes.c_float] + \
-        [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_void_p]
+        [ctypes.c_int] * 5 + [ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
     return lib
 
 
-def run(emu, q, k, scale=None, causal=False, k_past=-1, cls_len=None, h_norm=0, sms=148):
+INTERLEAVE_DEFAULT = 300000   # query rows from which the column pass deals its chunks round-robin
+
+
+def run(emu, q, k, scale=None, causal=False, k_past=-1, cls_len=None, h_norm=0, sms=148,
+        interleave_min_rows=INTERLEAVE_DEFAULT):
     B, H, Sq, D = q.shape
     Sk = k.shape[2]
     if scale is None:
@@ -42,7 +46,7 @@ def run(emu, q, k, scale=None, causal=False, k_past=-1, cls_len=None, h_norm=0, 
     qc, kc = q.contiguous(), k.contiguous()
     rc = emu.emulate_colsum(qc.data_ptr(), kc.data_ptr(), out.ctypes.data, B, H, Sq, Sk, D, scale,
                             int(causal), k_past, -1 if cls_len is None else cls_len, h_norm, sms,
-                            ctypes.addressof(nsplit), ctypes.addressof(steps))
+                            interleave_min_rows, ctypes.addressof(nsplit), ctypes.addressof(steps))
     assert rc == 0, f"schedule walk failed with code {rc}"
     return out, nsplit.value, steps.value
 
@@ -76,6 +80,30 @@ def test_schedule_reproduces_the_checker(emu, B, H, Sq, Sk, D, causal, cls, sms)
     want = c_oracle.colsum_c(q, k, is_causal=causal, cls_len=cls)
     rel, mx = parity_errors(got, want)
     assert rel < 2e-5 and mx < 2e-5, (rel, mx, nsplit, steps)
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk,D,causal,cls,sms", CASES)
+def test_interleaved_column_schedule_reproduces_the_checker(emu, B, H, Sq, Sk, D, causal, cls, sms):
+    """The same cases with the column pass dealing (b, h, key tile) chunks round-robin, the
+    distribution long inputs get."""
+    g = torch.Generator().manual_seed(B * 1000 + Sq + Sk)
+    q = torch.randn(B, H, Sq, D, generator=g)
+    k = torch.randn(B, H, Sk, D, generator=g) * 1.5
+    got, nsplit, steps = run(emu, q, k, causal=causal, cls_len=cls, sms=sms, interleave_min_rows=0)
+    want = c_oracle.colsum_c(q, k, is_causal=causal, cls_len=cls)
+    rel, mx = parity_errors(got, want)
+    assert rel < 2e-5 and mx < 2e-5, (rel, mx, nsplit, steps)
+
+
+def test_interleaved_schedule_with_many_query_blocks(emu):
+    """Few (b, h, key tile) items and many query blocks: the items are cut into parts."""
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(1, 1, 2100, 4, generator=g)
+    k = torch.randn(1, 1, 300, 4, generator=g)
+    for causal in (False, True):
+        got, _, _ = run(emu, q, k, causal=causal, sms=148, interleave_min_rows=0)
+        want = c_oracle.colsum_c(q, k, is_causal=causal)
+        assert parity_errors(got, want)[0] < 2e-5
 
 
 def test_key_range_split_is_used_when_items_are_few(emu):
