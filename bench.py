@@ -36,6 +36,7 @@ from flash_colsum_b200.inputs import WORKLOADS, Workload, make_inputs  # noqa: E
 
 METRIC = "colsum_effective_tflops"
 UNIT = "TFLOP/s"
+WORKLOAD_LABEL = "c2: non-causal B=8 H=16 S=2048 D=64 fp16 per GPU"
 L2_FLUSH_BYTES = 256 << 20
 
 
@@ -190,7 +191,8 @@ def run_reference_arm(args):
         "steps": len(times), "warmup": args.warmup, "ms_per_step": mean_s * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
         "data": "synthetic",
-        "config": {"workload": "c2: non-causal B=8 H=16 S=2048 D=64", "step": "one batch entry (B=1) per step",
+        "config": {"workload": WORKLOAD_LABEL, "flop_count": "4*B*H*Sq*Sk*D (two passes)",
+                   "step": "one batch entry (B=1) of the workload per step, fp32 on the host cores",
                    "l2": "host run"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                          "sample": "1 of 8 batch entries per step, CPU restatement of naive_colsum in fp32"},
@@ -419,7 +421,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
-            "config": {"workload": "c2: non-causal B=8 H=16 S=2048 D=64 fp16 per GPU",
+            "config": {"workload": WORKLOAD_LABEL,
                        "global_batch": w.B * world,
                        "parallelism": "single GPU" if world == 1 else f"batch sharded over {world} GPUs, no collective",
                        "flop_count": "4*B*H*Sq*Sk*D (two passes)",
