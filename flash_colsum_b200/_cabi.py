@@ -85,7 +85,7 @@ def load() -> ctypes.CDLL:
     lib.fcs_set_single_pass.restype = _i
     lib.fcs_set_single_pass.argtypes = [_i]
     lib.fcs_single_pass_applies.restype = _i
-    lib.fcs_single_pass_applies.argtypes = [_i, _i, _i, _i, _i]
+    lib.fcs_single_pass_applies.argtypes = [_i, _i, _i, _i, _i, _i]
     lib.fcs_single_pass_info.restype = _i
     lib.fcs_single_pass_info.argtypes = [_i, ctypes.POINTER(_i), ctypes.POINTER(_i)]
     lib.fcs_last_pass_ms.restype = _i
@@ -104,9 +104,11 @@ def set_profiling(enabled: bool) -> None:
     load().fcs_set_profiling(int(bool(enabled)))
 
 
-def single_pass_applies(B: int, H: int, sk: int, D: int = 64, is_causal: bool = False) -> bool:
-    """Whether a call with these sizes takes the single-pass kernel under the current mode."""
-    return bool(load().fcs_single_pass_applies(B, H, sk, D, int(is_causal)))
+def single_pass_applies(B: int, H: int, sk: int, D: int = 64, is_causal: bool = False,
+                        sq_rows: Optional[int] = None) -> bool:
+    """Whether a call with these sizes takes the single-pass kernel under the current mode
+    (``sq_rows``: query rows that enter the mean, default ``sk``)."""
+    return bool(load().fcs_single_pass_applies(B, H, sk if sq_rows is None else sq_rows, sk, D, int(is_causal)))
 
 
 def single_pass_info(sk: int):

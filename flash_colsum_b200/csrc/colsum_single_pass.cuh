@@ -28,6 +28,7 @@
 #pragma once
 
 #include "colsum_math.cuh"
+#include "schedule.h"
 #include "sm100_ptx.cuh"
 
 namespace fcs {
@@ -280,9 +281,13 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const uint32_t rank = cluster_ctarank();
     const int CL = p.CL;
     const int cluster_id = blockIdx.x / CL;
-    const int u0 = (int)((long long)p.units * cluster_id / p.clusters);
-    const int u1 = (int)((long long)p.units * (cluster_id + 1) / p.clusters);
     const int NQ = p.NQ;
+    // this cluster's share of the (batch, head, query tile) list
+    TileRange range;
+    range.init(p.units, NQ, cluster_id, p.clusters);
+    const int u0 = range.u0, u1 = range.u1;
+    auto t_lo = [&](int u) { return range.t_lo(u); };
+    auto t_hi = [&](int u) { return range.t_hi(u); };
 
     if (threadIdx.x == 0) {
         mbar_init(k_full, 1); mbar_init(k_empty, 2);
@@ -328,9 +333,7 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     // and every `flush_units` pairs: the tensor core truncates when it adds into its fp32
     // accumulator (about half a unit in the last place lost per accumulation), and the bound
     // keeps that bias below ~1e-4 of a column sum however many heads there are.
-    auto last_of_batch = [&](int u) {
-        return (u + 1 == u1) || ((u + 1) / p.H != u / p.H) || ((u + 1 - u0) % p.flush_units == 0);
-    };
+    auto last_of_batch = [&](int u) { return range.flush_after(u, p.H, p.flush_units); };
 
     if (warp == PRODUCER_WARP) {
         // ------------------------------------------------ TMA producer
@@ -344,7 +347,7 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 tma_load_4d(k_smem, &tm_k, k_full, 0, 256 * (int)rank, h, b);
             }
             __syncwarp();
-            for (int t = 0; t < NQ; ++t, ++i) {
+            for (int t = t_lo(u); t < t_hi(u); ++t, ++i) {
                 const int qs = i & 1;
                 if (!wait_all(q_empty(qs), ((i >> 1) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
                 if (elect_one_sync()) {
@@ -357,10 +360,10 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     } else if (warp >= XCHG_WARP) {
         // ------------------------------------------------ statistics exchange and weights
         const int xw = warp - XCHG_WARP;
-        const int total = (u1 - u0) * NQ;
+        const int total = range.tiles();
         for (int i = 0; i < total; ++i) {
             const int slot = i & 1;
-            const int t = i % NQ;
+            const int t = range.tile_of(i);
             // (1) the four groups' (max, sum) of this CTA -> one pair per row, posted to every CTA
             if (!wait_all(stats_bar(slot), (i >> 1) & 1, FCS_STATUS_WAIT_CONSUMER)) break;
             float mg[XCHG_ROWS_PER_LANE][CONSUMER_GROUPS];
@@ -461,7 +464,8 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         };
         for (int u = u0; ok && u < u1; ++u, ++uc) {
             if (!wait_all(k_full, uc & 1, FCS_STATUS_WAIT_MMA)) break;
-            for (int t = 0; t < NQ; ++t, ++i) {
+            const int t_end = t_hi(u);
+            for (int t = t_lo(u); t < t_end; ++t, ++i) {
                 const int qs = i & 1;
                 if (!wait_all(q_full(qs), (i >> 1) & 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
                 const uint64_t dq = umma_desc_k_sw128(q_smem + qs * Q_BYTES);
@@ -477,7 +481,7 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                                      dk + (uint64_t)((ks * 32) >> 4), p.idesc_scores, ks > 0 ? 1u : 0u);
                         umma_commit(s_full(hf));
                         umma_commit(q_empty(qs));
-                        if (t + 1 == NQ) umma_commit(k_empty);
+                        if (t + 1 == t_end) umma_commit(k_empty);
                     }
                     __syncwarp();
                 }
@@ -513,7 +517,7 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         int i = 0, fc = 0;
         bool ok = true;
         for (int u = u0; ok && u < u1; ++u) {
-            for (int t = 0; t < NQ; ++t, ++i) {
+            for (int t = t_lo(u); t < t_hi(u); ++t, ++i) {
                 const int slot = i & 1;
                 // ---- scores of this thread's row and group
                 ok = mbar_wait(s_full(hf), i & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);

@@ -665,9 +665,9 @@ static int launch_small_q(const void* q, const void* k, float* out, int64_t out_
 }
 
 // Short key axes (non-causal, head dimension 64, S_k <= 2048): the single-pass
-// cluster kernel.  g_single_pass: 0 = where it is the faster of the two (measured:
-// up to 1024 keys, when the keys fill their 256-key slices well and there are enough
-// (batch, head) pairs to occupy the device), 1 = never, 2 = whenever the shape allows.
+// cluster kernel.  g_single_pass: 0 = where it is the faster of the two (measured: keys
+// that fill their 256-key slices to 85 % or more, up to 1024 of them, or up to 2048 when
+// the call is small), 1 = never, 2 = whenever the shape allows.
 static int g_single_pass = 0;
 
 static int single_pass_cluster_size(int Sk) {
@@ -677,13 +677,16 @@ static int single_pass_cluster_size(int Sk) {
     return cl;
 }
 
-static bool single_pass_applies(int B, int H, int Sk, int D, int causal) {
+static bool single_pass_applies(int B, int H, int Sq, int Sk, int D, int causal) {
     if (g_single_pass == 1 || causal || D != 64 || Sk > 256 * sp::MAX_CL) return false;
     if (g_single_pass == 2) return true;
     const int cl = single_pass_cluster_size(Sk);
-    if (cl > 4) return false;                                  // 2048 keys: the two passes are faster
     if ((long long)Sk * 100 < (long long)cl * 256 * 85) return false;   // too much padding
-    return (long long)B * H * cl >= 32;
+    if (cl <= 4) return true;
+    // 2048 keys: only 15 eight-CTA clusters fit (120 of 148 SMs), so the two passes win on
+    // large calls; on small ones their fixed costs (two launches, partial waves) lose
+    const long long tiles = (long long)B * H * ((Sq + TILE - 1) / TILE);
+    return tiles <= 512;
 }
 
 // Clusters of `cl` CTAs that can be resident at once (0 if the query fails).
@@ -732,7 +735,11 @@ static int launch_single_pass(const CUtensorMap& tq, const CUtensorMap& tk, floa
     sp_.NQ = (Sq + TILE - 1) / TILE;
     sp_.CL = single_pass_cluster_size(Sk);
     sp_.units = B * H;
-    sp_.clusters = sp_.units < max_clusters ? sp_.units : max_clusters;
+    // the (batch, head, query tile) list is cut evenly over the clusters, through pairs if need be
+    {
+        const long long tiles = (long long)sp_.units * sp_.NQ;
+        sp_.clusters = tiles < max_clusters ? (int)tiles : max_clusters;
+    }
     // at most ~1024 accumulations (16 query rows each) per flush
     sp_.flush_units = 128 / sp_.NQ > 1 ? 128 / sp_.NQ : 1;
     sp_.c = fabsf(scale) * 1.4426950408889634f;
@@ -840,7 +847,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if ((rc = make_tensor_map(&tq_b, q, dtype, B, H, Sq, D, qsb, qsh, qss, BLOCK)) != FCS_OK) return rc;
     if ((rc = make_tensor_map(&tk_a, k, dtype, B, H, Sk, D, ksb, ksh, kss, TILE)) != FCS_OK) return rc;
     if ((rc = make_tensor_map(&tk_b, k, dtype, B, H, Sk, D, ksb, ksh, kss, BLOCK)) != FCS_OK) return rc;
-    if (single_pass_applies(B, H, Sk, D, causal)) {
+    if (single_pass_applies(B, H, Sq, Sk, D, causal)) {
         const int max_clusters = single_pass_max_clusters(single_pass_cluster_size(Sk));
         if (max_clusters > 0) {
             // reported as a call whose statistics and merge passes take no time
@@ -934,9 +941,9 @@ int fcs_set_single_pass(int mode) {
     return FCS_OK;
 }
 
-int fcs_single_pass_applies(int B, int H, int Sk, int D, int is_causal) {
-    if (B <= 0 || H <= 0 || Sk <= 0) return 0;
-    return fcs::single_pass_applies(B, H, Sk, D, is_causal ? 1 : 0) ? 1 : 0;
+int fcs_single_pass_applies(int B, int H, int sq_rows, int Sk, int D, int is_causal) {
+    if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0) return 0;
+    return fcs::single_pass_applies(B, H, sq_rows, Sk, D, is_causal ? 1 : 0) ? 1 : 0;
 }
 
 int fcs_single_pass_info(int Sk, int* cluster_size, int* max_clusters) {

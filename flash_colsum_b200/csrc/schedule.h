@@ -338,6 +338,37 @@ inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_pas
     p.col_parts = (int)parts;
 }
 
+// ---------------------------------------------------------------------------
+// Single-pass kernel: a cluster's share of the list of (batch, head, query tile)
+// triples, ordered with the query tile innermost.  The list is cut evenly over the
+// clusters, so a share starts and ends anywhere inside a (batch, head) pair.
+// ---------------------------------------------------------------------------
+struct TileRange {
+    long long g0, g1;   // tiles [g0, g1) of the list
+    int u0, u1;         // the (batch, head) pairs they touch: u0 .. u1-1
+    int NQ;
+
+    FCS_HD void init(long long units, int nq, int cluster, int clusters) {
+        NQ = nq;
+        const long long all = units * nq;
+        g0 = all * cluster / clusters;
+        g1 = all * (cluster + 1) / clusters;
+        u0 = (int)(g0 / nq);
+        u1 = (int)((g1 + nq - 1) / nq);
+    }
+    FCS_HD int tiles() const { return (int)(g1 - g0); }
+    // query tiles [t_lo, t_hi) of pair u belong to the share
+    FCS_HD int t_lo(int u) const { return u == u0 ? (int)(g0 - (long long)u0 * NQ) : 0; }
+    FCS_HD int t_hi(int u) const { return u + 1 == u1 ? (int)(g1 - (long long)(u1 - 1) * NQ) : NQ; }
+    // query tile of the i-th tile of the share
+    FCS_HD int tile_of(int i) const { return (int)((g0 + i) % NQ); }
+    // The column sums are written out after pair u: at the end of the share, of a batch entry
+    // (H pairs), and every `flush_units` pairs at the latest.
+    FCS_HD bool flush_after(int u, int H, int flush_units) const {
+        return (u + 1 == u1) || ((u + 1) / H != u / H) || ((u + 1 - u0) % flush_units == 0);
+    }
+};
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // Scratch layout: [neg_lse | ext | part]; returns the total and the offsets.

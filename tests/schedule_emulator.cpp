@@ -194,3 +194,33 @@ extern "C" int emulate_colsum(const float* q, const float* k, float* out, int B,
     if (walked != p.steps_total) return -24;
     return 0;
 }
+
+// Walk the single-pass kernel's work split: every (pair, query tile) must be visited exactly
+// once, in list order, by the clusters in turn; the tile counter of a share must agree with
+// `tile_of`; flush groups must not span batch entries nor exceed `flush_units` pairs.
+extern "C" int check_tile_ranges(long long units, int NQ, int H, int clusters, int flush_units) {
+    long long expect = 0;
+    for (int c = 0; c < clusters; ++c) {
+        TileRange r;
+        r.init(units, NQ, c, clusters);
+        if (r.g0 != expect) return -1;
+        int i = 0, group_first = r.u0;
+        for (int u = r.u0; u < r.u1; ++u) {
+            if (r.t_lo(u) >= r.t_hi(u)) return -2;               // a touched pair without tiles
+            for (int t = r.t_lo(u); t < r.t_hi(u); ++t, ++i) {
+                if ((long long)u * NQ + t != expect) return -3;  // out of order, skipped or repeated
+                if (r.tile_of(i) != t) return -4;
+                ++expect;
+            }
+            if (r.flush_after(u, H, flush_units)) {
+                if (group_first / H != u / H) return -5;          // a group spans two batch entries
+                if (u - group_first + 1 > flush_units) return -6;
+                group_first = u + 1;
+            } else if (u + 1 == r.u1) {
+                return -7;                                        // the share ends without a flush
+            }
+        }
+        if (i != r.tiles() || expect != r.g1) return -8;
+    }
+    return expect == units * NQ ? 0 : -9;
+}

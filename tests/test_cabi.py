@@ -77,9 +77,11 @@ def test_kernel_choice_rule_is_host_arithmetic():
         assert _cabi.single_pass_applies(8, 16, 1024)
         assert _cabi.single_pass_applies(8, 16, 900)           # 88 % of four slices
         assert not _cabi.single_pass_applies(8, 16, 577)       # 56 % of four slices
-        assert not _cabi.single_pass_applies(8, 16, 2048)      # eight-CTA clusters lose to two passes
+        assert not _cabi.single_pass_applies(8, 16, 2048)      # eight-CTA clusters lose to two passes ...
+        assert _cabi.single_pass_applies(1, 16, 2048)          # ... except on small calls
+        assert not _cabi.single_pass_applies(4, 16, 1280)      # 62 % of eight slices
         assert not _cabi.single_pass_applies(8, 16, 4096)      # does not fit a cluster
-        assert not _cabi.single_pass_applies(1, 2, 512)        # too few pairs to occupy the device
+        assert _cabi.single_pass_applies(1, 2, 512)            # small calls are cut at tile granularity
         assert not _cabi.single_pass_applies(8, 16, 512, D=128)
         assert not _cabi.single_pass_applies(8, 16, 512, is_causal=True)
         _cabi.set_single_pass(_cabi.SINGLE_PASS_ALWAYS)

@@ -25,6 +25,8 @@ def emu():
             or os.path.getmtime(LIB) < max(os.path.getmtime(SRC), os.path.getmtime(HDR))):
         subprocess.run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-o", LIB, SRC], check=True)
     lib = ctypes.CDLL(LIB)
+    lib.check_tile_ranges.restype = ctypes.c_int
+    lib.check_tile_ranges.argtypes = [ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
     lib.emulate_colsum.restype = ctypes.c_int
     lib.emulate_colsum.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 5 + [ctypes.c_float] + \
         [ctypes.c_int] * 5 + [ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
@@ -132,3 +134,17 @@ def test_explicit_k_past_and_negative_scale_and_head_norm(emu):
     got4, _, _ = run(emu, q, k[:, :, :50], h_norm=4)
     got2, _, _ = run(emu, q, k[:, :, :50])
     np.testing.assert_allclose(got4 * 2, got2, rtol=1e-5)
+
+
+@pytest.mark.parametrize("units,NQ,H,clusters,flush_units", [
+    (128, 16, 16, 15, 8),      # the headline shape on eight-CTA clusters: shares cut through pairs
+    (512, 8, 16, 33, 16),
+    (4, 4, 2, 16, 32),         # as many clusters as tiles
+    (1, 1, 1, 1, 128),
+    (7, 3, 7, 5, 42),
+    (2048, 2, 16, 74, 64),
+    (128, 4, 64, 148, 32),     # many heads: intermediate flushes inside a batch entry
+    (6, 5, 3, 30, 25),
+])
+def test_single_pass_work_split_covers_every_tile_once(emu, units, NQ, H, clusters, flush_units):
+    assert emu.check_tile_ranges(units, NQ, H, clusters, flush_units) == 0

@@ -120,7 +120,7 @@ def test_default_choice_by_shape(fc, kernel_choice):
     from flash_colsum_b200 import _cabi
     kernel_choice(0)
     assert _cabi.single_pass_applies(8, 16, 512) and _cabi.single_pass_applies(8, 16, 1024)
-    assert not _cabi.single_pass_applies(8, 16, 2048)
+    assert not _cabi.single_pass_applies(8, 16, 2048) and _cabi.single_pass_applies(1, 16, 2048)
     _cabi.set_profiling(True)
     try:
         def pass_ms(B, H, S):
