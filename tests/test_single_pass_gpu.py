@@ -114,6 +114,30 @@ def test_single_pass_strided_inputs_and_repeats(fc, kernel_choice):
         assert_parity(o.cpu().numpy(), want, "strided")
 
 
+def test_single_pass_call_replays_from_a_cuda_graph(fc, kernel_choice):
+    """The cluster launch (output clear + one kernel) neither synchronises nor allocates."""
+    w = Workload("sp_graph", 2, 4, 512, 512, 64, "fp16", seed=31)
+    q, k = (t.cuda() for t in make_inputs(w))
+    kernel_choice(2)
+    fc.flash_colsum(q, k)                      # first call outside capture (one-time set-up)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fc.flash_colsum(q, k)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = fc.flash_colsum(q, k)
+    want = c_oracle.colsum_c(q.cpu(), k.cpu())
+    for _ in range(3):
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert_parity(out.cpu().numpy(), want, "graph replay")
+    assert fc.device_status() == 0
+
+
 def test_default_choice_by_shape(fc, kernel_choice):
     """The default takes the single pass for well-filled short key axes; such a call runs one
     kernel, so it reports (next to) no statistics-pass time."""
