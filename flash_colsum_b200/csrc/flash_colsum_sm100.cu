@@ -188,6 +188,10 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above touched only this CTA's shared and tensor memory; from here on the
+    // results of the kernel before this one in the stream are read
+    grid_dependency_wait();
+    grid_launch_dependents();
 
     // The producer and MMA warps run their loops with all 32 lanes converged (so
     // that addresses, descriptors and counters stay in uniform registers) and
@@ -460,6 +464,8 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 // Combine the key-range partials of the statistics pass into the per-row value
 // the column pass subtracts.
 __global__ void merge_stats_kernel(const Problem p) {
+    grid_dependency_wait();
+    grid_launch_dependents();
     const long long rows = (long long)p.NQ * TILE;
     const long long n = (long long)p.B * p.H * rows;
     const float2* part = reinterpret_cast<const float2*>(p.part);
@@ -588,7 +594,7 @@ static int make_ext_tensor_map(CUtensorMap* m, const void* base, int dtype, long
 
 template <int D, int MODE>
 static cudaError_t launch_stream(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& text,
-                                 const Problem& p, int grid, cudaStream_t stream) {
+                                 const Problem& p, int grid, cudaStream_t stream, bool after_own_kernel) {
     using LayoutT = Layout<D, MODE>;
     static bool configured[64] = {false};
     int dev = 0;
@@ -600,8 +606,20 @@ static cudaError_t launch_stream(const CUtensorMap& ta, const CUtensorMap& tb, c
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    kern<<<grid, THREADS, LayoutT::DYN_BYTES, stream>>>(ta, tb, text, p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = LayoutT::DYN_BYTES;
+    cfg.stream = stream;
+    // a pass that follows another kernel of the same call starts its set-up (barriers, tensor
+    // memory) while that kernel drains; it waits for it inside (grid_dependency_wait)
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = after_own_kernel ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, text, p);
 }
 
 static int check_operand(const char* name, const void* ptr, int64_t sb, int64_t sh, int64_t ss) {
@@ -870,25 +888,34 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     PassTimers* tm = g_profiling ? timers_for_current_device() : nullptr;
     if (tm) { tm->recorded = false; cudaEventRecord(tm->ev[0], stream); }
     cudaError_t e;
-    e = (D == 64) ? launch_stream<64, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream)
-                  : launch_stream<128, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream);
+    e = (D == 64) ? launch_stream<64, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream, false)
+                  : launch_stream<128, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream, false);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics pass launch failed: %s", cudaGetErrorString(e));
     if (tm) cudaEventRecord(tm->ev[1], stream);
     if (p.nsplit > 1) {
         const long long n = (long long)B * H * p.NQ * TILE;
         int blocks = (int)((n + 255) / 256);
         if (blocks > sms * 8) blocks = sms * 8;
-        merge_stats_kernel<<<blocks, 256, 0, stream>>>(p);
-        e = cudaGetLastError();
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)blocks);
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = tm ? 0 : 1;   // (event records between the kernels when timing is on)
+        e = cudaLaunchKernelEx(&cfg, merge_stats_kernel, p);
         if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics merge launch failed: %s", cudaGetErrorString(e));
     }
     if (tm) cudaEventRecord(tm->ev[2], stream);
     if (use_ext)
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream)
-                      : launch_stream<128, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream);
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, !tm)
+                      : launch_stream<128, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, !tm);
     else
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream)
-                      : launch_stream<128, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream);
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream, !tm)
+                      : launch_stream<128, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream, !tm);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "column pass launch failed: %s", cudaGetErrorString(e));
     if (tm) { cudaEventRecord(tm->ev[3], stream); tm->recorded = true; }
     return FCS_OK;

@@ -37,6 +37,18 @@ __device__ __forceinline__ bool elect_one_sync() {
     return pred != 0;
 }
 
+// ---------------------------------------------------------------- dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while the
+// kernel before it in the stream is still running; `grid_dependency_wait` holds it until
+// that kernel has completed and its memory is visible (a no-op for an ordinary launch), and
+// `grid_launch_dependents` tells the scheduler that the next kernel may start filling SMs.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
