@@ -20,7 +20,10 @@
 // shared-memory layout serves as A (128 resident rows) or B (256 streamed rows)
 // of the MMA; one step is a 128 x 256 x D MMA into one of two accumulator
 // buffers of 256 tensor-memory columns.  Calls with at most four query rows
-// take the matrix-vector kernel of colsum_small_q.cuh instead.
+// take the matrix-vector kernel of colsum_small_q.cuh instead; short non-causal
+// key axes at head dimension 64 take the single-pass cluster kernel of
+// colsum_single_pass.cuh; select_topk.cuh holds the pruning step that callers
+// run on the result.
 #include "sm100_ptx.cuh"
 #include "schedule.h"
 #include "colsum_small_q.cuh"
