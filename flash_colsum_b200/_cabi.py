@@ -16,6 +16,7 @@ EXPORTED_SYMBOLS = (
     "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate",
     "fcs_set_single_pass", "fcs_single_pass_info", "fcs_single_pass_applies",
     "fcs_colsum_causal_batched", "fcs_select_topk",
+    "fcs_statistics_rows", "fcs_colsum_statistics", "fcs_colsum_columns",
 )
 
 FCS_OK = 0
@@ -73,6 +74,14 @@ def load() -> ctypes.CDLL:
     lib.fcs_colsum_causal_batched.restype = _i
     lib.fcs_colsum_causal_batched.argtypes = [_p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64,
                                               _i64, _f, _i, _i, _p, _sz, _p, _p]
+    lib.fcs_statistics_rows.restype = _sz
+    lib.fcs_statistics_rows.argtypes = [_i]
+    lib.fcs_colsum_statistics.restype = _i
+    lib.fcs_colsum_statistics.argtypes = [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,
+                                          _f, _i64, _i, _p, _sz, _p, _p]
+    lib.fcs_colsum_columns.restype = _i
+    lib.fcs_colsum_columns.argtypes = [_p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64,
+                                       _i64, _f, _p, _sz, _p, _p]
     lib.fcs_select_topk.restype = _i
     lib.fcs_select_topk.argtypes = [_p, _i64, _i, _i, _i, _p, _p, _p]
     lib.fcs_colsum_causal_accumulate.restype = _i

@@ -792,20 +792,47 @@ static int launch_single_pass(const CUtensorMap& tq, const CUtensorMap& tk, floa
     return FCS_OK;
 }
 
+enum : int { PASSES_BOTH = 0, PASSES_STATS = 1, PASSES_COLUMNS = 2 };
+
+// -(log-sum-exp) per query row -> the 16 extension columns the column pass contracts with.
+__global__ void ext_from_lse_kernel(const Problem p) {
+    const long long n = (long long)p.B * p.H * p.lse_rows;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+         idx += (long long)gridDim.x * blockDim.x) {
+        uint4 e0, e1;
+        make_ext_row(p.neg_lse[idx], p.inv_c, p.ext_bf16 != 0, e0, e1);
+        uint4* er = reinterpret_cast<uint4*>(p.ext) + idx * 2;
+        er[0] = e0;
+        er[1] = e1;
+    }
+}
+
 // The one implementation behind the three entry points.
 static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int Sq_full,
                        int Sk, int D, int dtype, int64_t qsb, int64_t qsh, int64_t qss, int64_t ksb,
                        int64_t ksh, int64_t kss, float scale, int causal, int k_past, int cls_n, int h_norm,
                        void* workspace, size_t workspace_bytes, int* status, void* stream_v,
-                       bool clear_out = true) {
+                       bool clear_out = true, int passes = PASSES_BOTH, float* shared_lse = nullptr,
+                       long long norm_rows = 0) {
+    // passes: both, or one of the two for work split over devices (non-causal only) --
+    // PASSES_STATS writes -(log-sum-exp + log2(h_norm * norm_rows)) of the given query rows to
+    // `shared_lse`; PASSES_COLUMNS takes that vector for ALL query rows and the given keys.
     g_err[0] = 0;
     if (B <= 0 || H <= 0 || Sq_full <= 0 || Sk <= 0)
         return fail(FCS_ERR_INVALID_ARGUMENT, "sizes must be positive (B=%d H=%d Sq=%d Sk=%d)", B, H, Sq_full, Sk);
     if (D != 64 && D != 128) return fail(FCS_ERR_UNSUPPORTED, "head dimension must be 64 or 128, got %d", D);
     if (dtype != FCS_DTYPE_FP16 && dtype != FCS_DTYPE_BF16)
         return fail(FCS_ERR_UNSUPPORTED, "dtype must be FCS_DTYPE_FP16 or FCS_DTYPE_BF16, got %d", dtype);
-    if (!out) return fail(FCS_ERR_INVALID_ARGUMENT, "out is NULL");
-    if (out_ld < Sk) return fail(FCS_ERR_INVALID_ARGUMENT, "out_ld (%lld) is smaller than the key length", (long long)out_ld);
+    if (passes != PASSES_STATS) {
+        if (!out) return fail(FCS_ERR_INVALID_ARGUMENT, "out is NULL");
+        if (out_ld < Sk)
+            return fail(FCS_ERR_INVALID_ARGUMENT, "out_ld (%lld) is smaller than the key length", (long long)out_ld);
+    }
+    if (passes != PASSES_BOTH) {
+        if (causal) return fail(FCS_ERR_UNSUPPORTED, "the passes can be run apart for non-causal calls only");
+        if (!shared_lse || reinterpret_cast<uintptr_t>(shared_lse) % 16)
+            return fail(FCS_ERR_INVALID_ARGUMENT, "the statistics vector must be a 16-byte aligned device pointer");
+    }
     if (!isfinite(scale)) return fail(FCS_ERR_INVALID_ARGUMENT, "scale must be finite");
     if (!causal && cls_n != -1 && cls_n <= 0)
         return fail(FCS_ERR_INVALID_ARGUMENT, "cls_n must be -1 or positive, got %d", cls_n);
@@ -819,7 +846,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
-    if (Sq <= SMALLQ_MAX_ROWS && smallq_smem_bytes(Sq, Sk, D) <= SMALLQ_MAX_SMEM) {
+    if (passes == PASSES_BOTH && Sq <= SMALLQ_MAX_ROWS && smallq_smem_bytes(Sq, Sk, D) <= SMALLQ_MAX_SMEM) {
         // reported as a call whose statistics and merge passes take no time
         PassTimers* tms = g_profiling ? timers_for_current_device() : nullptr;
         if (tms) {
@@ -842,20 +869,20 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
         return fail(FCS_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
     if (reinterpret_cast<uintptr_t>(workspace) % 256)
         return fail(FCS_ERR_WORKSPACE, "workspace must be 256-byte aligned");
-    p.neg_lse = reinterpret_cast<float*>(workspace);
+    p.neg_lse = passes == PASSES_BOTH ? reinterpret_cast<float*>(workspace) : shared_lse;
     p.part = reinterpret_cast<uint8_t*>(workspace) + part_off;
     p.ext = reinterpret_cast<uint8_t*>(workspace) + ext_off;
     p.ext_bf16 = dtype == FCS_DTYPE_BF16 ? 1 : 0;
     p.out = out;
     p.out_ld = out_ld;
-    p.clear_out = clear_out ? 1 : 0;
+    p.clear_out = (clear_out && passes == PASSES_BOTH) ? 1 : 0;   // (the statistics pass does the clearing)
     p.status = status;
     p.c = fabsf(scale) * 1.4426950408889634f;
     // -(lse) rides in the MMA of the column pass unless the scale is so small that
     // -(lse)/c leaves the range of its 16-bit parts
     const bool use_ext = p.c >= 1e-4f;
     p.inv_c = use_ext ? (scale < 0.f ? -1.0f : 1.0f) / p.c : 0.f;
-    p.log2_norm = log2f((float)h_norm * (float)Sq);
+    p.log2_norm = log2f((float)h_norm * (float)(norm_rows > 0 ? norm_rows : Sq));
     const uint32_t fmt = dtype == FCS_DTYPE_BF16 ? 1u : 0u;
     // fp32 accumulate, K-major A and B, M = 128, N = 256; a negative scale negates A
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((scale < 0.f ? 1u : 0u) << 13) |
@@ -868,7 +895,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if ((rc = make_tensor_map(&tq_b, q, dtype, B, H, Sq, D, qsb, qsh, qss, BLOCK)) != FCS_OK) return rc;
     if ((rc = make_tensor_map(&tk_a, k, dtype, B, H, Sk, D, ksb, ksh, kss, TILE)) != FCS_OK) return rc;
     if ((rc = make_tensor_map(&tk_b, k, dtype, B, H, Sk, D, ksb, ksh, kss, BLOCK)) != FCS_OK) return rc;
-    if (single_pass_applies(B, H, Sq, Sk, D, causal)) {
+    if (passes == PASSES_BOTH && single_pass_applies(B, H, Sq, Sk, D, causal)) {
         const int max_clusters = single_pass_max_clusters(single_pass_cluster_size(Sk));
         if (max_clusters > 0) {
             // reported as a call whose statistics and merge passes take no time
@@ -890,12 +917,23 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     const int grid2 = (int)(p.steps_total < sms ? p.steps_total : sms);
     PassTimers* tm = g_profiling ? timers_for_current_device() : nullptr;
     if (tm) { tm->recorded = false; cudaEventRecord(tm->ev[0], stream); }
-    cudaError_t e;
-    e = (D == 64) ? launch_stream<64, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream, false)
-                  : launch_stream<128, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream, false);
+    cudaError_t e = cudaSuccess;
+    if (passes == PASSES_COLUMNS) {
+        // the caller's statistics -> the column pass's operand form; the output starts from zero
+        int blocks = (int)(((long long)B * H * p.lse_rows + 255) / 256);
+        if (blocks > sms * 8) blocks = sms * 8;
+        ext_from_lse_kernel<<<blocks, 256, 0, stream>>>(p);
+        e = cudaGetLastError();
+        if (e == cudaSuccess && clear_out)
+            e = cudaMemset2DAsync(out, (size_t)out_ld * sizeof(float), 0, (size_t)Sk * sizeof(float), (size_t)B, stream);
+        if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "preparing the column pass failed: %s", cudaGetErrorString(e));
+    } else {
+        e = (D == 64) ? launch_stream<64, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream, false)
+                      : launch_stream<128, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream, false);
+    }
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics pass launch failed: %s", cudaGetErrorString(e));
     if (tm) cudaEventRecord(tm->ev[1], stream);
-    if (p.nsplit > 1) {
+    if (p.nsplit > 1 && passes != PASSES_COLUMNS) {
         const long long n = (long long)B * H * p.NQ * TILE;
         int blocks = (int)((n + 255) / 256);
         if (blocks > sms * 8) blocks = sms * 8;
@@ -913,12 +951,17 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
         if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics merge launch failed: %s", cudaGetErrorString(e));
     }
     if (tm) cudaEventRecord(tm->ev[2], stream);
+    if (passes == PASSES_STATS) {
+        if (tm) { cudaEventRecord(tm->ev[3], stream); tm->recorded = true; }
+        return FCS_OK;
+    }
+    const bool chained = !tm && passes == PASSES_BOTH;   // directly behind a kernel of this call
     if (use_ext)
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, !tm)
-                      : launch_stream<128, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, !tm);
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, chained)
+                      : launch_stream<128, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, chained);
     else
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream, !tm)
-                      : launch_stream<128, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream, !tm);
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream, chained)
+                      : launch_stream<128, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream, chained);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "column pass launch failed: %s", cudaGetErrorString(e));
     if (tm) { cudaEventRecord(tm->ev[3], stream); tm->recorded = true; }
     return FCS_OK;
@@ -1060,6 +1103,34 @@ int fcs_colsum_causal_batched(const void* q, const void* k, float* out, int64_t 
     return fcs::colsum_impl(q, k, out, out_ld, B, H, q_len, k_len, D, dtype, q_stride_b, q_stride_h, q_stride_s,
                             k_stride_b, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm, workspace,
                             workspace_bytes, status, stream);
+}
+
+size_t fcs_statistics_rows(int q_rows) {
+    return q_rows > 0 ? (size_t)fcs::ceil_div(q_rows, fcs::BLOCK) * fcs::BLOCK : 0;
+}
+
+int fcs_colsum_statistics(const void* q, const void* k, float* neg_lse, int B, int H, int q_rows, int Sk, int D,
+                          int dtype, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                          int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s, float scale,
+                          int64_t norm_rows, int h_norm, void* workspace, size_t workspace_bytes, int* status,
+                          void* stream) {
+    if (norm_rows < q_rows) {
+        fcs::g_err[0] = 0;
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "norm_rows (%lld) is smaller than the rows given (%d)",
+                         (long long)norm_rows, q_rows);
+    }
+    return fcs::colsum_impl(q, k, nullptr, 0, B, H, q_rows, Sk, D, dtype, q_stride_b, q_stride_h, q_stride_s,
+                            k_stride_b, k_stride_h, k_stride_s, scale, 0, 0, -1, h_norm, workspace,
+                            workspace_bytes, status, stream, false, fcs::PASSES_STATS, neg_lse, norm_rows);
+}
+
+int fcs_colsum_columns(const void* q, const void* k, const float* neg_lse, float* out, int64_t out_ld, int B, int H,
+                       int q_rows, int k_rows, int D, int dtype, int64_t q_stride_b, int64_t q_stride_h,
+                       int64_t q_stride_s, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                       float scale, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+    return fcs::colsum_impl(q, k, out, out_ld, B, H, q_rows, k_rows, D, dtype, q_stride_b, q_stride_h, q_stride_s,
+                            k_stride_b, k_stride_h, k_stride_s, scale, 0, 0, -1, 0, workspace, workspace_bytes,
+                            status, stream, true, fcs::PASSES_COLUMNS, const_cast<float*>(neg_lse), 0);
 }
 
 int fcs_select_topk(const float* colsum, int64_t ld, int B, int S, int k, int* indices, float* values,

@@ -259,6 +259,60 @@ def flash_colsum_causal(
     return out
 
 
+def statistics_rows(q_rows: int) -> int:
+    """Rows per (batch, head) of the vector :func:`colsum_statistics` returns (``q_rows``
+    rounded up to 256)."""
+    return int(_cabi.load().fcs_statistics_rows(int(q_rows)))
+
+
+def colsum_statistics(query_rows: torch.Tensor, key: torch.Tensor, scale: float, norm_rows: int,
+                      h_norm: int = 0) -> torch.Tensor:
+    """First pass alone (`fcs_colsum_statistics`): for the given query rows (any row range of a
+    call, as a view) against all keys, minus (log2-sum-exp + log2(heads * norm_rows)).
+
+    Returns fp32 ``(B * H, statistics_rows(rows))``; entries past the given rows are -inf.
+    Non-causal.  With :func:`colsum_columns` this splits the work of one call over devices
+    that all hold the inputs.
+    """
+    lib = _cabi.load()
+    Q, K, code = _prepare(query_rows, key)
+    B, H, rows, D = Q.shape
+    Sk = K.shape[2]
+    with torch.cuda.device(Q.device):
+        lse = torch.full((B * H, statistics_rows(rows)), float("-inf"), dtype=torch.float32, device=Q.device)
+        ws = _workspace(lib, Q.device, B, H, rows, Sk, D, False)
+        _check(lib.fcs_colsum_statistics(
+            Q.data_ptr(), K.data_ptr(), lse.data_ptr(), B, H, rows, Sk, D, code,
+            Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
+            float(scale), int(norm_rows), int(h_norm), ws.data_ptr(), ws.numel(),
+            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+    return lse
+
+
+def colsum_columns(query: torch.Tensor, key_rows: torch.Tensor, neg_lse: torch.Tensor,
+                   scale: float) -> torch.Tensor:
+    """Second pass alone (`fcs_colsum_columns`): column means of the given keys (any row range
+    of the key tensor, as a view) over all query rows of ``query``, from the statistics of all
+    those rows (``neg_lse``: fp32, contiguous, ``(B * H, statistics_rows(query rows))``).
+    Returns fp32 ``(B, key rows)``; nothing is left to reduce."""
+    lib = _cabi.load()
+    Q, K, code = _prepare(query, key_rows)
+    B, H, rows, D = Q.shape
+    k_rows = K.shape[2]
+    if (neg_lse.dtype != torch.float32 or not neg_lse.is_contiguous()
+            or tuple(neg_lse.shape) != (B * H, statistics_rows(rows))):
+        raise ValueError(f"neg_lse must be contiguous fp32 of shape {(B * H, statistics_rows(rows))}")
+    with torch.cuda.device(Q.device):
+        out = torch.empty((B, k_rows), device=Q.device, dtype=torch.float32)
+        ws = _workspace(lib, Q.device, B, H, rows, k_rows, D, False)
+        _check(lib.fcs_colsum_columns(
+            Q.data_ptr(), K.data_ptr(), neg_lse.data_ptr(), out.data_ptr(), k_rows, B, H, rows, k_rows, D, code,
+            Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
+            float(scale), ws.data_ptr(), ws.numel(),
+            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+    return out
+
+
 def topk_columns(colsum: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """The ``k`` most-attended key positions of every row of a column-mean tensor.
 

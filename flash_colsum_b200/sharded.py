@@ -1,4 +1,7 @@
-"""Head-sharded column means across the GPUs of one node.
+"""Column means across the GPUs of one node: heads split over the ranks (below), or the work
+of one call split by query rows and keys (`flash_colsum_work_sharded`, at the end).
+
+Head-sharded:
 
 Each (batch, head) unit contributes additively to its batch row of the result,
 so the heads are split over the ranks, every rank runs the local kernels with
@@ -133,3 +136,63 @@ def flash_colsum_head_sharded(
 
 
 __all__ = ["shard_range", "flash_colsum_head_sharded", "PeerAccumulator"]
+
+
+def work_shares(n: int, world_size: int, granule: int):
+    """Contiguous shares of ``n`` rows over ``world_size`` ranks, each a multiple of ``granule``
+    rows long (the last one takes what is left, later ones may be empty).  Returns the share
+    length and the list of ``(lo, hi)``."""
+    per = -(-n // world_size)
+    share = -(-per // granule) * granule
+    return share, [(min(n, r * share), min(n, (r + 1) * share)) for r in range(world_size)]
+
+
+def flash_colsum_work_sharded(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    scale: Optional[float] = None,
+    cls_len: Optional[int] = None,
+    group=None,
+    stats_fn: Optional[Callable] = None,
+    columns_fn: Optional[Callable] = None,
+) -> torch.Tensor:
+    """One non-causal call split over the ranks of ``group`` by WORK, not by heads: every rank
+    holds the whole ``query`` and ``key`` (B, H, S, D); rank r runs the statistics pass for its
+    share of the query rows, the ranks all-gather the per-row statistics (4 bytes per row and
+    head), rank r runs the column pass for its share of the keys, and the finished column
+    blocks are all-gathered into the (B, S) result on every rank.  For calls with fewer heads
+    than GPUs (a long single sample).  ``stats_fn`` / ``columns_fn`` replace the two kernels
+    (CPU tests)."""
+    if query.ndim != 4 or key.shape != query.shape:
+        raise ValueError(f"query and key must be 4-D tensors of the same shape, got {query.shape}, {key.shape}")
+    group = group if group is not None else dist.group.WORLD
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    B, H, S, D = query.shape
+    if scale is None:
+        scale = 1.0 / (D ** 0.5)
+    rows = S if cls_len is None else min(int(cls_len), S)
+    stats_fn = stats_fn or ops.colsum_statistics
+    columns_fn = columns_fn or ops.colsum_columns
+    dev = query.device
+
+    # pass 1 on a share of the query rows (multiples of 256 so that the vectors concatenate)
+    q_share, q_ranges = work_shares(rows, world, 256)
+    lo, hi = q_ranges[rank]
+    mine = torch.full((B * H, q_share), float("-inf"), dtype=torch.float32, device=dev)
+    if hi > lo:
+        part = stats_fn(query[:, :, lo:hi], key, scale, rows)
+        mine[:, :part.shape[1]] = part[:, :q_share]
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine, group=group)
+    total_rows = -(-rows // 256) * 256
+    neg_lse = torch.cat(gathered, dim=1)[:, :total_rows].contiguous()
+
+    # pass 2 on a share of the keys: its output columns are final
+    k_share, k_ranges = work_shares(S, world, 128)
+    lo, hi = k_ranges[rank]
+    block = torch.zeros((B, k_share), dtype=torch.float32, device=dev)
+    if hi > lo:
+        block[:, :hi - lo] = columns_fn(query[:, :, :rows], key[:, :, lo:hi], neg_lse, scale)
+    blocks = [torch.empty_like(block) for _ in range(world)]
+    dist.all_gather(blocks, block, group=group)
+    return torch.cat(blocks, dim=1)[:, :S].contiguous()

@@ -177,6 +177,35 @@ int fcs_colsum_batched_static_scratch(const void *q, const void *k, float *out, 
                                       int *status, void *stream);
 
 /*
+ * The two passes apart, for splitting the WORK of one non-causal call over several devices
+ * that all hold the inputs (the reference has no multi-device path; its single-sample
+ * launcher is flash_colsum/kernel_noncausal.py:95).  Device r runs fcs_colsum_statistics on
+ * its share of the query rows (a view of q) against all keys, the devices exchange the
+ * resulting vectors, and device r runs fcs_colsum_columns on its share of the keys (a view
+ * of k) against all query rows -- the output columns of the shares are final, there is
+ * nothing to reduce.
+ *
+ * neg_lse    fp32 [B*H][fcs_statistics_rows(q_rows)]: per query row minus (log2-sum-exp of
+ *            its scores + log2(h_norm * norm_rows)); rows past q_rows are not written by
+ *            fcs_colsum_statistics (fill them with -inf) and are ignored by fcs_colsum_columns.
+ * norm_rows  query rows that enter the mean over the whole call (>= q_rows of a share).
+ * Shares of query rows must start at multiples of 256 for the vectors to concatenate.
+ */
+size_t fcs_statistics_rows(int q_rows);
+int fcs_colsum_statistics(const void *q, const void *k, float *neg_lse,
+                          int B, int H, int q_rows, int Sk, int D, int dtype,
+                          int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                          int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                          float scale, int64_t norm_rows, int h_norm,
+                          void *workspace, size_t workspace_bytes, int *status, void *stream);
+int fcs_colsum_columns(const void *q, const void *k, const float *neg_lse, float *out, int64_t out_ld,
+                       int B, int H, int q_rows, int k_rows, int D, int dtype,
+                       int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                       int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                       float scale,
+                       void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+/*
  * Token pruning on top of the column means (the operator's use in the reference's
  * README: keep the most-attended visual tokens): for each of the B rows of `colsum`
  * (fp32, S valid entries, row stride ld) the k positions with the largest value, written

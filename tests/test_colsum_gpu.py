@@ -396,3 +396,36 @@ def test_topk_columns_matches_a_plain_sort(fc):
         fc.topk_columns(col, 0)
     with pytest.raises(ValueError):
         fc.topk_columns(col, 578)
+
+
+def test_passes_run_apart_reproduce_the_call(fc):
+    """The work split over devices, emulated on one: statistics per share of the query rows,
+    the vectors concatenated, column means per share of the keys -- equal to the whole call."""
+    from flash_colsum_b200 import ops
+    from flash_colsum_b200.sharded import work_shares
+    for (B, H, S, D, dtype, cls, world) in [(1, 3, 1500, 64, "fp16", None, 3), (2, 2, 700, 128, "bf16", None, 2),
+                                            (1, 2, 1100, 64, "fp16", 600, 4), (1, 1, 300, 64, "fp16", None, 8)]:
+        w = Workload("apart", B, H, S, S, D, dtype, cls_len=cls, seed=S + world)
+        q, k = make_inputs(w)
+        qc, kc = q.cuda(), k.cuda()
+        rows = S if cls is None else min(cls, S)
+        scale = 1.0 / D ** 0.5
+        q_share, q_ranges = work_shares(rows, world, 256)
+        pieces = []
+        for lo, hi in q_ranges:
+            piece = torch.full((B * H, q_share), float("-inf"), device="cuda")
+            if hi > lo:
+                part = ops.colsum_statistics(qc[:, :, lo:hi], kc, scale, rows)
+                assert part.shape == (B * H, ops.statistics_rows(hi - lo))
+                piece[:, :part.shape[1]] = part
+            pieces.append(piece)
+        neg_lse = torch.cat(pieces, dim=1)[:, :ops.statistics_rows(rows)].contiguous()
+        k_share, k_ranges = work_shares(S, world, 128)
+        cols = [ops.colsum_columns(qc[:, :, :rows], kc[:, :, lo:hi], neg_lse, scale) for lo, hi in k_ranges if hi > lo]
+        got = torch.cat(cols, dim=1)
+        assert fc.device_status() == 0
+        assert got.shape == (B, S)
+        assert_parity(got.cpu().numpy(), c_oracle.colsum_c(q, k, cls_len=cls), f"apart {B}x{H}x{S} world {world}")
+        torch.testing.assert_close(got, fc.flash_colsum(qc, kc, cls_len=cls), rtol=2e-4, atol=1e-9)
+    with pytest.raises(RuntimeError, match="norm_rows"):
+        ops.colsum_statistics(qc[:, :, :256], kc, scale, 100)

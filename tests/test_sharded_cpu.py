@@ -76,3 +76,79 @@ def test_shard_range_covers_every_unit_once():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         shard_range(4, 2, 2)
+
+
+# ---------------------------------------------------------------------------
+# Work split (query rows for the statistics, keys for the column means) on two and three
+# CPU ranks: the two kernels are replaced by float64 numpy, so what is tested is the share
+# arithmetic, the padding of the gathered vectors and the two all-gathers.
+# ---------------------------------------------------------------------------
+def _stats_numpy(query_rows, key, scale, norm_rows, h_norm=0):
+    q = query_rows.double().numpy()
+    k = key.double().numpy()
+    B, H, rows, _ = q.shape
+    pad = -(-rows // 256) * 256
+    out = np.full((B * H, pad), -np.inf)
+    c = scale * np.log2(np.e)
+    for b in range(B):
+        for h in range(H):
+            s = (q[b, h] @ k[b, h].T) * c
+            m = s.max(axis=1)
+            lse = m + np.log2(np.exp2(s - m[:, None]).sum(axis=1))
+            out[b * H + h, :rows] = -(lse + np.log2(H * norm_rows))
+    return torch.from_numpy(out).float()
+
+
+def _columns_numpy(query, key_rows, neg_lse, scale):
+    q = query.double().numpy()
+    k = key_rows.double().numpy()
+    B, H, rows, _ = q.shape
+    nl = neg_lse.double().numpy()
+    c = scale * np.log2(np.e)
+    out = np.zeros((B, k.shape[2]))
+    for b in range(B):
+        for h in range(H):
+            s = (q[b, h] @ k[b, h].T) * c
+            out[b] += np.exp2(s + nl[b * H + h, :rows, None]).sum(axis=0)
+    return torch.from_numpy(out).float()
+
+
+def _work_worker(rank, world, port, S, cls, results):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from flash_colsum_b200.inputs import Workload, make_inputs
+        from flash_colsum_b200.sharded import flash_colsum_work_sharded
+        q, k = make_inputs(Workload("w", 2, 2, S, S, 64, "fp16", cls_len=cls, seed=S))
+        out = flash_colsum_work_sharded(q, k, cls_len=cls, stats_fn=_stats_numpy, columns_fn=_columns_numpy)
+        results[rank] = out.numpy()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,S,cls", [(2, 300, None), (3, 700, None), (2, 520, 260), (3, 100, None)])
+def test_work_split_matches_unsharded(world, S, cls):
+    from flash_colsum_b200.inputs import Workload, make_inputs
+    from oracle import c_oracle
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_work_worker, args=(world, _free_port(), S, cls, results), nprocs=world, join=True)
+    q, k = make_inputs(Workload("w", 2, 2, S, S, 64, "fp16", cls_len=cls, seed=S))
+    want = c_oracle.colsum_c(q, k, cls_len=cls)
+    for r in range(world):
+        assert results[r].shape == (2, S)
+        np.testing.assert_allclose(results[r], want, rtol=2e-5, atol=1e-9)
+
+
+def test_work_shares_cover_the_rows_in_granules():
+    from flash_colsum_b200.sharded import work_shares
+    for n, world, g in [(1000, 4, 256), (577, 2, 128), (100, 8, 256), (131072, 8, 256), (1, 3, 128)]:
+        share, ranges = work_shares(n, world, g)
+        assert share % g == 0 and len(ranges) == world
+        assert ranges[0][0] == 0 and ranges[-1][1] == n
+        for r, (lo, hi) in enumerate(ranges):
+            assert lo == min(n, r * share) and lo <= hi <= lo + share
+            if r:
+                assert lo == ranges[r - 1][1]

@@ -1,5 +1,6 @@
 """Head-sharded causal call on two GPUs: NCCL all-reduce and the in-kernel
-peer-memory reduce both reproduce the unsharded result.  Needs two devices; on a
+peer-memory reduce both reproduce the unsharded result; so does a single-head non-causal
+call split by work (query rows, then keys).  Needs two devices; on a
 single-GPU box the test is skipped."""
 
 import os
@@ -46,7 +47,14 @@ def _worker(rank, world, port, results):
         outs = [flash_colsum_head_sharded(q, k, H, is_causal=True, peer=peer).clone() for _ in range(3)]
         torch.cuda.synchronize()
         assert flash_colsum_b200.device_status() == 0
-        results[rank] = (out_nccl.cpu().numpy(), [o.cpu().numpy() for o in outs])
+        # one single-head sample split by work: query rows for the statistics, keys for the columns
+        from flash_colsum_b200.sharded import flash_colsum_work_sharded
+        w2 = Workload("w", 1, 1, 3000, 3000, 64, "fp16", seed=23)
+        q2, k2 = (t.to(dev) for t in make_inputs(w2))
+        out_work = flash_colsum_work_sharded(q2, k2)
+        torch.cuda.synchronize()
+        assert flash_colsum_b200.device_status() == 0
+        results[rank] = (out_nccl.cpu().numpy(), [o.cpu().numpy() for o in outs], out_work.cpu().numpy())
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -70,3 +78,8 @@ def test_two_gpus_match_unsharded():
     for o in results[0][1]:          # the peer-memory reduce lands on rank 0
         rel, mx = parity_errors(o, want)
         assert rel <= 1e-3 and mx <= 1e-3, ("peer", rel, mx)
+    q2, k2 = make_inputs(Workload("w", 1, 1, 3000, 3000, 64, "fp16", seed=23))
+    want2 = c_oracle.colsum_c(q2, k2)
+    for r in (0, 1):                 # the work split leaves the whole result on every rank
+        rel, mx = parity_errors(results[r][2], want2)
+        assert rel <= 1e-3 and mx <= 1e-3, ("work split", r, rel, mx)
