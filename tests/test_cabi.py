@@ -1,6 +1,7 @@
 """The C-ABI library loads and exports what the header declares; the operator's
 host-side validation behaves like the reference's.  No GPU needed."""
 
+import ctypes
 import os
 import re
 
@@ -43,6 +44,31 @@ def test_argument_errors_come_back_as_codes_not_crashes():
     rc = lib.fcs_colsum_causal(None, None, None, 1, 1, 1, 96, 0, 96, 96, 96, 96, 1.0, -1, 0,
                                None, 0, None, None)
     assert rc == -2 and "head dimension" in _cabi.last_error()
+
+
+def test_argument_errors_of_the_added_entry_points():
+    """Top-k selection, the passes apart and the batched causal call refuse bad arguments with a
+    code and a message before anything is launched."""
+    lib = _cabi.load()
+    assert lib.fcs_statistics_rows(1) == 256 and lib.fcs_statistics_rows(256) == 256
+    assert lib.fcs_statistics_rows(257) == 512 and lib.fcs_statistics_rows(0) == 0
+    assert lib.fcs_select_topk(None, 8, 1, 8, 2, None, None, None) == -1
+    assert "NULL" in _cabi.last_error()
+    buf = (ctypes.c_float * 64)()
+    idx = (ctypes.c_int * 64)()
+    addr = ctypes.addressof
+    assert lib.fcs_select_topk(addr(buf), 8, 1, 8, 9, addr(idx), None, None) == -1      # k > S
+    assert "k must be" in _cabi.last_error()
+    assert lib.fcs_select_topk(addr(buf), 4, 1, 8, 2, addr(idx), None, None) == -1      # row stride < S
+    # statistics of a share: the normalisation cannot count fewer rows than the share has
+    assert lib.fcs_colsum_statistics(addr(buf), addr(buf), addr(buf), 1, 1, 300, 300, 64, 0, 64, 64, 64, 64, 64, 64,
+                                     1.0, 100, 0, None, 0, None, None) == -1
+    assert "norm_rows" in _cabi.last_error()
+    assert lib.fcs_colsum_columns(addr(buf), addr(buf), None, addr(buf), 300, 1, 1, 300, 300, 64, 0,
+                                  64, 64, 64, 64, 64, 64, 1.0, None, 0, None, None) == -1
+    assert "statistics vector" in _cabi.last_error()
+    assert lib.fcs_colsum_causal_batched(None, None, None, 0, 2, 1, 1, 1, 96, 0, 96, 96, 96, 96, 96, 96,
+                                         1.0, -1, 0, None, 0, None, None) < 0
 
 
 def test_validation_order_and_messages_without_a_gpu():
