@@ -9,7 +9,9 @@ S=2048, D=64, fp16).  At N GPUs each rank runs that shape on its own batch shard
 (weak scaling, no collective: the output is batch-sharded), and the JSON line
 also carries the long-context causal shape (131072 keys, 512 suffix queries,
 D=128, bf16) with its 32 heads split over the ranks and one NCCL all-reduce of
-the fp32 per-key partials (strong scaling) under "causal_long_context".
+the fp32 per-key partials (strong scaling) under "causal_long_context", and the reference's
+batched sweep shape (B=128 H=16 S=1024 per GPU), which takes the single-pass cluster kernel,
+next to the two-pass kernels on the same inputs under "short_key_axis".
 
 Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
 the reference's materialising implementation on the host cores instead.
@@ -411,6 +413,30 @@ def main():
         del q5, k5
     assert fc.device_status() == 0
 
+    # ------------------------------------------------------------ short key axis (single-pass kernel)
+    # the reference's batched sweep shape (benchmarks/benchmark_colsum.py:289: H=16 S=1024 D=64),
+    # B=128 per GPU; takes the single-pass cluster kernel, timed next to the two passes
+    short_keys = None
+    if not args.skip_long_context:
+        ws_ = Workload("batched_s1024", 128, 16, 1024, 1024, 64, "fp16", seed=5 + rank)
+        g = torch.Generator(device=dev).manual_seed(ws_.seed)
+        qs = torch.randn(ws_.B, ws_.H, ws_.Sq, ws_.D, generator=g, device=dev).to(ws_.torch_dtype)
+        ks = torch.randn(ws_.B, ws_.H, ws_.Sk, ws_.D, generator=g, device=dev).to(ws_.torch_dtype)
+        n_short = max(5, min(args.steps // 4, 20))
+        t_single = time_steps(lambda: fc.flash_colsum(qs, ks), n_short, 3, flush_buf, barrier)
+        _cabi.set_single_pass(_cabi.SINGLE_PASS_NEVER)
+        t_double = time_steps(lambda: fc.flash_colsum(qs, ks), n_short, 3, flush_buf, barrier)
+        _cabi.set_single_pass(_cabi.SINGLE_PASS_AUTO)
+        ms_single = max_over_ranks(sum(t_single) / len(t_single))
+        ms_double = max_over_ranks(sum(t_double) / len(t_double))
+        short_keys = {"workload": "batched non-causal B=128 H=16 S=1024 D=64 fp16 per GPU (inputs 512 MiB)",
+                      "kernel": "colsum_single_pass_kernel, clusters of 4" if _cabi.single_pass_applies(
+                          ws_.B, ws_.H, ws_.Sk) else "two passes",
+                      "ms_per_call": ms_single, "value": ws_.flop * world / (ms_single * 1e-3) / 1e12,
+                      "unit": UNIT, "two_pass_ms_per_call": ms_double}
+        del qs, ks
+    assert fc.device_status() == 0
+
     # ------------------------------------------------------------ CPU baseline (rank 0, one GPU only)
     cpu = None
     if rank == 0 and world == 1:
@@ -434,6 +460,7 @@ def main():
             "gpu_launches": launches_per_call * args.steps,
             "clocks": clocks,
             "causal_long_context": long_ctx,
+            "short_key_axis": short_keys,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
