@@ -21,10 +21,11 @@
 // the column-sum MMA of tile i runs while the consumers work on tiles i+1 and i+2,
 // which is the time the statistics of tile i have to go around the cluster.
 //
-// Measured against the two-pass kernels (fp16, H = 16): 1.67x at S = 256, 1.43x at
-// 512, 1.12-1.15x at 1024, 0.87x at 2048 (15 resident clusters of 8 use 120 of the
-// 148 SMs, and eight CTAs advance in step); key lengths that fill less than ~85 %
-// of their cluster's slices lose to the padding.  The host side picks accordingly.
+// Measured against the two-pass kernels (fp16, B = 32, H = 16): 1.2-1.3x at 400-1024
+// keys, 1.07-1.14x at 1152-1536, 0.84x / 0.95x at 1792 / 2048 (only 15 clusters of seven
+// or eight CTAs are resident at a time: 105 / 120 of the 148 SMs); key lengths that fill
+// less than ~75 % of their cluster's slices lose to the padding.  The host side picks
+// accordingly.
 #pragma once
 
 #include "colsum_math.cuh"
@@ -36,7 +37,7 @@ namespace fcs {
 struct SinglePassParams {
     int B, H, Sq, Sk;
     int NQ;                 // 128-row query tiles
-    int CL;                 // CTAs per cluster = 256-key slices (1, 2, 4 or 8)
+    int CL;                 // CTAs per cluster = 256-key slices (1 .. 8)
     int units;              // B * H
     int clusters;           // gridDim.x / CL
     int flush_units;        // most (batch, head) pairs accumulated in tensor memory before a flush

@@ -686,37 +686,34 @@ static int launch_small_q(const void* q, const void* k, float* out, int64_t out_
 }
 
 // Short key axes (non-causal, head dimension 64, S_k <= 2048): the single-pass
-// cluster kernel.  g_single_pass: 0 = where it is the faster of the two (measured: keys
-// that fill their 256-key slices to 85 % or more, up to 1024 of them, or up to 2048 when
-// the call is small), 1 = never, 2 = whenever the shape allows.
+// cluster kernel.  g_single_pass: 0 = where it is the faster of the two (see
+// single_pass_applies), 1 = never, 2 = whenever the shape allows.
 static int g_single_pass = 0;
 
 static int single_pass_cluster_size(int Sk) {
-    const int slices = (Sk + 255) / 256;
-    int cl = 1;
-    while (cl < slices) cl *= 2;
-    return cl;
+    return (Sk + 255) / 256;   // one CTA per 256 keys; any size up to eight is a legal cluster
 }
 
 static bool single_pass_applies(int B, int H, int Sq, int Sk, int D, int causal) {
     if (g_single_pass == 1 || causal || D != 64 || Sk > 256 * sp::MAX_CL) return false;
     if (g_single_pass == 2) return true;
     const int cl = single_pass_cluster_size(Sk);
-    if ((long long)Sk * 100 < (long long)cl * 256 * 85) return false;   // too much padding
-    if (cl <= 4) return true;
-    // 2048 keys: only 15 eight-CTA clusters fit (120 of 148 SMs), so the two passes win on
-    // large calls; on small ones their fixed costs (two launches, partial waves) lose
+    // measured at B=32 H=16 against the two passes: 1.2-1.3x at 400-1024 keys, 1.07-1.14x at
+    // 1152-1536, 1.02x at 577 (75 % of three slices); clusters of 7 and 8 fit only 15 at a time
+    // (105 / 120 of 148 SMs) and lose on large calls (0.84x / 0.95x) but win on small ones,
+    // where the fixed costs of two launches and partial waves weigh more
+    if (cl <= 6) return (long long)Sk * 100 >= (long long)cl * 256 * 75;
+    if ((long long)Sk * 100 < (long long)cl * 256 * 85) return false;
     const long long tiles = (long long)B * H * ((Sq + TILE - 1) / TILE);
     return tiles <= 512;
 }
 
 // Clusters of `cl` CTAs that can be resident at once (0 if the query fails).
 static int single_pass_max_clusters(int cl) {
-    static int cached[64][4] = {{0}};
+    static int cached[64][sp::MAX_CL + 1] = {{0}};
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-    int idx = 0;
-    while ((1 << idx) < cl) ++idx;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || cl < 1 || cl > sp::MAX_CL) return 0;
+    const int idx = cl;
     if (cached[dev][idx] == 0) {
         if (cudaFuncSetAttribute(colsum_single_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  sp::DYN_BYTES) != cudaSuccess)

@@ -234,8 +234,8 @@ int fcs_last_pass_ms(float *stats_ms, float *merge_ms, float *colsum_ms);
  * Kernel choice for non-causal calls with head dimension 64 and at most 2048
  * keys, which can run as one pass on thread-block clusters instead of the two
  * streaming passes.  No counterpart in the reference.  mode 0 (default): the
- * single pass where it is the faster one (keys that fill their 256-key slices
- * to 85 % or more: up to 1024 of them, or up to 2048 when the call is small);
+ * single pass where it is the faster one (up to 1536 keys that fill their
+ * 256-key slices to 75 % or more, or up to 2048 when the call is small);
  * 1: never; 2: whenever the shape allows.  Process-wide; not
  * thread-safe.  A single-pass call reports its whole duration as the column
  * pass in fcs_last_pass_ms().  Its results agree with the two-pass kernels to
@@ -246,8 +246,8 @@ int fcs_set_single_pass(int mode);
  * single pass under the current mode (host arithmetic only; calls with at most four query rows take the few-row kernel
  * before this choice is made). */
 int fcs_single_pass_applies(int B, int H, int sq_rows, int Sk, int D, int is_causal);
-/* CTAs per cluster the single pass uses for `Sk` keys (one per 256 keys, rounded up
- * to a power of two) and how many such clusters the current device runs at once. */
+/* CTAs per cluster the single pass uses for `Sk` keys (one per 256 keys) and how many
+ * such clusters the current device runs at once. */
 int fcs_single_pass_info(int Sk, int *cluster_size, int *max_clusters);
 
 /*

@@ -100,12 +100,13 @@ def test_kernel_choice_rule_is_host_arithmetic():
         _cabi.set_single_pass(_cabi.SINGLE_PASS_AUTO)
         assert _cabi.single_pass_applies(8, 16, 256)
         assert _cabi.single_pass_applies(8, 16, 512)
+        assert _cabi.single_pass_applies(8, 16, 577)           # 75 % of three slices
         assert _cabi.single_pass_applies(8, 16, 1024)
-        assert _cabi.single_pass_applies(8, 16, 900)           # 88 % of four slices
-        assert not _cabi.single_pass_applies(8, 16, 577)       # 56 % of four slices
+        assert _cabi.single_pass_applies(8, 16, 1536)          # six slices
+        assert not _cabi.single_pass_applies(8, 16, 300)       # 59 % of two slices
+        assert not _cabi.single_pass_applies(8, 16, 1792)      # seven-CTA clusters: 15 fit, 105 SMs
         assert not _cabi.single_pass_applies(8, 16, 2048)      # eight-CTA clusters lose to two passes ...
         assert _cabi.single_pass_applies(1, 16, 2048)          # ... except on small calls
-        assert not _cabi.single_pass_applies(4, 16, 1280)      # 62 % of eight slices
         assert not _cabi.single_pass_applies(8, 16, 4096)      # does not fit a cluster
         assert _cabi.single_pass_applies(1, 2, 512)            # small calls are cut at tile granularity
         assert not _cabi.single_pass_applies(8, 16, 512, D=128)

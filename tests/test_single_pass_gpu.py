@@ -52,9 +52,12 @@ SHAPES = [
     (2, 2, 100, "fp16", None),       # 1, ragged keys and queries inside one tile
     (3, 2, 300, "bf16", None),       # 2, ragged second slice
     (2, 2, 512, "fp16", None),       # 2
-    (2, 3, 577, "fp16", None),       # 4, one key in the last slice's first group
+    (2, 3, 577, "fp16", None),       # 3, one key in the last slice's first group
+    (2, 2, 1200, "bf16", None),      # 5
+    (1, 3, 1536, "fp16", None),      # 6
+    (2, 2, 1700, "fp16", None),      # 7
     (2, 4, 1024, "fp16", None),      # 4
-    (3, 5, 1500, "bf16", None),      # 8, ragged, more (batch, head) pairs than clusters can split evenly
+    (3, 5, 1500, "bf16", None),      # 6, ragged, more (batch, head) pairs than clusters can split evenly
     (2, 4, 2048, "fp16", None),      # 8, the longest key axis
     (3, 4, 577, "fp16", 5),          # cls_len: five query rows (more than the few-row kernel takes)
     (3, 4, 577, "fp16", 200),        # cls_len: ragged second query tile
@@ -162,4 +165,4 @@ def test_default_choice_by_shape(fc, kernel_choice):
         _cabi.set_profiling(False)
     cl, resident = _cabi.single_pass_info(2048)
     assert cl == 8 and resident >= 1
-    assert _cabi.single_pass_info(256)[0] == 1
+    assert _cabi.single_pass_info(256)[0] == 1 and _cabi.single_pass_info(577)[0] == 3
