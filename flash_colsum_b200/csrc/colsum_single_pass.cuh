@@ -5,7 +5,7 @@
 // The two-pass kernels evaluate every score and every exp twice.  When the whole
 // key axis fits a cluster of up to eight CTAs (256 keys each), one pass is enough:
 //
-//   S      = Q_tile K_slice^T            tcgen05 MMA, 128 queries x 2 x 128 keys, fp32 in tensor memory
+//   S      = Q_tile K_slice^T            tcgen05 MMA, 128 queries x 256 keys, fp32 in tensor memory
 //   P~     = exp2(c*S - m_g)             per thread (= query row) and 64-key group g, fp16 -> shared memory
 //   (m, l) exchange                      per row: 4 groups in the CTA, then all CTAs of the cluster
 //                                        through distributed shared memory (st.async + mbarrier
@@ -46,7 +46,7 @@ struct SinglePassParams {
     float* out;
     long long out_ld;
     int* status;
-    uint32_t idesc_scores;  // 128 x 128 x 16, K-major operands
+    uint32_t idesc_scores;  // 128 x 256 x 16, K-major operands
     uint32_t idesc_colsum;  // 128 x 16 x 16, A = P~ (M-major), B = W (K-major), fp16
 };
 
@@ -236,11 +236,12 @@ __device__ __forceinline__ void exp8_packed(int pair0, const uint32_t* s, f32x2 
 // Roles in a CTA (20 warps):
 //   16 consumer warps  four groups of 128 threads (thread = query row of the tile, group =
 //                      64 key columns).  Groups 0,1 and groups 2,3 form two "halves" (the two
-//                      128-key tiles of the slice) with their own score accumulator, P~
-//                      buffers, column-sum accumulator and barriers, so that one half computes
-//                      while the other waits for its next scores.
+//                      128-key tiles of the slice), each with its own P~ buffers, column-sum
+//                      accumulator and barriers for the second MMA; the scores of both halves
+//                      come from one 128 x 256 MMA (separate score accumulators per half or
+//                      per group were measured: no faster, more instructions to issue).
 //   1 TMA warp         key slice per (batch, head), query tile per step.
-//   1 MMA warp         scores(i) of both halves, column sums(i-2) of both halves, scores(i+1), ...
+//   1 MMA warp         scores(i), column sums(i-2) of both halves, scores(i+1), ...
 //   2 exchange warps   64 rows each: combine the four groups' (max, sum) of a row, post the
 //                      result to every CTA of the cluster, and when all CTAs' values are in,
 //                      write the weights W of the four groups.
@@ -263,8 +264,7 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const uint32_t k_full = bars, k_empty = bars + 8;
     auto q_full = [&](int s) { return bars + 8u * (2 + s); };
     auto q_empty = [&](int s) { return bars + 8u * (4 + s); };
-    auto s_full = [&](int hf) { return bars + 8u * (6 + hf); };
-    auto s_empty = [&](int hf) { return bars + 8u * (8 + hf); };
+    const uint32_t s_full = bars + 8u * 6, s_empty = bars + 8u * 8;   // the score accumulator (slots 7, 9 unused)
     auto stats_bar = [&](int s) { return bars + 8u * (10 + s); };
     auto xchg_bar = [&](int s) { return bars + 8u * (12 + s); };
     auto w_ready = [&](int s) { return bars + 8u * (14 + s); };
@@ -291,10 +291,10 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     auto t_hi = [&](int u) { return range.t_hi(u); };
 
     if (threadIdx.x == 0) {
-        mbar_init(k_full, 1); mbar_init(k_empty, 2);
+        mbar_init(k_full, 1); mbar_init(k_empty, 1);
+        mbar_init(s_full, 1); mbar_init(s_empty, CONSUMER_THREADS);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(q_full(i), 1); mbar_init(q_empty(i), 2);   // released by both halves' score MMAs
-            mbar_init(s_full(i), 1); mbar_init(s_empty(i), HALF_THREADS);
+            mbar_init(q_full(i), 1); mbar_init(q_empty(i), 1);
             mbar_init(stats_bar(i), CONSUMER_THREADS);
             mbar_init(xchg_bar(i), XCHG_WARPS);   // this CTA's exchange warps; the data counts as bytes
             mbar_init(w_ready(i), XCHG_WARPS * 32);
@@ -427,10 +427,10 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------ MMA issuer
-        // Issue order: scores(i) of both halves, column sums(i-2) of both halves, scores(i+1),
-        // ... -- the order in which their inputs become ready: scores(i+1) when the consumers
-        // have read scores(i) out of tensor memory, column sums(i-1) only after the statistics
-        // of tile i-1 have gone around the cluster.
+        // Issue order: scores(i), column sums(i-2) of both halves, scores(i+1), ... -- the order
+        // in which their inputs become ready: scores(i+1) when the consumers have read scores(i)
+        // out of tensor memory, column sums(i-1) only after the statistics of tile i-1 have gone
+        // around the cluster.
         int i = 0, uc = 0, fc = 0;
         int first = 0;                // first tile of the current batch entry on this CTA
         bool ok = true, fresh = true; // fresh: the next column-sum MMAs start a new accumulation
@@ -470,17 +470,16 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 const int qs = i & 1;
                 if (!wait_all(q_full(qs), (i >> 1) & 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
                 const uint64_t dq = umma_desc_k_sw128(q_smem + qs * Q_BYTES);
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    if (!wait_all(s_empty(hf), (i & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+                {
+                    if (!wait_all(s_empty, (i & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t dk = umma_desc_k_sw128(k_smem + hf * (K_BYTES / 2));
+                    const uint64_t dk = umma_desc_k_sw128(k_smem);
                     if (elect_one_sync()) {
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks)
-                            umma_f16(tmem_base + 128 * hf, dq + (uint64_t)((ks * 32) >> 4),
+                            umma_f16(tmem_base, dq + (uint64_t)((ks * 32) >> 4),
                                      dk + (uint64_t)((ks * 32) >> 4), p.idesc_scores, ks > 0 ? 1u : 0u);
-                        umma_commit(s_full(hf));
+                        umma_commit(s_full);
                         umma_commit(q_empty(qs));
                         if (t + 1 == t_end) umma_commit(k_empty);
                     }
@@ -521,7 +520,7 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             for (int t = t_lo(u); t < t_hi(u); ++t, ++i) {
                 const int slot = i & 1;
                 // ---- scores of this thread's row and group
-                ok = mbar_wait(s_full(hf), i & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+                ok = mbar_wait(s_full, i & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -531,7 +530,7 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 tmem_ld_wait(sa);
                 tmem_ld_wait(sb);
                 tc_fence_before();
-                mbar_arrive(s_empty(hf));
+                mbar_arrive(s_empty);
 
                 // ---- P~ = exp2(c*s - m_g) as packed fp16
                 uint32_t h[32];

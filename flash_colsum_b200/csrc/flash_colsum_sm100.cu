@@ -766,9 +766,9 @@ static int launch_single_pass(const CUtensorMap& tq, const CUtensorMap& tk, floa
     sp_.out_ld = out_ld;
     sp_.status = status;
     const uint32_t fmt = dtype == FCS_DTYPE_BF16 ? 1u : 0u;
-    // one score MMA covers the 128 keys of a half: M = 128, N = 128
+    // one score MMA covers the 256 keys of the slice: M = 128, N = 256
     sp_.idesc_scores = (1u << 4) | (fmt << 7) | (fmt << 10) | ((scale < 0.f ? 1u : 0u) << 13) |
-                       ((uint32_t)(TILE >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
+                       ((uint32_t)(BLOCK >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
     // fp16 x fp16 -> fp32, A stored with the M index contiguous, B K-major, M = 128, N = 16
     sp_.idesc_colsum = (1u << 4) | (1u << 15) | ((uint32_t)(sp::W_N >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
     cudaLaunchConfig_t cfg;
