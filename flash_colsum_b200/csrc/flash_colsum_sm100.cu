@@ -66,22 +66,24 @@ constexpr int EXT_B_BYTES = BLOCK * EXT_ROW_BYTES;   // the query-side columns o
 
 template <int D, int MODE>
 struct Layout {
-    static constexpr bool EXT = (MODE == MODE_COLSUM_EXT);
+    static constexpr bool SHORT = (MODE == MODE_COLSUM_EXT_SHORT);
+    static constexpr bool EXT = (MODE == MODE_COLSUM_EXT) || SHORT;
     static constexpr int SLABS = D / 64;              // 64-element (128-byte) column slabs
     static constexpr int A_SLAB_BYTES = TILE * 128;
     static constexpr int B_SLAB_BYTES = BLOCK * 128;
     static constexpr int A_BYTES = SLABS * A_SLAB_BYTES;
     static constexpr int B_BYTES = SLABS * B_SLAB_BYTES;
     static constexpr int B_STAGE_BYTES = B_BYTES + (EXT ? EXT_B_BYTES : 0);   // block, then its extension
-    static constexpr int NS = (D == 64) ? 4 : 2;      // streamed-operand stages
+    static constexpr int NS = SHORT ? 1 : (D == 64) ? 4 : 2;      // streamed-operand stages
+    static constexpr int NA = SHORT ? 256 / SLABS / 32 : 2;       // resident-operand buffers (128 KiB when they are what streams)
     static constexpr int A_OFF = 0;
-    static constexpr int B_OFF = 2 * A_BYTES;
+    static constexpr int B_OFF = NA * A_BYTES;
     static constexpr int EXTA_OFF = B_OFF + NS * B_STAGE_BYTES;             // 128 rows of the constant
     static constexpr int LSE_OFF = EXTA_OFF + (EXT ? EXT_A_BYTES : 0);      // NUM_LSE slots of 256 floats
     static constexpr int BAR_OFF = LSE_OFF + (MODE == MODE_COLSUM ? NUM_LSE * BLOCK * 4 : 0);
-    // barriers: a_full[2] a_empty[2] b_full[NS] b_empty[NS] t_full[2] t_empty[2] merge[MERGE_SLOTS]
+    // barriers: a_full[NA] a_empty[NA] b_full[NS] b_empty[NS] t_full[2] t_empty[2] merge[MERGE_SLOTS]
     //           l_full[NUM_LSE] l_empty[NUM_LSE]
-    static constexpr int NUM_BARS = 4 + 2 * NS + 2 * NUM_TBUF + MERGE_SLOTS + 2 * NUM_LSE;
+    static constexpr int NUM_BARS = 2 * NA + 2 * NS + 2 * NUM_TBUF + MERGE_SLOTS + 2 * NUM_LSE;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;        // tmem address, abort flag
     static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // float2[MERGE_SLOTS][groups][128]
     static constexpr int TOTAL = MERGE_OFF + (MODE == MODE_STATS ? MERGE_SLOTS * CONSUMER_GROUPS * TILE * 8 : 0);
@@ -133,8 +135,9 @@ template <int D, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ CUtensorMap tm_ext, const Problem p) {
-    constexpr bool EXT = (MODE == MODE_COLSUM_EXT);
+    constexpr bool EXT = (MODE == MODE_COLSUM_EXT) || (MODE == MODE_COLSUM_EXT_SHORT);
     using L = Layout<D, MODE>;
+    constexpr int NA = L::NA;
     using Items = typename ItemsOf<MODE>::type;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -145,14 +148,14 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     const uint32_t lse_smem = smem_base + L::LSE_OFF;
     const uint32_t bars = smem_base + L::BAR_OFF;
     auto a_full = [&](int i) { return bars + 8u * i; };
-    auto a_empty = [&](int i) { return bars + 8u * (2 + i); };
-    auto b_full = [&](int i) { return bars + 8u * (4 + i); };
-    auto b_empty = [&](int i) { return bars + 8u * (4 + L::NS + i); };
-    auto t_full = [&](int i) { return bars + 8u * (4 + 2 * L::NS + i); };
-    auto t_empty = [&](int i) { return bars + 8u * (4 + 2 * L::NS + NUM_TBUF + i); };
-    auto merge_bar = [&](int i) { return bars + 8u * (4 + 2 * L::NS + 2 * NUM_TBUF + i); };
-    auto l_full = [&](int i) { return bars + 8u * (4 + MERGE_SLOTS + 2 * L::NS + 2 * NUM_TBUF + i); };
-    auto l_empty = [&](int i) { return bars + 8u * (4 + MERGE_SLOTS + 2 * L::NS + 2 * NUM_TBUF + NUM_LSE + i); };
+    auto a_empty = [&](int i) { return bars + 8u * (NA + i); };
+    auto b_full = [&](int i) { return bars + 8u * (2 * NA + i); };
+    auto b_empty = [&](int i) { return bars + 8u * (2 * NA + L::NS + i); };
+    auto t_full = [&](int i) { return bars + 8u * (2 * NA + 2 * L::NS + i); };
+    auto t_empty = [&](int i) { return bars + 8u * (2 * NA + 2 * L::NS + NUM_TBUF + i); };
+    auto merge_bar = [&](int i) { return bars + 8u * (2 * NA + 2 * L::NS + 2 * NUM_TBUF + i); };
+    auto l_full = [&](int i) { return bars + 8u * (2 * NA + MERGE_SLOTS + 2 * L::NS + 2 * NUM_TBUF + i); };
+    auto l_empty = [&](int i) { return bars + 8u * (2 * NA + MERGE_SLOTS + 2 * L::NS + 2 * NUM_TBUF + NUM_LSE + i); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFF + 4);
     float2* merge_buf = reinterpret_cast<float2*>(smem + L::MERGE_OFF);
@@ -161,7 +164,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), 1); }
+        for (int i = 0; i < NA; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), 1); }
         for (int i = 0; i < L::NS; ++i) { mbar_init(b_full(i), 1); mbar_init(b_empty(i), 1); }
         for (int i = 0; i < NUM_TBUF; ++i) { mbar_init(t_full(i), 1); mbar_init(t_empty(i), CONSUMER_THREADS); }
         for (int i = 0; i < MERGE_SLOTS; ++i) mbar_init(merge_bar(i), CONSUMER_THREADS);
@@ -219,9 +222,10 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             long long held[L::NS];
 #pragma unroll
             for (int i = 0; i < L::NS; ++i) held[i] = -1;
+            int cur_bh = -1, b_cnt = 0;   // (short query axes: the query block in shared memory)
             for (; ok && !it.done; it.next(p), ++a_cnt) {
-                const int ab = a_cnt & 1;
-                if (!wait_all(a_empty(ab), ((a_cnt >> 1) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
+                const int ab = a_cnt % NA;
+                if (!wait_all(a_empty(ab), ((a_cnt / NA) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
                 if (elect_one_sync()) {
                     mbar_arrive_expect_tx(a_full(ab), L::A_BYTES);
 #pragma unroll
@@ -233,6 +237,25 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 if constexpr (MODE == MODE_COLSUM)
                     lse_src = p.neg_lse + ((long long)it.b * p.H + it.h) * p.lse_rows;
                 const int bh = it.b * p.H + it.h;
+                if constexpr (L::SHORT) {
+                    // one query block per (batch, head), loaded when the head changes; the key
+                    // tiles above are what runs ahead, as far as their ring is deep
+                    if (bh != cur_bh) {
+                        if (!wait_all(b_empty(0), (b_cnt & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
+                        if (elect_one_sync()) {
+                            mbar_arrive_expect_tx(b_full(0), L::B_STAGE_BYTES);
+#pragma unroll
+                            for (int sl = 0; sl < L::SLABS; ++sl)
+                                tma_load_4d(b_smem + sl * L::B_SLAB_BYTES, &tm_b, b_full(0), sl * 64, it.b_row(0),
+                                            it.h, it.b);
+                            tma_load_3d(b_smem + L::B_BYTES, &tm_ext, b_full(0), 0, it.b_row(0), bh);
+                        }
+                        __syncwarp();
+                        ++b_cnt;
+                        cur_bh = bh;
+                    }
+                    continue;
+                }
                 for (int st = it.s0; st < it.s1; ++st, ++n) {
                     if (!wait_all(b_empty(stage), phase ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
                     const long long block_id = ((long long)bh << 32) | (unsigned)st;
@@ -275,12 +298,27 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             int a_cnt = 0, stage = 0, n = 0;
             uint32_t phase = 0;
             bool ok = true;
+            int cur_bh = -1, b_cnt = 0;
             for (; ok && !it.done; it.next(p), ++a_cnt) {
-                const int ab = a_cnt & 1;
-                if (!wait_all(a_full(ab), (a_cnt >> 1) & 1, FCS_STATUS_WAIT_MMA)) break;
+                const int ab = a_cnt % NA;
+                if constexpr (L::SHORT) {
+                    const int bh = it.b * p.H + it.h;
+                    if (bh != cur_bh) {
+                        // the MMAs of the head before this one have read its query block: hand
+                        // the buffer back, then wait for this head's block
+                        if (cur_bh >= 0 && elect_one_sync()) umma_commit(b_empty(0));
+                        __syncwarp();
+                        if (!wait_all(b_full(0), b_cnt & 1, FCS_STATUS_WAIT_MMA)) break;
+                        ++b_cnt;
+                        cur_bh = bh;
+                    }
+                }
+                if (!wait_all(a_full(ab), (a_cnt / NA) & 1, FCS_STATUS_WAIT_MMA)) break;
                 const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::A_BYTES);
                 for (int st = it.s0; st < it.s1; ++st, ++n) {
-                    if (!wait_all(b_full(stage), phase, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+                    if constexpr (!L::SHORT) {
+                        if (!wait_all(b_full(stage), phase, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+                    }
                     const int buf = n & (NUM_TBUF - 1);
                     if (!wait_all(t_empty(buf), ((n >> 1) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
                     tc_fence_after();
@@ -297,7 +335,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                         if constexpr (EXT)   // + (key-side constant) x (-(lse)/c parts of the queries)
                             umma_f16(d_tmem, umma_desc_k_sw32(smem_base + L::EXTA_OFF),
                                      umma_desc_k_sw32(b_smem + stage * L::B_STAGE_BYTES + L::B_BYTES), p.idesc, 1u);
-                        umma_commit(b_empty(stage));
+                        if constexpr (!L::SHORT) umma_commit(b_empty(stage));
                         umma_commit(t_full(buf));
                         if (st + 1 == it.s1) umma_commit(a_empty(ab));
                     }
@@ -392,7 +430,23 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     }
                 } else if constexpr (EXT) {
                     // the accumulator already holds s - lse/c
-                    if (full) {
+                    const int blk_end = colsum_end_visible(p, st);
+                    if (blk_end <= BLOCK / 2) {
+                        // at most 128 query columns in this block (short query axes, the ragged end
+                        // of long ones): the four groups take 32 columns each, not two of them 64
+                        const int c0 = wg * (GROUP_COLS / 2);
+                        const int end = blk_end - c0;
+                        const int thr = colsum_first_visible(p, it.kt, st, row) - c0;
+                        const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - c0;
+                        const int thr_last_row = colsum_first_visible(p, it.kt, st, TILE - 1) - c0;
+                        if (end > 0 && thr_first_row < GROUP_COLS / 2) {
+                            uint32_t r[32];
+                            tmem_ld_x32(taddr - col0 + c0, r);
+                            tmem_ld_wait(r);
+                            if (end >= GROUP_COLS / 2 && thr_last_row <= 0) colsum_chunk_ext<false>(r, 0, 32, c, acc);
+                            else colsum_chunk_ext<true>(r, thr, end, c, acc);
+                        }
+                    } else if (full) {
                         colsum_tile_ext<false>(taddr, 0, GROUP_COLS, c, acc);
                     } else {
                         const int thr = colsum_first_visible(p, it.kt, st, row) - col0;
@@ -407,7 +461,19 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     const float4* nl = reinterpret_cast<const float4*>(smem + L::LSE_OFF + ls * BLOCK * 4) + col0 / 4;
-                    if (full) {
+                    const int blk_end = colsum_end_visible(p, st);
+                    if (blk_end <= BLOCK / 2) {   // 32 columns per group, as above
+                        const int c0 = wg * (GROUP_COLS / 2);
+                        const int end = blk_end - c0;
+                        const int thr = colsum_first_visible(p, it.kt, st, row) - c0;
+                        const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - c0;
+                        if (end > 0 && thr_first_row < GROUP_COLS / 2) {
+                            uint32_t r[32];
+                            tmem_ld_x32(taddr - col0 + c0, r);
+                            tmem_ld_wait(r);
+                            colsum_chunk<true>(r, nl - col0 / 4 + c0 / 4, thr, end, c, acc);
+                        }
+                    } else if (full) {
                         colsum_tile<false>(taddr, nl, 0, GROUP_COLS, c, acc);
                     } else {
                         const int thr = colsum_first_visible(p, it.kt, st, row) - col0;
@@ -953,7 +1019,13 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
         return FCS_OK;
     }
     const bool chained = !tm && passes == PASSES_BOTH;   // directly behind a kernel of this call
-    if (use_ext)
+    // a query axis of at most 128 rows fills half a streamed block: the MMAs need N = 128 only
+    if (Sq <= BLOCK / 2)
+        p.idesc = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((BLOCK / 2) >> 3) << 17);
+    if (use_ext && p.col_interleave == COL_HEAD_MAJOR)   // one query block per head, many key tiles: the key tiles stream
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT>(tk_a, tq_b, text, p, grid2, stream, chained)
+                      : launch_stream<128, MODE_COLSUM_EXT_SHORT>(tk_a, tq_b, text, p, grid2, stream, chained);
+    else if (use_ext)
         e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, chained);
     else

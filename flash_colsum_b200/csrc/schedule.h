@@ -24,7 +24,11 @@ constexpr int TILE = 128;      // rows of the resident operand tile (MMA M)
 constexpr int BLOCK = 256;     // rows of the streamed operand block (MMA N)
 constexpr int MAX_SPLIT = 64;  // most key ranges a query tile is split into
 
-enum : int { MODE_STATS = 0, MODE_COLSUM = 1, MODE_COLSUM_EXT = 2 };
+// MODE_COLSUM_EXT_SHORT: the column pass of a query axis that fits one streamed block --
+// every item is a single step, so the key tiles are what streams: deep ring for them, one stage for the queries
+enum : int { MODE_STATS = 0, MODE_COLSUM = 1, MODE_COLSUM_EXT = 2, MODE_COLSUM_EXT_SHORT = 3 };
+// values of Problem::col_interleave (how the column pass deals out its work, see ColsumItems)
+enum : int { COL_CONTIGUOUS = 0, COL_INTERLEAVED = 1, COL_HEAD_MAJOR = 2 };
 
 struct Problem {
     int B, H, Sq, Sk;   // Sq: query rows that enter the mean
@@ -35,7 +39,7 @@ struct Problem {
     int clear_out;      // the statistics pass zeroes `out` before the column pass adds into it
     int nsplit;         // key ranges per (b, h, query tile) in the statistics pass
     int kreg;           // leading key tiles that every query block contributes to
-    int col_interleave; // column pass: (b, h, key tile) chunks dealt round-robin instead of one contiguous range per CTA
+    int col_interleave; // column pass: COL_CONTIGUOUS steps, or (b, h, key tile) chunks dealt round-robin / in contiguous runs
     int col_parts;      // ... each cut into this many query-block ranges
     long long stats_items;
     long long steps_per_batch;  // column pass: steps of one batch entry
@@ -177,16 +181,18 @@ struct StatsItems {
 // -- with contiguous ranges every CTA is in a different place and the working set is
 // all heads at once (measured at B=1 H=16 S=32768: 4.3 GB read from DRAM for 134 MB of
 // inputs).  Every chunk flushes.
+// Head-major (a query axis of one block, many key tiles): the same chunk list, a
+// contiguous run of it per CTA -- the CTA stays with one head for as long as possible,
+// keeps that head's only query block in shared memory and streams key tiles.
 struct ColsumItems {
     bool done, flush_;
     int b, h, kt, s0, s1, qlo;        // steps = query blocks s0..s1-1
     long long s, s_end;
-    long long chunk;                  // interleaved mode: current chunk and the stride to the next
+    long long chunk, chunk_end;       // chunk modes: current chunk, end of the CTA's chunks, stride to the next
     int stride;
 
     FCS_HD void load_chunk(const Problem& p) {
-        const long long total = (long long)p.B * p.H * p.NKC * p.col_parts;
-        for (; chunk < total; chunk += stride) {
+        for (; chunk < chunk_end; chunk += stride) {
             const int part = (int)(chunk % p.col_parts);
             long long item = chunk / p.col_parts;
             kt = (int)(item % p.NKC);
@@ -215,6 +221,12 @@ struct ColsumItems {
         s = s_end = 0;
         chunk = cta;
         stride = grid;
+        chunk_end = (long long)p.B * p.H * p.NKC * p.col_parts;
+        if (p.col_interleave == COL_HEAD_MAJOR) {   // a contiguous run of the (b, h, key tile) list
+            chunk = chunk_end * cta / grid;
+            chunk_end = chunk_end * (cta + 1) / grid;
+            stride = 1;
+        }
         if (p.col_interleave) {
             done = false;
             load_chunk(p);
@@ -250,6 +262,16 @@ struct ColsumItems {
         cut(p);
     }
     FCS_HD void next(const Problem& p) {
+        if (p.col_interleave == COL_HEAD_MAJOR) {
+            // one step per chunk (a single query block, never cut into parts): walk on without
+            // the divisions of load_chunk, which would cost more than the step itself
+            if (++chunk >= chunk_end) { done = true; return; }
+            if (++kt >= p.NKC) {
+                kt = 0;
+                if (++h >= p.H) { h = 0; ++b; }
+            }
+            return;
+        }
         if (p.col_interleave) {
             chunk += stride;
             load_chunk(p);
@@ -276,6 +298,7 @@ template <int MODE> struct ItemsOf;
 template <> struct ItemsOf<MODE_STATS> { typedef StatsItems type; };
 template <> struct ItemsOf<MODE_COLSUM> { typedef ColsumItems type; };
 template <> struct ItemsOf<MODE_COLSUM_EXT> { typedef ColsumItems type; };
+template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT> { typedef ColsumItems type; };
 
 // ---------------------------------------------------------------------------
 // Planning (host): fills the shape-derived fields of `p`.
@@ -284,6 +307,7 @@ template <> struct ItemsOf<MODE_COLSUM_EXT> { typedef ColsumItems type; };
 // the rows and their extension columns (up to 288 bytes each) then exceed what the L2
 // keeps for data that every SM reads.
 constexpr long long COL_INTERLEAVE_MIN_ROWS = 300000;
+constexpr int COL_HEAD_MAJOR_MIN_TILES = 16;   // key tiles per head from which the head-major order is used
 
 inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_past, int sms,
                  long long interleave_min_rows = COL_INTERLEAVE_MIN_ROWS) {
@@ -336,6 +360,10 @@ inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_pas
     long long parts = items >= 8ll * sms ? 1 : (8ll * sms + items - 1) / items;
     if (parts > p.NQB) parts = p.NQB;
     p.col_parts = (int)parts;
+    if (p.NQB == 1 && p.NKC >= COL_HEAD_MAJOR_MIN_TILES) {
+        p.col_interleave = COL_HEAD_MAJOR;
+        p.col_parts = 1;
+    }
 }
 
 // ---------------------------------------------------------------------------

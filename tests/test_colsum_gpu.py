@@ -75,6 +75,11 @@ SHAPES = [
     (1, 2, 513, 3000, 128, "bf16", True, None),
     (1, 2, 300, 100, 64, "fp16", True, None),        # keys shorter than queries
     (2, 2, 640, 640, 64, "fp16", False, 130),        # cls prefix spanning two query tiles
+    # one query block, sixteen or more key tiles: the column pass streams key tiles head by head
+    (1, 5, 100, 2500, 64, "bf16", True, None),
+    (1, 3, 256, 3000, 128, "fp16", True, None),
+    (2, 4, 2100, 2100, 64, "fp16", False, 200),
+    (1, 40, 70, 2200, 128, "bf16", True, None),      # a head change every few tiles
 ]
 
 
@@ -336,7 +341,8 @@ def test_batched_causal_and_explicit_k_past(fc):
     but its operator does not offer."""
     from oracle.naive_colsum import naive_colsum_f64
     # batch of three, ragged sizes, both head dimensions
-    for (B, H, Sq, Sk, D, dtype) in [(3, 2, 200, 500, 64, "bf16"), (2, 3, 128, 1024, 128, "fp16")]:
+    for (B, H, Sq, Sk, D, dtype) in [(3, 2, 200, 500, 64, "bf16"), (2, 3, 128, 1024, 128, "fp16"),
+                                     (3, 2, 130, 2300, 64, "fp16")]:
         w = Workload("bc", B, H, Sq, Sk, D, dtype, is_causal=True, seed=Sq + Sk)
         q, k = make_inputs(w)
         got = fc.flash_colsum_causal(q.cuda(), k.cuda()).cpu().numpy()

@@ -70,6 +70,10 @@ CASES = [
     (1, 2, 300, 700, 8, True, None, 3),
     (1, 1, 260, 2000, 4, True, None, 148),
     (1, 2, 129, 129, 8, True, None, 2),
+    # one query block and sixteen or more key tiles: contiguous runs of the (b, h, key tile) list
+    (1, 3, 128, 2300, 8, True, None, 148),
+    (2, 2, 100, 2100, 8, True, None, 5),        # runs cut through heads and batch entries
+    (1, 2, 2100, 2100, 4, False, 200, 7),
 ]
 
 
