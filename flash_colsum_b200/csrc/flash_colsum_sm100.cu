@@ -223,16 +223,21 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 #pragma unroll
             for (int i = 0; i < L::NS; ++i) held[i] = -1;
             int cur_bh = -1, b_cnt = 0;   // (short query axes: the query block in shared memory)
-            for (; ok && !it.done; it.next(p), ++a_cnt) {
-                const int ab = a_cnt % NA;
-                if (!wait_all(a_empty(ab), ((a_cnt / NA) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
-                if (elect_one_sync()) {
-                    mbar_arrive_expect_tx(a_full(ab), L::A_BYTES);
+            for (; ok && !it.done; it.next(p)) {
+                // the item's resident tile(s): one, or in the short-query mode up to two key tiles
+                const int tiles = L::SHORT ? it.nt : 1;
+                for (int t = 0; t < tiles; ++t, ++a_cnt) {
+                    const int ab = a_cnt % NA;
+                    if (!wait_all(a_empty(ab), ((a_cnt / NA) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
+                    if (elect_one_sync()) {
+                        mbar_arrive_expect_tx(a_full(ab), L::A_BYTES);
 #pragma unroll
-                    for (int sl = 0; sl < L::SLABS; ++sl)
-                        tma_load_4d(a_smem + ab * L::A_BYTES + sl * L::A_SLAB_BYTES, &tm_a, a_full(ab),
-                                    sl * 64, it.a_row(), it.h, it.b);
+                        for (int sl = 0; sl < L::SLABS; ++sl)
+                            tma_load_4d(a_smem + ab * L::A_BYTES + sl * L::A_SLAB_BYTES, &tm_a, a_full(ab),
+                                        sl * 64, it.a_row() + t * TILE, it.h, it.b);
+                    }
                 }
+                if (!ok) break;
                 const float* lse_src = nullptr;
                 if constexpr (MODE == MODE_COLSUM)
                     lse_src = p.neg_lse + ((long long)it.b * p.H + it.h) * p.lse_rows;
@@ -299,8 +304,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             uint32_t phase = 0;
             bool ok = true;
             int cur_bh = -1, b_cnt = 0;
-            for (; ok && !it.done; it.next(p), ++a_cnt) {
-                const int ab = a_cnt % NA;
+            for (; ok && !it.done; it.next(p), a_cnt += L::SHORT ? 0 : 1) {
                 if constexpr (L::SHORT) {
                     const int bh = it.b * p.H + it.h;
                     if (bh != cur_bh) {
@@ -312,7 +316,34 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                         ++b_cnt;
                         cur_bh = bh;
                     }
+                    // one step: the item's key tiles side by side in one accumulator buffer
+                    const int buf = n & (NUM_TBUF - 1);
+                    if (!wait_all(t_empty(buf), ((n >> 1) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) break;
+                    const uint64_t db = umma_desc_k_sw128(b_smem);
+                    for (int t = 0; t < it.nt; ++t, ++a_cnt) {
+                        const int ab = a_cnt % NA;
+                        if (!wait_all(a_full(ab), (a_cnt / NA) & 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::A_BYTES);
+                        const uint32_t d_tmem = tmem_base + buf * BLOCK + t * (BLOCK / 2);
+                        if (elect_one_sync()) {
+#pragma unroll
+                            for (int ks = 0; ks < D / 16; ++ks) {
+                                const uint64_t oa = (uint64_t)(((ks >> 2) * L::A_SLAB_BYTES + (ks & 3) * 32) >> 4);
+                                const uint64_t ob = (uint64_t)(((ks >> 2) * L::B_SLAB_BYTES + (ks & 3) * 32) >> 4);
+                                umma_f16(d_tmem, da + oa, db + ob, p.idesc, ks > 0 ? 1u : 0u);
+                            }
+                            umma_f16(d_tmem, umma_desc_k_sw32(smem_base + L::EXTA_OFF),
+                                     umma_desc_k_sw32(b_smem + L::B_BYTES), p.idesc, 1u);
+                            umma_commit(a_empty(ab));
+                            if (t + 1 == it.nt) umma_commit(t_full(buf));
+                        }
+                        __syncwarp();
+                    }
+                    ++n;
+                    continue;
                 }
+                const int ab = a_cnt % NA;
                 if (!wait_all(a_full(ab), (a_cnt / NA) & 1, FCS_STATUS_WAIT_MMA)) break;
                 const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::A_BYTES);
                 for (int st = it.s0; st < it.s1; ++st, ++n) {
@@ -431,7 +462,23 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 } else if constexpr (EXT) {
                     // the accumulator already holds s - lse/c
                     const int blk_end = colsum_end_visible(p, st);
-                    if (blk_end <= BLOCK / 2) {
+                    if (L::SHORT && p.col_pack == 2) {
+                        // two key tiles in this accumulator buffer, 128 query columns each: groups
+                        // 0, 1 take the halves of the first tile's columns, groups 2, 3 the second's
+                        const int tg = wg >> 1;
+                        if (tg < it.nt) {
+                            const int ktg = it.kt + tg;
+                            const int q0 = (wg & 1) * GROUP_COLS;
+                            const int end = blk_end - q0;
+                            const int thr = colsum_first_visible(p, ktg, st, row) - q0;
+                            const int thr_first_row = colsum_first_visible(p, ktg, st, 0) - q0;
+                            const int thr_last_row = colsum_first_visible(p, ktg, st, TILE - 1) - q0;
+                            if (end > 0 && thr_first_row < GROUP_COLS) {
+                                if (end >= GROUP_COLS && thr_last_row <= 0) colsum_tile_ext<false>(taddr, 0, GROUP_COLS, c, acc);
+                                else colsum_tile_ext<true>(taddr, thr, end, c, acc);
+                            }
+                        }
+                    } else if (blk_end <= BLOCK / 2) {
                         // at most 128 query columns in this block (short query axes, the ragged end
                         // of long ones): the four groups take 32 columns each, not two of them 64
                         const int c0 = wg * (GROUP_COLS / 2);
@@ -506,8 +553,10 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 m_run = -INFINITY; l_run = 0.f;
             } else {
                 if (it.flush()) {
-                    const int k_abs = it.kt * TILE + row;
-                    if (k_abs < p.Sk)
+                    // (two key tiles per item: this group's tile is the first or the second)
+                    const int tg = (L::SHORT && p.col_pack == 2) ? (wg >> 1) : 0;
+                    const int k_abs = (it.kt + tg) * TILE + row;
+                    if (k_abs < p.Sk && tg < it.nt)
                         // system scope: `out` may live on another GPU and take adds from several
                         atomicAdd_system(p.out + (long long)it.b * p.out_ld + k_abs,
                                          (acc[0] + acc[1]) + (acc[2] + acc[3]));
@@ -977,7 +1026,10 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if (use_ext && (rc = make_ext_tensor_map(&text, p.ext, dtype, (long long)B * H, p.lse_rows)) != FCS_OK) return rc;
 
     const int grid1 = (int)(p.stats_items < sms ? p.stats_items : sms);
-    const int grid2 = (int)(p.steps_total < sms ? p.steps_total : sms);
+    if (!use_ext) p.col_pack = 1;   // (the kernel without the extension columns takes one key tile per item)
+    long long col_items = p.steps_total;
+    if (p.col_interleave == COL_HEAD_MAJOR) col_items = (long long)B * H * ceil_div(p.NKC, p.col_pack);
+    const int grid2 = (int)(col_items < sms ? col_items : sms);
     PassTimers* tm = g_profiling ? timers_for_current_device() : nullptr;
     if (tm) { tm->recorded = false; cudaEventRecord(tm->ev[0], stream); }
     cudaError_t e = cudaSuccess;

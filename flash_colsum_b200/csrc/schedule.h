@@ -41,6 +41,7 @@ struct Problem {
     int kreg;           // leading key tiles that every query block contributes to
     int col_interleave; // column pass: COL_CONTIGUOUS steps, or (b, h, key tile) chunks dealt round-robin / in contiguous runs
     int col_parts;      // ... each cut into this many query-block ranges
+    int col_pack;       // head-major order: key tiles per item (2 when the queries fill half an accumulator, else 1)
     long long stats_items;
     long long steps_per_batch;  // column pass: steps of one batch entry
     long long steps_total;
@@ -140,6 +141,7 @@ FCS_HD inline void colsum_full_range(const Problem& p, int kt, int& lo, int& hi)
 struct StatsItems {
     bool done;
     int b, h, qt, sp, s0, s1, grid;   // steps = key blocks s0..s1-1
+    static constexpr int nt = 1;      // resident tiles per item
     long long item;
 
     FCS_HD void load(const Problem& p) {
@@ -183,14 +185,30 @@ struct StatsItems {
 // inputs).  Every chunk flushes.
 // Head-major (a query axis of one block, many key tiles): the same chunk list, a
 // contiguous run of it per CTA -- the CTA stays with one head for as long as possible,
-// keeps that head's only query block in shared memory and streams key tiles.
+// keeps that head's only query block in shared memory and streams key tiles.  When the
+// queries fill at most half an accumulator (128 of its 256 columns), an item is two
+// key tiles, computed side by side, so that the per-item costs are paid half as often.
 struct ColsumItems {
     bool done, flush_;
     int b, h, kt, s0, s1, qlo;        // steps = query blocks s0..s1-1
+    int nt;                           // key tiles of the item (head-major order: up to col_pack), from kt on
     long long s, s_end;
     long long chunk, chunk_end;       // chunk modes: current chunk, end of the CTA's chunks, stride to the next
     int stride;
 
+    // Head-major order: item `chunk` of the (b, h, group of col_pack key tiles) list.
+    FCS_HD void load_packed(const Problem& p) {
+        if (chunk >= chunk_end) { done = true; return; }
+        const int per_head = ceil_div(p.NKC, p.col_pack);
+        long long item = chunk;
+        kt = (int)(item % per_head) * p.col_pack;
+        item /= per_head;
+        h = (int)(item % p.H);
+        b = (int)(item / p.H);
+        nt = p.NKC - kt < p.col_pack ? p.NKC - kt : p.col_pack;
+        qlo = 0; s0 = 0; s1 = 1;
+        flush_ = true;
+    }
     FCS_HD void load_chunk(const Problem& p) {
         for (; chunk < chunk_end; chunk += stride) {
             const int part = (int)(chunk % p.col_parts);
@@ -222,10 +240,15 @@ struct ColsumItems {
         chunk = cta;
         stride = grid;
         chunk_end = (long long)p.B * p.H * p.NKC * p.col_parts;
-        if (p.col_interleave == COL_HEAD_MAJOR) {   // a contiguous run of the (b, h, key tile) list
-            chunk = chunk_end * cta / grid;
-            chunk_end = chunk_end * (cta + 1) / grid;
+        nt = 1;
+        if (p.col_interleave == COL_HEAD_MAJOR) {   // a contiguous run of the (b, h, key tiles) list
+            const long long all = (long long)p.B * p.H * ceil_div(p.NKC, p.col_pack);
+            chunk = all * cta / grid;
+            chunk_end = all * (cta + 1) / grid;
             stride = 1;
+            done = false;
+            load_packed(p);
+            return;
         }
         if (p.col_interleave) {
             done = false;
@@ -266,10 +289,12 @@ struct ColsumItems {
             // one step per chunk (a single query block, never cut into parts): walk on without
             // the divisions of load_chunk, which would cost more than the step itself
             if (++chunk >= chunk_end) { done = true; return; }
-            if (++kt >= p.NKC) {
+            kt += p.col_pack;
+            if (kt >= p.NKC) {
                 kt = 0;
                 if (++h >= p.H) { h = 0; ++b; }
             }
+            nt = p.NKC - kt < p.col_pack ? p.NKC - kt : p.col_pack;
             return;
         }
         if (p.col_interleave) {
@@ -360,9 +385,11 @@ inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_pas
     long long parts = items >= 8ll * sms ? 1 : (8ll * sms + items - 1) / items;
     if (parts > p.NQB) parts = p.NQB;
     p.col_parts = (int)parts;
+    p.col_pack = 1;
     if (p.NQB == 1 && p.NKC >= COL_HEAD_MAJOR_MIN_TILES) {
         p.col_interleave = COL_HEAD_MAJOR;
         p.col_parts = 1;
+        if (Sq <= BLOCK / 2) p.col_pack = 2;   // two key tiles side by side in one accumulator
     }
 }
 
