@@ -222,29 +222,25 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             long long held[L::NS];
 #pragma unroll
             for (int i = 0; i < L::NS; ++i) held[i] = -1;
-            int cur_bh = -1, b_cnt = 0;   // (short query axes: the query block in shared memory)
-            for (; ok && !it.done; it.next(p)) {
-                // the item's resident tile(s): one, or in the short-query mode up to two key tiles
-                const int tiles = L::SHORT ? it.nt : 1;
-                for (int t = 0; t < tiles; ++t, ++a_cnt) {
-                    const int ab = a_cnt % NA;
-                    if (!wait_all(a_empty(ab), ((a_cnt / NA) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
-                    if (elect_one_sync()) {
-                        mbar_arrive_expect_tx(a_full(ab), L::A_BYTES);
+            if constexpr (L::SHORT) {
+                // Short query axis: an item is one or two key tiles against the head's only query
+                // block.  The key tiles run ahead as far as their ring is deep; the query block
+                // is loaded when the head changes.
+                int cur_bh = -1, b_cnt = 0;
+                for (; ok && !it.done; it.next(p)) {
+                    for (int t = 0; t < it.nt; ++t, ++a_cnt) {
+                        const int ab = a_cnt % NA;
+                        if (!wait_all(a_empty(ab), ((a_cnt / NA) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
+                        if (elect_one_sync()) {
+                            mbar_arrive_expect_tx(a_full(ab), L::A_BYTES);
 #pragma unroll
-                        for (int sl = 0; sl < L::SLABS; ++sl)
-                            tma_load_4d(a_smem + ab * L::A_BYTES + sl * L::A_SLAB_BYTES, &tm_a, a_full(ab),
-                                        sl * 64, it.a_row() + t * TILE, it.h, it.b);
+                            for (int sl = 0; sl < L::SLABS; ++sl)
+                                tma_load_4d(a_smem + ab * L::A_BYTES + sl * L::A_SLAB_BYTES, &tm_a, a_full(ab),
+                                            sl * 64, it.a_row() + t * TILE, it.h, it.b);
+                        }
                     }
-                }
-                if (!ok) break;
-                const float* lse_src = nullptr;
-                if constexpr (MODE == MODE_COLSUM)
-                    lse_src = p.neg_lse + ((long long)it.b * p.H + it.h) * p.lse_rows;
-                const int bh = it.b * p.H + it.h;
-                if constexpr (L::SHORT) {
-                    // one query block per (batch, head), loaded when the head changes; the key
-                    // tiles above are what runs ahead, as far as their ring is deep
+                    if (!ok) break;
+                    const int bh = it.b * p.H + it.h;
                     if (bh != cur_bh) {
                         if (!wait_all(b_empty(0), (b_cnt & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
                         if (elect_one_sync()) {
@@ -259,8 +255,22 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                         ++b_cnt;
                         cur_bh = bh;
                     }
-                    continue;
                 }
+            } else {
+            for (; ok && !it.done; it.next(p), ++a_cnt) {
+                const int ab = a_cnt & 1;
+                if (!wait_all(a_empty(ab), ((a_cnt >> 1) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
+                if (elect_one_sync()) {
+                    mbar_arrive_expect_tx(a_full(ab), L::A_BYTES);
+#pragma unroll
+                    for (int sl = 0; sl < L::SLABS; ++sl)
+                        tma_load_4d(a_smem + ab * L::A_BYTES + sl * L::A_SLAB_BYTES, &tm_a, a_full(ab),
+                                    sl * 64, it.a_row(), it.h, it.b);
+                }
+                const float* lse_src = nullptr;
+                if constexpr (MODE == MODE_COLSUM)
+                    lse_src = p.neg_lse + ((long long)it.b * p.H + it.h) * p.lse_rows;
+                const int bh = it.b * p.H + it.h;
                 for (int st = it.s0; st < it.s1; ++st, ++n) {
                     if (!wait_all(b_empty(stage), phase ^ 1, FCS_STATUS_WAIT_PRODUCER)) { ok = false; break; }
                     const long long block_id = ((long long)bh << 32) | (unsigned)st;
@@ -296,6 +306,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     if (++stage == L::NS) { stage = 0; phase ^= 1; }
                 }
             }
+            }
         } else if (warp == MMA_WARP) {
             // -------------------------------------------- MMA issuer
             Items it;
@@ -303,9 +314,9 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             int a_cnt = 0, stage = 0, n = 0;
             uint32_t phase = 0;
             bool ok = true;
-            int cur_bh = -1, b_cnt = 0;
-            for (; ok && !it.done; it.next(p), a_cnt += L::SHORT ? 0 : 1) {
-                if constexpr (L::SHORT) {
+            if constexpr (L::SHORT) {
+                int cur_bh = -1, b_cnt = 0;
+                for (; ok && !it.done; it.next(p), ++n) {
                     const int bh = it.b * p.H + it.h;
                     if (bh != cur_bh) {
                         // the MMAs of the head before this one have read its query block: hand
@@ -340,16 +351,14 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                         }
                         __syncwarp();
                     }
-                    ++n;
-                    continue;
                 }
-                const int ab = a_cnt % NA;
-                if (!wait_all(a_full(ab), (a_cnt / NA) & 1, FCS_STATUS_WAIT_MMA)) break;
+            } else {
+            for (; ok && !it.done; it.next(p), ++a_cnt) {
+                const int ab = a_cnt & 1;
+                if (!wait_all(a_full(ab), (a_cnt >> 1) & 1, FCS_STATUS_WAIT_MMA)) break;
                 const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::A_BYTES);
                 for (int st = it.s0; st < it.s1; ++st, ++n) {
-                    if constexpr (!L::SHORT) {
-                        if (!wait_all(b_full(stage), phase, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
-                    }
+                    if (!wait_all(b_full(stage), phase, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
                     const int buf = n & (NUM_TBUF - 1);
                     if (!wait_all(t_empty(buf), ((n >> 1) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
                     tc_fence_after();
@@ -366,13 +375,14 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                         if constexpr (EXT)   // + (key-side constant) x (-(lse)/c parts of the queries)
                             umma_f16(d_tmem, umma_desc_k_sw32(smem_base + L::EXTA_OFF),
                                      umma_desc_k_sw32(b_smem + stage * L::B_STAGE_BYTES + L::B_BYTES), p.idesc, 1u);
-                        if constexpr (!L::SHORT) umma_commit(b_empty(stage));
+                        umma_commit(b_empty(stage));
                         umma_commit(t_full(buf));
                         if (st + 1 == it.s1) umma_commit(a_empty(ab));
                     }
                     __syncwarp();
                     if (++stage == L::NS) { stage = 0; phase ^= 1; }
                 }
+            }
             }
         }
     } else {
@@ -461,46 +471,55 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     }
                 } else if constexpr (EXT) {
                     // the accumulator already holds s - lse/c
-                    const int blk_end = colsum_end_visible(p, st);
-                    if (L::SHORT && p.col_pack == 2) {
-                        // two key tiles in this accumulator buffer, 128 query columns each: groups
-                        // 0, 1 take the halves of the first tile's columns, groups 2, 3 the second's
-                        const int tg = wg >> 1;
-                        if (tg < it.nt) {
-                            const int ktg = it.kt + tg;
-                            const int q0 = (wg & 1) * GROUP_COLS;
-                            const int end = blk_end - q0;
-                            const int thr = colsum_first_visible(p, ktg, st, row) - q0;
-                            const int thr_first_row = colsum_first_visible(p, ktg, st, 0) - q0;
-                            const int thr_last_row = colsum_first_visible(p, ktg, st, TILE - 1) - q0;
-                            if (end > 0 && thr_first_row < GROUP_COLS) {
-                                if (end >= GROUP_COLS && thr_last_row <= 0) colsum_tile_ext<false>(taddr, 0, GROUP_COLS, c, acc);
-                                else colsum_tile_ext<true>(taddr, thr, end, c, acc);
-                            }
-                        }
-                    } else if (blk_end <= BLOCK / 2) {
-                        // at most 128 query columns in this block (short query axes, the ragged end
-                        // of long ones): the four groups take 32 columns each, not two of them 64
-                        const int c0 = wg * (GROUP_COLS / 2);
-                        const int end = blk_end - c0;
-                        const int thr = colsum_first_visible(p, it.kt, st, row) - c0;
-                        const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - c0;
-                        const int thr_last_row = colsum_first_visible(p, it.kt, st, TILE - 1) - c0;
-                        if (end > 0 && thr_first_row < GROUP_COLS / 2) {
-                            uint32_t r[32];
-                            tmem_ld_x32(taddr - col0 + c0, r);
-                            tmem_ld_wait(r);
-                            if (end >= GROUP_COLS / 2 && thr_last_row <= 0) colsum_chunk_ext<false>(r, 0, 32, c, acc);
-                            else colsum_chunk_ext<true>(r, thr, end, c, acc);
-                        }
-                    } else if (full) {
+                    if (full) {
                         colsum_tile_ext<false>(taddr, 0, GROUP_COLS, c, acc);
                     } else {
-                        const int thr = colsum_first_visible(p, it.kt, st, row) - col0;
-                        const int end = colsum_end_visible(p, st) - col0;
-                        // skip the block when no key of the tile is seen by any of its queries
-                        const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - col0;
-                        if (end > 0 && thr_first_row < GROUP_COLS) colsum_tile_ext<true>(taddr, thr, end, c, acc);
+                        bool done_short = false;
+                        if constexpr (L::SHORT) {
+                            if (p.col_pack == 2) {
+                                // two key tiles in this accumulator buffer, 128 query columns each: groups
+                                // 0, 1 take the halves of the first tile's columns, groups 2, 3 the second's
+                                done_short = true;
+                                const int tg = wg >> 1;
+                                if (tg < it.nt) {
+                                    const int ktg = it.kt + tg;
+                                    const int q0 = (wg & 1) * GROUP_COLS;
+                                    const int end = colsum_end_visible(p, st) - q0;
+                                    const int thr = colsum_first_visible(p, ktg, st, row) - q0;
+                                    const int thr_first_row = colsum_first_visible(p, ktg, st, 0) - q0;
+                                    const int thr_last_row = colsum_first_visible(p, ktg, st, TILE - 1) - q0;
+                                    if (end > 0 && thr_first_row < GROUP_COLS) {
+                                        if (end >= GROUP_COLS && thr_last_row <= 0)
+                                            colsum_tile_ext<false>(taddr, 0, GROUP_COLS, c, acc);
+                                        else
+                                            colsum_tile_ext<true>(taddr, thr, end, c, acc);
+                                    }
+                                }
+                            } else if (colsum_end_visible(p, st) <= BLOCK / 2) {
+                                // at most 128 query columns, one key tile per item: the four groups take
+                                // 32 columns each, not two of them 64
+                                done_short = true;
+                                const int c0 = wg * (GROUP_COLS / 2);
+                                const int end = colsum_end_visible(p, st) - c0;
+                                const int thr = colsum_first_visible(p, it.kt, st, row) - c0;
+                                const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - c0;
+                                const int thr_last_row = colsum_first_visible(p, it.kt, st, TILE - 1) - c0;
+                                if (end > 0 && thr_first_row < GROUP_COLS / 2) {
+                                    uint32_t r[32];
+                                    tmem_ld_x32(taddr - col0 + c0, r);
+                                    tmem_ld_wait(r);
+                                    if (end >= GROUP_COLS / 2 && thr_last_row <= 0) colsum_chunk_ext<false>(r, 0, 32, c, acc);
+                                    else colsum_chunk_ext<true>(r, thr, end, c, acc);
+                                }
+                            }
+                        }
+                        if (!done_short) {
+                            const int thr = colsum_first_visible(p, it.kt, st, row) - col0;
+                            const int end = colsum_end_visible(p, st) - col0;
+                            // skip the block when no key of the tile is seen by any of its queries
+                            const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - col0;
+                            if (end > 0 && thr_first_row < GROUP_COLS) colsum_tile_ext<true>(taddr, thr, end, c, acc);
+                        }
                     }
                 } else {
                     const int ls = n & (NUM_LSE - 1);
@@ -508,19 +527,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     const float4* nl = reinterpret_cast<const float4*>(smem + L::LSE_OFF + ls * BLOCK * 4) + col0 / 4;
-                    const int blk_end = colsum_end_visible(p, st);
-                    if (blk_end <= BLOCK / 2) {   // 32 columns per group, as above
-                        const int c0 = wg * (GROUP_COLS / 2);
-                        const int end = blk_end - c0;
-                        const int thr = colsum_first_visible(p, it.kt, st, row) - c0;
-                        const int thr_first_row = colsum_first_visible(p, it.kt, st, 0) - c0;
-                        if (end > 0 && thr_first_row < GROUP_COLS / 2) {
-                            uint32_t r[32];
-                            tmem_ld_x32(taddr - col0 + c0, r);
-                            tmem_ld_wait(r);
-                            colsum_chunk<true>(r, nl - col0 / 4 + c0 / 4, thr, end, c, acc);
-                        }
-                    } else if (full) {
+                    if (full) {
                         colsum_tile<false>(taddr, nl, 0, GROUP_COLS, c, acc);
                     } else {
                         const int thr = colsum_first_visible(p, it.kt, st, row) - col0;
@@ -554,9 +561,13 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             } else {
                 if (it.flush()) {
                     // (two key tiles per item: this group's tile is the first or the second)
-                    const int tg = (L::SHORT && p.col_pack == 2) ? (wg >> 1) : 0;
+                    int tg = 0;
+                    bool mine = true;
+                    if constexpr (L::SHORT) {
+                        if (p.col_pack == 2) { tg = wg >> 1; mine = tg < it.nt; }
+                    }
                     const int k_abs = (it.kt + tg) * TILE + row;
-                    if (k_abs < p.Sk && tg < it.nt)
+                    if (k_abs < p.Sk && mine)
                         // system scope: `out` may live on another GPU and take adds from several
                         atomicAdd_system(p.out + (long long)it.b * p.out_ld + k_abs,
                                          (acc[0] + acc[1]) + (acc[2] + acc[3]));
@@ -972,9 +983,12 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     }
 
     const int sms = num_sms();
+    // -(lse) rides in the MMA of the column pass unless the scale is so small that
+    // -(lse)/c leaves the range of its 16-bit parts
+    const bool use_ext = fabsf(scale) * 1.4426950408889634f >= 1e-4f;
     Problem p;
     memset(&p, 0, sizeof(p));
-    plan(p, B, H, Sq, Sk, causal, k_past, sms);
+    plan(p, B, H, Sq, Sk, causal, k_past, sms, COL_INTERLEAVE_MIN_ROWS, /*head_major_ok=*/use_ext);
     size_t part_off = 0, ext_off = 0;
     const size_t need = workspace_layout(p, &part_off, &ext_off);
     if (!workspace || workspace_bytes < need)
@@ -990,9 +1004,6 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     p.clear_out = (clear_out && passes == PASSES_BOTH) ? 1 : 0;   // (the statistics pass does the clearing)
     p.status = status;
     p.c = fabsf(scale) * 1.4426950408889634f;
-    // -(lse) rides in the MMA of the column pass unless the scale is so small that
-    // -(lse)/c leaves the range of its 16-bit parts
-    const bool use_ext = p.c >= 1e-4f;
     p.inv_c = use_ext ? (scale < 0.f ? -1.0f : 1.0f) / p.c : 0.f;
     p.log2_norm = log2f((float)h_norm * (float)(norm_rows > 0 ? norm_rows : Sq));
     const uint32_t fmt = dtype == FCS_DTYPE_BF16 ? 1u : 0u;
@@ -1026,7 +1037,6 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if (use_ext && (rc = make_ext_tensor_map(&text, p.ext, dtype, (long long)B * H, p.lse_rows)) != FCS_OK) return rc;
 
     const int grid1 = (int)(p.stats_items < sms ? p.stats_items : sms);
-    if (!use_ext) p.col_pack = 1;   // (the kernel without the extension columns takes one key tile per item)
     long long col_items = p.steps_total;
     if (p.col_interleave == COL_HEAD_MAJOR) col_items = (long long)B * H * ceil_div(p.NKC, p.col_pack);
     const int grid2 = (int)(col_items < sms ? col_items : sms);

@@ -141,7 +141,6 @@ FCS_HD inline void colsum_full_range(const Problem& p, int kt, int& lo, int& hi)
 struct StatsItems {
     bool done;
     int b, h, qt, sp, s0, s1, grid;   // steps = key blocks s0..s1-1
-    static constexpr int nt = 1;      // resident tiles per item
     long long item;
 
     FCS_HD void load(const Problem& p) {
@@ -183,34 +182,18 @@ struct StatsItems {
 // -- with contiguous ranges every CTA is in a different place and the working set is
 // all heads at once (measured at B=1 H=16 S=32768: 4.3 GB read from DRAM for 134 MB of
 // inputs).  Every chunk flushes.
-// Head-major (a query axis of one block, many key tiles): the same chunk list, a
-// contiguous run of it per CTA -- the CTA stays with one head for as long as possible,
-// keeps that head's only query block in shared memory and streams key tiles.  When the
-// queries fill at most half an accumulator (128 of its 256 columns), an item is two
-// key tiles, computed side by side, so that the per-item costs are paid half as often.
+// (A query axis of one block with many key tiles is dealt out a third way, head-major,
+// by PackedItems below.)
 struct ColsumItems {
     bool done, flush_;
     int b, h, kt, s0, s1, qlo;        // steps = query blocks s0..s1-1
-    int nt;                           // key tiles of the item (head-major order: up to col_pack), from kt on
     long long s, s_end;
-    long long chunk, chunk_end;       // chunk modes: current chunk, end of the CTA's chunks, stride to the next
+    long long chunk;                  // interleaved mode: current chunk and the stride to the next
     int stride;
 
-    // Head-major order: item `chunk` of the (b, h, group of col_pack key tiles) list.
-    FCS_HD void load_packed(const Problem& p) {
-        if (chunk >= chunk_end) { done = true; return; }
-        const int per_head = ceil_div(p.NKC, p.col_pack);
-        long long item = chunk;
-        kt = (int)(item % per_head) * p.col_pack;
-        item /= per_head;
-        h = (int)(item % p.H);
-        b = (int)(item / p.H);
-        nt = p.NKC - kt < p.col_pack ? p.NKC - kt : p.col_pack;
-        qlo = 0; s0 = 0; s1 = 1;
-        flush_ = true;
-    }
     FCS_HD void load_chunk(const Problem& p) {
-        for (; chunk < chunk_end; chunk += stride) {
+        const long long total = (long long)p.B * p.H * p.NKC * p.col_parts;
+        for (; chunk < total; chunk += stride) {
             const int part = (int)(chunk % p.col_parts);
             long long item = chunk / p.col_parts;
             kt = (int)(item % p.NKC);
@@ -239,17 +222,6 @@ struct ColsumItems {
         s = s_end = 0;
         chunk = cta;
         stride = grid;
-        chunk_end = (long long)p.B * p.H * p.NKC * p.col_parts;
-        nt = 1;
-        if (p.col_interleave == COL_HEAD_MAJOR) {   // a contiguous run of the (b, h, key tiles) list
-            const long long all = (long long)p.B * p.H * ceil_div(p.NKC, p.col_pack);
-            chunk = all * cta / grid;
-            chunk_end = all * (cta + 1) / grid;
-            stride = 1;
-            done = false;
-            load_packed(p);
-            return;
-        }
         if (p.col_interleave) {
             done = false;
             load_chunk(p);
@@ -285,18 +257,6 @@ struct ColsumItems {
         cut(p);
     }
     FCS_HD void next(const Problem& p) {
-        if (p.col_interleave == COL_HEAD_MAJOR) {
-            // one step per chunk (a single query block, never cut into parts): walk on without
-            // the divisions of load_chunk, which would cost more than the step itself
-            if (++chunk >= chunk_end) { done = true; return; }
-            kt += p.col_pack;
-            if (kt >= p.NKC) {
-                kt = 0;
-                if (++h >= p.H) { h = 0; ++b; }
-            }
-            nt = p.NKC - kt < p.col_pack ? p.NKC - kt : p.col_pack;
-            return;
-        }
         if (p.col_interleave) {
             chunk += stride;
             load_chunk(p);
@@ -319,11 +279,55 @@ struct ColsumItems {
     FCS_HD bool flush() const { return flush_; }
 };
 
+// Head-major order of the column pass (a query axis of one block, sixteen or more key
+// tiles): the list of (b, h, group of col_pack key tiles) is cut into one contiguous run
+// per CTA, so that a CTA stays with one head for as long as possible, keeps that head's
+// only query block in shared memory and streams key tiles.  Every item is a single step
+// and flushes.  When the queries fill at most half an accumulator (128 of its 256
+// columns) an item is two key tiles (`nt`, from `kt` on), computed side by side, so that
+// the per-item costs are paid half as often.
+struct PackedItems {
+    bool done;
+    int b, h, kt, nt;
+    long long chunk, chunk_end;
+    static constexpr int s0 = 0, s1 = 1;
+
+    FCS_HD void init(const Problem& p, int cta, int grid) {
+        const int per_head = ceil_div(p.NKC, p.col_pack);
+        const long long all = (long long)p.B * p.H * per_head;
+        chunk = all * cta / grid;
+        chunk_end = all * (cta + 1) / grid;
+        done = chunk >= chunk_end;
+        b = h = kt = 0;
+        nt = 1;
+        if (done) return;
+        long long item = chunk;
+        kt = (int)(item % per_head) * p.col_pack;
+        item /= per_head;
+        h = (int)(item % p.H);
+        b = (int)(item / p.H);
+        nt = p.NKC - kt < p.col_pack ? p.NKC - kt : p.col_pack;
+    }
+    // (no divisions here: a step is short, and every role of the CTA walks the list)
+    FCS_HD void next(const Problem& p) {
+        if (++chunk >= chunk_end) { done = true; return; }
+        kt += p.col_pack;
+        if (kt >= p.NKC) {
+            kt = 0;
+            if (++h >= p.H) { h = 0; ++b; }
+        }
+        nt = p.NKC - kt < p.col_pack ? p.NKC - kt : p.col_pack;
+    }
+    FCS_HD int a_row() const { return kt * TILE; }        // resident = key tiles
+    FCS_HD int b_row(int) const { return 0; }             // the query block
+    FCS_HD bool flush() const { return true; }
+};
+
 template <int MODE> struct ItemsOf;
 template <> struct ItemsOf<MODE_STATS> { typedef StatsItems type; };
 template <> struct ItemsOf<MODE_COLSUM> { typedef ColsumItems type; };
 template <> struct ItemsOf<MODE_COLSUM_EXT> { typedef ColsumItems type; };
-template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT> { typedef ColsumItems type; };
+template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT> { typedef PackedItems type; };
 
 // ---------------------------------------------------------------------------
 // Planning (host): fills the shape-derived fields of `p`.
@@ -335,7 +339,7 @@ constexpr long long COL_INTERLEAVE_MIN_ROWS = 300000;
 constexpr int COL_HEAD_MAJOR_MIN_TILES = 16;   // key tiles per head from which the head-major order is used
 
 inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_past, int sms,
-                 long long interleave_min_rows = COL_INTERLEAVE_MIN_ROWS) {
+                 long long interleave_min_rows = COL_INTERLEAVE_MIN_ROWS, bool head_major_ok = true) {
     p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk;
     p.NQ = ceil_div(Sq, TILE);
     p.NKT = ceil_div(Sk, TILE);
@@ -386,7 +390,7 @@ inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_pas
     if (parts > p.NQB) parts = p.NQB;
     p.col_parts = (int)parts;
     p.col_pack = 1;
-    if (p.NQB == 1 && p.NKC >= COL_HEAD_MAJOR_MIN_TILES) {
+    if (head_major_ok && p.NQB == 1 && p.NKC >= COL_HEAD_MAJOR_MIN_TILES) {
         p.col_interleave = COL_HEAD_MAJOR;
         p.col_parts = 1;
         if (Sq <= BLOCK / 2) p.col_pack = 2;   // two key tiles side by side in one accumulator

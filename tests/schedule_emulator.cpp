@@ -142,37 +142,32 @@ extern "C" int emulate_colsum(const float* q, const float* k, float* out, int B,
     long long col_items = p.steps_total;
     if (p.col_interleave == COL_HEAD_MAJOR) col_items = (long long)B * H * ceil_div(p.NKC, p.col_pack);
     const int grid2 = (int)(col_items < sms ? col_items : sms);
-    const bool packed = p.col_interleave == COL_HEAD_MAJOR && p.col_pack == 2;
     long long walked = 0;
-    for (int cta = 0; cta < grid2; ++cta) {
-        ColsumItems it;
-        it.init(p, cta, grid2);
-        float acc[TILE];
-        for (int r = 0; r < TILE; ++r) acc[r] = 0.f;
-        int cur_b = -1, cur_kt = -1;
-        bool pending = false;
-        for (; !it.done; it.next(p)) {
-            if (it.s0 >= it.s1) return -25;
-            if (packed) {
-                // two key tiles per item, each against the one query block; a group takes 64 of the
-                // 128 query columns of one tile; every item flushes
-                if (!it.flush() || it.s0 != 0 || it.s1 != 1 || it.nt < 1 || it.nt > 2 || it.kt + it.nt > p.NKC ||
-                    it.h < 0 || it.h >= H || it.b < 0 || it.b >= B || (it.kt & 1))
+    if (p.col_interleave == COL_HEAD_MAJOR) {
+        // one query block, contiguous runs of the (b, h, key tiles) list; every item flushes
+        const int GQ = p.col_pack == 2 ? GC : BLOCK;       // query columns a consumer group covers
+        const int NG = p.col_pack == 2 ? 2 : 1;
+        for (int cta = 0; cta < grid2; ++cta) {
+            PackedItems it;
+            it.init(p, cta, grid2);
+            for (; !it.done; it.next(p)) {
+                if (!it.flush() || it.nt < 1 || it.nt > p.col_pack || it.kt + it.nt > p.NKC || it.kt < 0 ||
+                    it.h < 0 || it.h >= H || it.b < 0 || it.b >= B || (it.kt % p.col_pack))
                     return -28;
                 const float* nl = neg_lse.data() + ((long long)it.b * H + it.h) * p.lse_rows;
                 for (int tg = 0; tg < it.nt; ++tg) {
                     const int ktg = it.kt + tg;
                     ++walked;
-                    for (int g2 = 0; g2 < 2; ++g2) {
-                        const int q0 = g2 * GC;
+                    for (int g2 = 0; g2 < NG; ++g2) {
+                        const int q0 = g2 * GQ;
                         const int end = colsum_end_visible(p, 0) - q0;
-                        const bool skip = !(end > 0 && colsum_first_visible(p, ktg, 0, 0) - q0 < GC);
-                        const bool full = end >= GC && colsum_first_visible(p, ktg, 0, TILE - 1) - q0 <= 0;
+                        const bool skip = !(end > 0 && colsum_first_visible(p, ktg, 0, 0) - q0 < GQ);
+                        const bool full = end >= GQ && colsum_first_visible(p, ktg, 0, TILE - 1) - q0 <= 0;
                         for (int r = 0; r < TILE; ++r) {
                             const int thr = colsum_first_visible(p, ktg, 0, r) - q0;
                             const int k_abs = ktg * TILE + r;
                             const float* kr = krow(it.b, it.h, k_abs);
-                            for (int j = 0; j < GC; ++j) {
+                            for (int j = 0; j < GQ; ++j) {
                                 const bool vis = (j >= thr && j < end);
                                 if (full && !vis) return -22;
                                 if (!vis) continue;
@@ -183,8 +178,20 @@ extern "C" int emulate_colsum(const float* q, const float* k, float* out, int B,
                         }
                     }
                 }
-                continue;
             }
+        }
+        if (walked != p.steps_total) return -24;
+        return 0;
+    }
+    for (int cta = 0; cta < grid2; ++cta) {
+        ColsumItems it;
+        it.init(p, cta, grid2);
+        float acc[TILE];
+        for (int r = 0; r < TILE; ++r) acc[r] = 0.f;
+        int cur_b = -1, cur_kt = -1;
+        bool pending = false;
+        for (; !it.done; it.next(p)) {
+            if (it.s0 >= it.s1) return -25;
             if (pending && (it.b != cur_b || it.kt != cur_kt)) return -20;   // left a key tile without flushing
             cur_b = it.b; cur_kt = it.kt; pending = true;
             if (it.s0 < 0 || it.s1 > p.NQB || it.kt < 0 || it.kt >= p.NKC || it.h < 0 || it.h >= H || it.b >= B)
