@@ -11,7 +11,8 @@ also carries the long-context causal shape (131072 keys, 512 suffix queries,
 D=128, bf16) with its 32 heads split over the ranks and one NCCL all-reduce of
 the fp32 per-key partials (strong scaling) under "causal_long_context", and the reference's
 batched sweep shape (B=128 H=16 S=1024 per GPU), which takes the single-pass cluster kernel,
-next to the two-pass kernels on the same inputs under "short_key_axis".
+next to the two-pass kernels on the same inputs under "short_key_axis", and a point of the
+reference's causal sweep (H=32 Q=128 K=65536 D=128), which is bound by HBM, under "causal_suffix".
 
 Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
 the reference's materialising implementation on the host cores instead.
@@ -437,6 +438,27 @@ def main():
         del qs, ks
     assert fc.device_status() == 0
 
+    # ------------------------------------------------------------ causal suffix queries (short-query column pass)
+    # a point of the reference's causal sweep (benchmarks/benchmark_colsum.py:289: H=32 Q=128 D=128):
+    # one sweep over the keys per pass, so the bound is HBM -- reported against the copy bandwidth
+    suffix = None
+    if not args.skip_long_context:
+        wq = Workload("causal_q128", 1, 32, 128, 65536, 128, "fp16", is_causal=True, seed=9 + rank)
+        g = torch.Generator(device=dev).manual_seed(wq.seed)
+        qq = torch.randn(wq.B, wq.H, wq.Sq, wq.D, generator=g, device=dev).to(wq.torch_dtype)
+        kq = torch.randn(wq.B, wq.H, wq.Sk, wq.D, generator=g, device=dev).to(wq.torch_dtype)
+        n_q = max(5, min(args.steps // 4, 20))
+        t_q = time_steps(lambda: fc.flash_colsum(qq, kq, is_causal=True), n_q, 3, flush_buf, barrier)
+        ms_q = max_over_ranks(sum(t_q) / len(t_q))
+        key_bytes = 2 * kq.numel() * 2      # the keys are read once per pass
+        suffix = {"workload": "causal H=32 Q=128 K=65536 D=128 fp16 per GPU (keys 512 MiB)",
+                  "ms_per_call": ms_q, "value": wq.flop * world / (ms_q * 1e-3) / 1e12, "unit": UNIT,
+                  "roofline": {"bound": "hbm", "achieved": key_bytes / (ms_q * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                               "unit": "GB/s", "frac": key_bytes / (ms_q * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                               "bytes": "keys once per pass, two passes; the whole call incl. the merge kernel"}}
+        del qq, kq
+    assert fc.device_status() == 0
+
     # ------------------------------------------------------------ CPU baseline (rank 0, one GPU only)
     cpu = None
     if rank == 0 and world == 1:
@@ -461,6 +483,7 @@ def main():
             "clocks": clocks,
             "causal_long_context": long_ctx,
             "short_key_axis": short_keys,
+            "causal_suffix": suffix,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
