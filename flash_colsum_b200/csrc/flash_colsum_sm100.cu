@@ -66,7 +66,8 @@ constexpr int EXT_B_BYTES = BLOCK * EXT_ROW_BYTES;   // the query-side columns o
 
 template <int D, int MODE>
 struct Layout {
-    static constexpr bool SHORT = (MODE == MODE_COLSUM_EXT_SHORT);
+    static constexpr bool SHORT = (MODE == MODE_COLSUM_EXT_SHORT) || (MODE == MODE_COLSUM_EXT_SHORT2);
+    static constexpr int NB = (MODE == MODE_COLSUM_EXT_SHORT2) ? 2 : 1;   // (short modes) resident query blocks
     static constexpr bool EXT = (MODE == MODE_COLSUM_EXT) || SHORT;
     static constexpr int SLABS = D / 64;              // 64-element (128-byte) column slabs
     static constexpr int A_SLAB_BYTES = TILE * 128;
@@ -74,8 +75,10 @@ struct Layout {
     static constexpr int A_BYTES = SLABS * A_SLAB_BYTES;
     static constexpr int B_BYTES = SLABS * B_SLAB_BYTES;
     static constexpr int B_STAGE_BYTES = B_BYTES + (EXT ? EXT_B_BYTES : 0);   // block, then its extension
-    static constexpr int NS = SHORT ? 1 : (D == 64) ? 4 : 2;      // streamed-operand stages
-    static constexpr int NA = SHORT ? 256 / SLABS / 32 : 2;       // resident-operand buffers (128 KiB when they are what streams)
+    static constexpr int NS = SHORT ? NB : (D == 64) ? 4 : 2;     // streamed-operand stages
+    // resident-operand buffers: two; in the short modes they are what streams -- 128 KiB of them,
+    // or what two 128-wide query blocks leave
+    static constexpr int NA = !SHORT ? 2 : (NB == 2 && D == 128) ? 2 : 256 / SLABS / 32;
     static constexpr int A_OFF = 0;
     static constexpr int B_OFF = NA * A_BYTES;
     static constexpr int EXTA_OFF = B_OFF + NS * B_STAGE_BYTES;             // 128 rows of the constant
@@ -135,8 +138,8 @@ template <int D, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ CUtensorMap tm_ext, const Problem p) {
-    constexpr bool EXT = (MODE == MODE_COLSUM_EXT) || (MODE == MODE_COLSUM_EXT_SHORT);
     using L = Layout<D, MODE>;
+    constexpr bool EXT = L::EXT;
     constexpr int NA = L::NA;
     using Items = typename ItemsOf<MODE>::type;
     extern __shared__ uint8_t smem_raw[];
@@ -244,12 +247,15 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     if (bh != cur_bh) {
                         if (!wait_all(b_empty(0), (b_cnt & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
                         if (elect_one_sync()) {
-                            mbar_arrive_expect_tx(b_full(0), L::B_STAGE_BYTES);
+                            mbar_arrive_expect_tx(b_full(0), (uint32_t)p.NQB * L::B_STAGE_BYTES);
+                            for (int qb = 0; qb < p.NQB; ++qb) {
 #pragma unroll
-                            for (int sl = 0; sl < L::SLABS; ++sl)
-                                tma_load_4d(b_smem + sl * L::B_SLAB_BYTES, &tm_b, b_full(0), sl * 64, it.b_row(0),
-                                            it.h, it.b);
-                            tma_load_3d(b_smem + L::B_BYTES, &tm_ext, b_full(0), 0, it.b_row(0), bh);
+                                for (int sl = 0; sl < L::SLABS; ++sl)
+                                    tma_load_4d(b_smem + qb * L::B_STAGE_BYTES + sl * L::B_SLAB_BYTES, &tm_b, b_full(0),
+                                                sl * 64, qb * BLOCK, it.h, it.b);
+                                tma_load_3d(b_smem + qb * L::B_STAGE_BYTES + L::B_BYTES, &tm_ext, b_full(0), 0,
+                                            qb * BLOCK, bh);
+                            }
                         }
                         __syncwarp();
                         ++b_cnt;
@@ -316,7 +322,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             bool ok = true;
             if constexpr (L::SHORT) {
                 int cur_bh = -1, b_cnt = 0;
-                for (; ok && !it.done; it.next(p), ++n) {
+                for (; ok && !it.done; it.next(p)) {
                     const int bh = it.b * p.H + it.h;
                     if (bh != cur_bh) {
                         // the MMAs of the head before this one have read its query block: hand
@@ -326,6 +332,34 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                         if (!wait_all(b_full(0), b_cnt & 1, FCS_STATUS_WAIT_MMA)) break;
                         ++b_cnt;
                         cur_bh = bh;
+                    }
+                    if constexpr (MODE == MODE_COLSUM_EXT_SHORT2) {
+                        // one key tile against the head's resident query blocks, a step each
+                        const int ab = a_cnt % NA;
+                        if (!wait_all(a_full(ab), (a_cnt / NA) & 1, FCS_STATUS_WAIT_MMA)) break;
+                        const uint64_t da = umma_desc_k_sw128(a_smem + ab * L::A_BYTES);
+                        for (int st = it.s0; st < it.s1; ++st, ++n) {
+                            const int buf = n & (NUM_TBUF - 1);
+                            if (!wait_all(t_empty(buf), ((n >> 1) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+                            tc_fence_after();
+                            const uint64_t db = umma_desc_k_sw128(b_smem + st * L::B_STAGE_BYTES);
+                            const uint32_t d_tmem = tmem_base + buf * BLOCK;
+                            if (elect_one_sync()) {
+#pragma unroll
+                                for (int ks = 0; ks < D / 16; ++ks) {
+                                    const uint64_t oa = (uint64_t)(((ks >> 2) * L::A_SLAB_BYTES + (ks & 3) * 32) >> 4);
+                                    const uint64_t ob = (uint64_t)(((ks >> 2) * L::B_SLAB_BYTES + (ks & 3) * 32) >> 4);
+                                    umma_f16(d_tmem, da + oa, db + ob, p.idesc, ks > 0 ? 1u : 0u);
+                                }
+                                umma_f16(d_tmem, umma_desc_k_sw32(smem_base + L::EXTA_OFF),
+                                         umma_desc_k_sw32(b_smem + st * L::B_STAGE_BYTES + L::B_BYTES), p.idesc, 1u);
+                                umma_commit(t_full(buf));
+                                if (st + 1 == it.s1) umma_commit(a_empty(ab));
+                            }
+                            __syncwarp();
+                        }
+                        ++a_cnt;
+                        continue;
                     }
                     // one step: the item's key tiles side by side in one accumulator buffer
                     const int buf = n & (NUM_TBUF - 1);
@@ -351,6 +385,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                         }
                         __syncwarp();
                     }
+                    ++n;
                 }
             } else {
             for (; ok && !it.done; it.next(p), ++a_cnt) {
@@ -1084,7 +1119,10 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     // a query axis of at most 128 rows fills half a streamed block: the MMAs need N = 128 only
     if (Sq <= BLOCK / 2)
         p.idesc = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((BLOCK / 2) >> 3) << 17);
-    if (use_ext && p.col_interleave == COL_HEAD_MAJOR)   // one query block per head, many key tiles: the key tiles stream
+    if (use_ext && p.col_interleave == COL_HEAD_MAJOR && p.NQB == 2)   // two resident query blocks per head
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT2>(tk_a, tq_b, text, p, grid2, stream, chained)
+                      : launch_stream<128, MODE_COLSUM_EXT_SHORT2>(tk_a, tq_b, text, p, grid2, stream, chained);
+    else if (use_ext && p.col_interleave == COL_HEAD_MAJOR)   // one query block per head, many key tiles: the key tiles stream
         e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM_EXT_SHORT>(tk_a, tq_b, text, p, grid2, stream, chained);
     else if (use_ext)

@@ -26,7 +26,8 @@ constexpr int MAX_SPLIT = 64;  // most key ranges a query tile is split into
 
 // MODE_COLSUM_EXT_SHORT: the column pass of a query axis that fits one streamed block --
 // every item is a single step, so the key tiles are what streams: deep ring for them, one stage for the queries
-enum : int { MODE_STATS = 0, MODE_COLSUM = 1, MODE_COLSUM_EXT = 2, MODE_COLSUM_EXT_SHORT = 3 };
+// MODE_COLSUM_EXT_SHORT2: the same for a query axis of two blocks, both resident
+enum : int { MODE_STATS = 0, MODE_COLSUM = 1, MODE_COLSUM_EXT = 2, MODE_COLSUM_EXT_SHORT = 3, MODE_COLSUM_EXT_SHORT2 = 4 };
 // values of Problem::col_interleave (how the column pass deals out its work, see ColsumItems)
 enum : int { COL_CONTIGUOUS = 0, COL_INTERLEAVED = 1, COL_HEAD_MAJOR = 2 };
 
@@ -323,11 +324,48 @@ struct PackedItems {
     FCS_HD bool flush() const { return true; }
 };
 
+// The same order for a query axis of two blocks (both stay in shared memory): an item is one
+// key tile against the query blocks s0..s1-1 that see it.
+struct ResidentItems {
+    bool done;
+    int b, h, kt, s0, s1;
+    long long chunk, chunk_end;
+    static constexpr int nt = 1;
+
+    FCS_HD void init(const Problem& p, int cta, int grid) {
+        const long long all = (long long)p.B * p.H * p.NKC;
+        chunk = all * cta / grid;
+        chunk_end = all * (cta + 1) / grid;
+        done = chunk >= chunk_end;
+        b = h = kt = s0 = 0;
+        s1 = p.NQB;
+        if (done) return;
+        long long item = chunk;
+        kt = (int)(item % p.NKC);
+        item /= p.NKC;
+        h = (int)(item % p.H);
+        b = (int)(item / p.H);
+        s0 = colsum_first_q_block(p, kt);
+    }
+    FCS_HD void next(const Problem& p) {
+        if (++chunk >= chunk_end) { done = true; return; }
+        if (++kt >= p.NKC) {
+            kt = 0;
+            if (++h >= p.H) { h = 0; ++b; }
+        }
+        s0 = colsum_first_q_block(p, kt);
+    }
+    FCS_HD int a_row() const { return kt * TILE; }            // resident = key tile
+    FCS_HD int b_row(int st) const { return st * BLOCK; }     // the query blocks
+    FCS_HD bool flush() const { return true; }
+};
+
 template <int MODE> struct ItemsOf;
 template <> struct ItemsOf<MODE_STATS> { typedef StatsItems type; };
 template <> struct ItemsOf<MODE_COLSUM> { typedef ColsumItems type; };
 template <> struct ItemsOf<MODE_COLSUM_EXT> { typedef ColsumItems type; };
 template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT> { typedef PackedItems type; };
+template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT2> { typedef ResidentItems type; };
 
 // ---------------------------------------------------------------------------
 // Planning (host): fills the shape-derived fields of `p`.
@@ -336,6 +374,7 @@ template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT> { typedef PackedItems type; };
 // the rows and their extension columns (up to 288 bytes each) then exceed what the L2
 // keeps for data that every SM reads.
 constexpr long long COL_INTERLEAVE_MIN_ROWS = 300000;
+constexpr int COL_HEAD_MAJOR_MAX_BLOCKS = 2;   // query blocks that stay in shared memory next to a ring of key tiles
 constexpr int COL_HEAD_MAJOR_MIN_TILES = 16;   // key tiles per head from which the head-major order is used
 
 inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_past, int sms,
@@ -390,7 +429,7 @@ inline void plan(Problem& p, int B, int H, int Sq, int Sk, int causal, int k_pas
     if (parts > p.NQB) parts = p.NQB;
     p.col_parts = (int)parts;
     p.col_pack = 1;
-    if (head_major_ok && p.NQB == 1 && p.NKC >= COL_HEAD_MAJOR_MIN_TILES) {
+    if (head_major_ok && p.NQB <= COL_HEAD_MAJOR_MAX_BLOCKS && p.NKC >= COL_HEAD_MAJOR_MIN_TILES) {
         p.col_interleave = COL_HEAD_MAJOR;
         p.col_parts = 1;
         if (Sq <= BLOCK / 2) p.col_pack = 2;   // two key tiles side by side in one accumulator

@@ -147,6 +147,36 @@ extern "C" int emulate_colsum(const float* q, const float* k, float* out, int B,
         // one query block, contiguous runs of the (b, h, key tiles) list; every item flushes
         const int GQ = p.col_pack == 2 ? GC : BLOCK;       // query columns a consumer group covers
         const int NG = p.col_pack == 2 ? 2 : 1;
+        if (p.NQB == 2) {
+            // two resident query blocks: an item is one key tile against the blocks that see it
+            for (int cta = 0; cta < grid2; ++cta) {
+                ResidentItems it;
+                it.init(p, cta, grid2);
+                for (; !it.done; it.next(p)) {
+                    if (!it.flush() || it.kt < 0 || it.kt >= p.NKC || it.h < 0 || it.h >= H || it.b < 0 || it.b >= B ||
+                        it.s0 < 0 || it.s0 >= it.s1 || it.s1 != p.NQB)
+                        return -29;
+                    const float* nl_bh = neg_lse.data() + ((long long)it.b * H + it.h) * p.lse_rows;
+                    for (int st = 0; st < p.NQB; ++st) {
+                        const bool taken = st >= it.s0 && st < it.s1;
+                        if (taken) ++walked;
+                        const int end = colsum_end_visible(p, st);
+                        for (int r = 0; r < TILE; ++r) {
+                            const int thr = colsum_first_visible(p, it.kt, st, r);
+                            const int k_abs = it.kt * TILE + r;
+                            const float* kr = krow(it.b, it.h, k_abs);
+                            for (int j = thr; j < end; ++j) {
+                                if (!taken) return -30;   // a block with visible elements was left out
+                                const float sc = sgn * dot(kr, qrow(it.b, it.h, st * BLOCK + j), D);
+                                if (k_abs < Sk) out[(size_t)it.b * Sk + k_abs] += exp2f(sc * c + nl_bh[st * BLOCK + j]);
+                            }
+                        }
+                    }
+                }
+            }
+            if (walked != p.steps_total) return -24;
+            return 0;
+        }
         for (int cta = 0; cta < grid2; ++cta) {
             PackedItems it;
             it.init(p, cta, grid2);

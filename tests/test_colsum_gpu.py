@@ -80,6 +80,11 @@ SHAPES = [
     (1, 3, 256, 3000, 128, "fp16", True, None),
     (2, 4, 2100, 2100, 64, "fp16", False, 200),
     (1, 40, 70, 2200, 128, "bf16", True, None),      # a head change every few tiles
+    # two query blocks, both resident in shared memory next to the ring of key tiles
+    (1, 3, 400, 2500, 128, "bf16", True, None),
+    (1, 5, 512, 2304, 64, "fp16", True, None),
+    (2, 3, 2100, 2100, 64, "fp16", False, 300),
+    (1, 20, 300, 2200, 128, "fp16", True, None),
 ]
 
 

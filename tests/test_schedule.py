@@ -74,6 +74,11 @@ CASES = [
     (1, 3, 128, 2300, 8, True, None, 148),
     (2, 2, 100, 2100, 8, True, None, 5),        # runs cut through heads and batch entries
     (1, 2, 2100, 2100, 4, False, 200, 7),
+    # two query blocks, both resident
+    (1, 3, 400, 2500, 8, True, None, 148),
+    (2, 2, 512, 2304, 8, True, None, 5),
+    (1, 2, 2100, 2100, 4, False, 300, 7),
+    (1, 2, 300, 2200, 4, True, None, 148),     # late key tiles are seen by the second block only
 ]
 
 
