@@ -14,7 +14,12 @@
 //                    flushes that with one atomic add per (key tile, CTA range).
 //                    -lse/c reaches the accumulator through 16 extra contraction
 //                    columns (MODE_COLSUM_EXT); for tiny scales it is staged
-//                    through shared memory instead (MODE_COLSUM).
+//                    through shared memory instead (MODE_COLSUM).  A query axis of
+//                    one or two 256-row blocks over sixteen or more key tiles swaps
+//                    the roles (MODE_COLSUM_EXT_SHORT / _SHORT2): the head's query
+//                    blocks stay in shared memory, the key tiles stream through a
+//                    deep ring, and with at most 128 queries two key tiles share
+//                    one accumulator buffer.
 //
 // Both operands are row tiles with the head dimension contiguous, so the same
 // shared-memory layout serves as A (128 resident rows) or B (256 streamed rows)
