@@ -71,8 +71,10 @@ constexpr int EXT_B_BYTES = BLOCK * EXT_ROW_BYTES;   // the query-side columns o
 
 template <int D, int MODE>
 struct Layout {
-    static constexpr bool SHORT = (MODE == MODE_COLSUM_EXT_SHORT) || (MODE == MODE_COLSUM_EXT_SHORT2);
-    static constexpr int NB = (MODE == MODE_COLSUM_EXT_SHORT2) ? 2 : 1;   // (short modes) resident query blocks
+    static constexpr bool COMBINE = (MODE == MODE_COLSUM_EXT_SHORT_COMBINE) || (MODE == MODE_COLSUM_EXT_SHORT2_COMBINE);
+    static constexpr bool SHORT2 = (MODE == MODE_COLSUM_EXT_SHORT2) || (MODE == MODE_COLSUM_EXT_SHORT2_COMBINE);
+    static constexpr bool SHORT = (MODE == MODE_COLSUM_EXT_SHORT) || (MODE == MODE_COLSUM_EXT_SHORT_COMBINE) || SHORT2;
+    static constexpr int NB = SHORT2 ? 2 : 1;   // (short modes) resident query blocks
     static constexpr bool EXT = (MODE == MODE_COLSUM_EXT) || SHORT;
     static constexpr int SLABS = D / 64;              // 64-element (128-byte) column slabs
     static constexpr int A_SLAB_BYTES = TILE * 128;
@@ -94,7 +96,9 @@ struct Layout {
     static constexpr int NUM_BARS = 2 * NA + 2 * NS + 2 * NUM_TBUF + MERGE_SLOTS + 2 * NUM_LSE;
     static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;        // tmem address, abort flag
     static constexpr int MERGE_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // float2[MERGE_SLOTS][groups][128]
-    static constexpr int TOTAL = MERGE_OFF + (MODE == MODE_STATS ? MERGE_SLOTS * CONSUMER_GROUPS * TILE * 8 : 0);
+    // (short column modes: float[MERGE_SLOTS][groups][128], the groups' sums of an item before the one add)
+    static constexpr int TOTAL = MERGE_OFF + (MODE == MODE_STATS ? MERGE_SLOTS * CONSUMER_GROUPS * TILE * 8
+                                                                 : COMBINE ? MERGE_SLOTS * CONSUMER_GROUPS * TILE * 4 : 0);
     static constexpr int DYN_BYTES = TOTAL + 1024;    // slack to align the base to 1024
     static_assert(DYN_BYTES <= 227 * 1024, "shared memory budget");
 };
@@ -338,7 +342,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                         ++b_cnt;
                         cur_bh = bh;
                     }
-                    if constexpr (MODE == MODE_COLSUM_EXT_SHORT2) {
+                    if constexpr (L::SHORT2) {
                         // one key tile against the head's resident query blocks, a step each
                         const int ab = a_cnt % NA;
                         if (!wait_all(a_full(ab), (a_cnt / NA) & 1, FCS_STATUS_WAIT_MMA)) break;
@@ -487,6 +491,33 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             }
             return true;
         };
+        // short column modes: every item ends a key tile, and its sums sit in four groups.  When
+        // `out` may be another GPU's memory (the _COMBINE modes) they meet in shared memory and one group,
+        // a different one every item, adds them into the output after its next step -- one add per
+        // key over NVLink instead of four, nobody waits.  (With a local `out` the four adds are
+        // cheaper than the meeting: measured +2 % on the long-context shape.)
+        float* colbuf = reinterpret_cast<float*>(smem + L::MERGE_OFF);
+        bool cpend = false;
+        int cp_cnt = 0, cp_b = 0, cp_kt = 0, cp_nt = 0;
+        auto finish_cols = [&]() -> bool {
+            const int slot = cp_cnt & (MERGE_SLOTS - 1);
+            bool good = mbar_wait(merge_bar(slot), (cp_cnt / MERGE_SLOTS) & 1, abort_flag, p.status,
+                                  FCS_STATUS_WAIT_CONSUMER);
+            good = __all_sync(0xffffffffu, good);
+            cpend = false;
+            if (!good) return false;
+            const float* cb = colbuf + slot * CONSUMER_GROUPS * TILE + row;
+            // system scope: `out` may live on another GPU and take adds from several
+            float* dst = p.out + (long long)cp_b * p.out_ld;
+            const int k0 = cp_kt * TILE + row;
+            if (p.col_pack == 2) {   // groups 0, 1 hold the first key tile, groups 2, 3 the second
+                if (k0 < p.Sk) atomicAdd_system(dst + k0, cb[0] + cb[TILE]);
+                if (cp_nt == 2 && k0 + TILE < p.Sk) atomicAdd_system(dst + k0 + TILE, cb[2 * TILE] + cb[3 * TILE]);
+            } else if (k0 < p.Sk) {
+                atomicAdd_system(dst + k0, (cb[0] + cb[TILE]) + (cb[2 * TILE] + cb[3 * TILE]));
+            }
+            return true;
+        };
         for (; ok && !it.done; it.next(p), ++item_cnt) {
             // steps f_lo <= st < f_hi need no masks: their per-step work is kept minimal
             int f_lo, f_hi;
@@ -583,6 +614,9 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 if constexpr (MODE == MODE_STATS) {
                     if (pending) { ok = finish_item(); if (!ok) break; }
                 }
+                if constexpr (L::COMBINE) {
+                    if (cpend) { ok = finish_cols(); if (!ok) break; }
+                }
             }
             if (!ok) break;
             if constexpr (MODE == MODE_STATS) {
@@ -598,16 +632,32 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                     pend_cnt = item_cnt; pend_b = it.b; pend_h = it.h; pend_qt = it.qt; pend_sp = it.sp;
                 }
                 m_run = -INFINITY; l_run = 0.f;
-            } else {
-                if (it.flush()) {
-                    // (two key tiles per item: this group's tile is the first or the second)
+            } else if constexpr (L::SHORT) {
+                if constexpr (!L::COMBINE) {
+                    // four adds per key, straight from the groups: cheapest when `out` is local
                     int tg = 0;
                     bool mine = true;
-                    if constexpr (L::SHORT) {
-                        if (p.col_pack == 2) { tg = wg >> 1; mine = tg < it.nt; }
-                    }
+                    if (p.col_pack == 2) { tg = wg >> 1; mine = tg < it.nt; }
                     const int k_abs = (it.kt + tg) * TILE + row;
                     if (k_abs < p.Sk && mine)
+                        atomicAdd_system(p.out + (long long)it.b * p.out_ld + k_abs,
+                                         (acc[0] + acc[1]) + (acc[2] + acc[3]));
+                    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                } else {
+                    if (cpend) { ok = finish_cols(); if (!ok) break; }
+                    const int slot = item_cnt & (MERGE_SLOTS - 1);
+                    colbuf[(slot * CONSUMER_GROUPS + wg) * TILE + row] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                    mbar_arrive(merge_bar(slot));
+                    if ((item_cnt % CONSUMER_GROUPS) == wg) {
+                        cpend = true;
+                        cp_cnt = item_cnt; cp_b = it.b; cp_kt = it.kt; cp_nt = it.nt;
+                    }
+                    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                }
+            } else {
+                if (it.flush()) {
+                    const int k_abs = it.kt * TILE + row;
+                    if (k_abs < p.Sk)
                         // system scope: `out` may live on another GPU and take adds from several
                         atomicAdd_system(p.out + (long long)it.b * p.out_ld + k_abs,
                                          (acc[0] + acc[1]) + (acc[2] + acc[3]));
@@ -617,6 +667,9 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
         }
         if constexpr (MODE == MODE_STATS) {
             if (ok && pending) finish_item();
+        }
+        if constexpr (L::COMBINE) {
+            if (ok && cpend) finish_cols();
         }
     }
 
@@ -1042,6 +1095,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     p.out = out;
     p.out_ld = out_ld;
     p.clear_out = (clear_out && passes == PASSES_BOTH) ? 1 : 0;   // (the statistics pass does the clearing)
+    p.col_combine = clear_out ? 0 : 1;   // accumulating into a caller's buffer: it may be peer-mapped
     p.status = status;
     p.c = fabsf(scale) * 1.4426950408889634f;
     p.inv_c = use_ext ? (scale < 0.f ? -1.0f : 1.0f) / p.c : 0.f;
@@ -1124,10 +1178,17 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     // a query axis of at most 128 rows fills half a streamed block: the MMAs need N = 128 only
     if (Sq <= BLOCK / 2)
         p.idesc = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((BLOCK / 2) >> 3) << 17);
-    if (use_ext && p.col_interleave == COL_HEAD_MAJOR && p.NQB == 2)   // two resident query blocks per head
+    const bool head_major = use_ext && p.col_interleave == COL_HEAD_MAJOR;
+    if (head_major && p.col_combine && p.NQB == 2)
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT2_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained)
+                      : launch_stream<128, MODE_COLSUM_EXT_SHORT2_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained);
+    else if (head_major && p.col_combine)
+        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained)
+                      : launch_stream<128, MODE_COLSUM_EXT_SHORT_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained);
+    else if (head_major && p.NQB == 2)   // two resident query blocks per head
         e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT2>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM_EXT_SHORT2>(tk_a, tq_b, text, p, grid2, stream, chained);
-    else if (use_ext && p.col_interleave == COL_HEAD_MAJOR)   // one query block per head, many key tiles: the key tiles stream
+    else if (head_major)   // one query block per head, many key tiles: the key tiles stream
         e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM_EXT_SHORT>(tk_a, tq_b, text, p, grid2, stream, chained);
     else if (use_ext)

@@ -27,7 +27,10 @@ constexpr int MAX_SPLIT = 64;  // most key ranges a query tile is split into
 // MODE_COLSUM_EXT_SHORT: the column pass of a query axis that fits one streamed block --
 // every item is a single step, so the key tiles are what streams: deep ring for them, one stage for the queries
 // MODE_COLSUM_EXT_SHORT2: the same for a query axis of two blocks, both resident
-enum : int { MODE_STATS = 0, MODE_COLSUM = 1, MODE_COLSUM_EXT = 2, MODE_COLSUM_EXT_SHORT = 3, MODE_COLSUM_EXT_SHORT2 = 4 };
+// ..._COMBINE: the same two, with the consumer groups' sums of an item combined in shared memory
+// before one add per key (for an output that may be another GPU's memory)
+enum : int { MODE_STATS = 0, MODE_COLSUM = 1, MODE_COLSUM_EXT = 2, MODE_COLSUM_EXT_SHORT = 3, MODE_COLSUM_EXT_SHORT2 = 4,
+             MODE_COLSUM_EXT_SHORT_COMBINE = 5, MODE_COLSUM_EXT_SHORT2_COMBINE = 6 };
 // values of Problem::col_interleave (how the column pass deals out its work, see ColsumItems)
 enum : int { COL_CONTIGUOUS = 0, COL_INTERLEAVED = 1, COL_HEAD_MAJOR = 2 };
 
@@ -43,6 +46,7 @@ struct Problem {
     int col_interleave; // column pass: COL_CONTIGUOUS steps, or (b, h, key tile) chunks dealt round-robin / in contiguous runs
     int col_parts;      // ... each cut into this many query-block ranges
     int col_pack;       // head-major order: key tiles per item (2 when the queries fill half an accumulator, else 1)
+    int col_combine;    // head-major order: the kernels that combine the consumer groups' sums before one add per key are used
     long long stats_items;
     long long steps_per_batch;  // column pass: steps of one batch entry
     long long steps_total;
@@ -366,6 +370,8 @@ template <> struct ItemsOf<MODE_COLSUM> { typedef ColsumItems type; };
 template <> struct ItemsOf<MODE_COLSUM_EXT> { typedef ColsumItems type; };
 template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT> { typedef PackedItems type; };
 template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT2> { typedef ResidentItems type; };
+template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT_COMBINE> { typedef PackedItems type; };
+template <> struct ItemsOf<MODE_COLSUM_EXT_SHORT2_COMBINE> { typedef ResidentItems type; };
 
 // ---------------------------------------------------------------------------
 // Planning (host): fills the shape-derived fields of `p`.

@@ -440,3 +440,27 @@ def test_passes_run_apart_reproduce_the_call(fc):
         torch.testing.assert_close(got, fc.flash_colsum(qc, kc, cls_len=cls), rtol=2e-4, atol=1e-9)
     with pytest.raises(RuntimeError, match="norm_rows"):
         ops.colsum_statistics(qc[:, :, :256], kc, scale, 100)
+
+
+def test_head_shards_accumulate_into_one_buffer(fc):
+    """The accumulate entry (what head-sharded ranks call with a possibly peer-mapped buffer):
+    two head shards added into one cleared buffer, normalised by the total head count, give the
+    unsharded result -- on the short-query column modes, whose consumer groups combine their sums
+    in shared memory before the one add per key that this entry issues."""
+    from flash_colsum_b200 import ops
+    for (H, Sq, Sk, D, dtype) in [(6, 100, 2500, 64, "bf16"),      # one query block, two key tiles per step
+                                  (4, 256, 3000, 128, "fp16"),     # one query block, one key tile per step
+                                  (6, 400, 2500, 128, "bf16"),     # two resident query blocks
+                                  (4, 130, 2177, 64, "fp16")]:     # ragged: an odd number of key tiles
+        w = Workload("acc", 1, H, Sq, Sk, D, dtype, is_causal=True, seed=H + Sq + Sk)
+        q, k = make_inputs(w)
+        qd, kd = q.cuda(), k.cuda()
+        target = torch.zeros(Sk, device="cuda", dtype=torch.float32)
+        half = H // 2
+        scale = 1.0 / D ** 0.5
+        for lo, hi in ((0, half), (half, H)):
+            ops._flash_colsum_causal(qd[:, lo:hi], kd[:, lo:hi], scale, h_norm=H, accumulate_into=target)
+        torch.cuda.synchronize()
+        assert fc.device_status() == 0
+        got = target.cpu().numpy()[None, :]
+        assert_parity(got, c_oracle.colsum_c(q, k, is_causal=True), f"accumulate {H}x{Sq}x{Sk}x{D}")
