@@ -9,6 +9,7 @@ the library is missing the call raises.
 
 from __future__ import annotations
 
+import contextlib
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -38,9 +39,32 @@ def device_status(device=None) -> int:
 
 def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     """Unit inner stride, outer strides multiples of 16 bytes, 16-byte aligned base."""
-    ok = (t.stride(3) == 1 and all(s > 0 and s % 8 == 0 for s in t.stride()[:3])
-          and t.data_ptr() % 16 == 0)
-    return t if ok else t.contiguous()
+    s0, s1, s2, s3 = t.stride()
+    if s3 == 1 and s0 > 0 and s1 > 0 and s2 > 0 and (s0 | s1 | s2) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
+# The wrappers below run for every call, and calls of a dozen microseconds of GPU work are
+# bound by them: the device guard is skipped when the tensors' device is the current one, and
+# the stream handle comes from the raw getter instead of a Stream object.
+_NO_GUARD = contextlib.nullcontext()
+_raw_stream_getter = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _on_device(device: torch.device):
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
+
+
+def _raw_stream(device: torch.device) -> int:
+    """cudaStream_t of torch's current stream on `device`, as an integer."""
+    if _raw_stream_getter is not None:
+        idx = device.index
+        return _raw_stream_getter(torch.cuda.current_device() if idx is None else idx)
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 def _rows(cls_n: int, S: int) -> int:
@@ -64,10 +88,18 @@ def _prepare(query: torch.Tensor, key: torch.Tensor) -> Tuple[torch.Tensor, torc
     return _tma_ready(query), _tma_ready(key), _DTYPE_CODE[query.dtype]
 
 
+_workspace_bytes: Dict[tuple, int] = {}   # (sizes) -> fcs_workspace_bytes, pure host arithmetic
+
+
 def _workspace(lib, device, B, H, rows, Sk, D, causal) -> torch.Tensor:
-    n = lib.fcs_workspace_bytes(B, H, rows, Sk, D, int(causal))
-    if n == 0:
-        raise RuntimeError("flash_colsum_b200: fcs_workspace_bytes rejected the sizes")
+    key = (B, H, rows, Sk, D, causal)
+    n = _workspace_bytes.get(key)
+    if n is None:
+        n = lib.fcs_workspace_bytes(B, H, rows, Sk, D, int(causal))
+        if n == 0:
+            raise RuntimeError("flash_colsum_b200: fcs_workspace_bytes rejected the sizes")
+        if len(_workspace_bytes) < 4096:
+            _workspace_bytes[key] = n
     return torch.empty(n, dtype=torch.uint8, device=device)
 
 
@@ -77,14 +109,14 @@ def _flash_colsum_batched(Q: torch.Tensor, K: torch.Tensor, scale: float, CLS_N:
     lib = _cabi.load()
     Q, K, code = _prepare(Q, K)
     B, H, S, D = Q.shape
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         out = torch.empty((B, S), device=Q.device, dtype=torch.float32)
         ws = _workspace(lib, Q.device, B, H, _rows(CLS_N, S), S, D, False)
         _check(lib.fcs_colsum_batched(
             Q.data_ptr(), K.data_ptr(), out.data_ptr(), S, B, H, S, D, code,
             Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
             float(scale), int(CLS_N), int(h_norm), ws.data_ptr(), ws.numel(),
-            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+            _status_word(Q.device).data_ptr(), _raw_stream(Q.device)))
     return out
 
 
@@ -94,14 +126,14 @@ def _flash_colsum_non_batched(Q: torch.Tensor, K: torch.Tensor, scale: float, CL
     lib = _cabi.load()
     Q, K, code = _prepare(Q, K)
     _, H, S, D = Q.shape
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         out = torch.empty((1, S), device=Q.device, dtype=torch.float32)
         ws = _workspace(lib, Q.device, 1, H, _rows(CLS_N, S), S, D, False)
         _check(lib.fcs_colsum_non_batched(
             Q.data_ptr(), K.data_ptr(), out.data_ptr(), H, S, D, code,
             Q.stride(1), Q.stride(2), K.stride(1), K.stride(2),
             float(scale), int(CLS_N), int(h_norm), ws.data_ptr(), ws.numel(),
-            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+            _status_word(Q.device).data_ptr(), _raw_stream(Q.device)))
     return out
 
 
@@ -117,7 +149,7 @@ def _flash_colsum_causal(Q: torch.Tensor, K: torch.Tensor, scale: float, K_past:
     Q, K, code = _prepare(Q, K)
     _, H, Q_len, D = Q.shape
     K_len = K.shape[2]
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         if accumulate_into is None:
             out = torch.empty((1, K_len), device=Q.device, dtype=torch.float32)
             entry = lib.fcs_colsum_causal
@@ -132,7 +164,7 @@ def _flash_colsum_causal(Q: torch.Tensor, K: torch.Tensor, scale: float, K_past:
             Q.stride(1), Q.stride(2), K.stride(1), K.stride(2),
             float(scale), -1 if K_past is None else int(K_past), int(h_norm),
             ws.data_ptr(), ws.numel(),
-            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+            _status_word(Q.device).data_ptr(), _raw_stream(Q.device)))
     return out
 
 
@@ -246,14 +278,14 @@ def flash_colsum_causal(
     lib = _cabi.load()
     Q, K, code = _prepare(query, key)
     K_len = K.shape[2]
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         out = torch.empty((B, K_len), device=Q.device, dtype=torch.float32)
         ws = _workspace(lib, Q.device, B, H, Q_len, K_len, D, True)
         _check(lib.fcs_colsum_causal_batched(
             Q.data_ptr(), K.data_ptr(), out.data_ptr(), K_len, B, H, Q_len, K_len, D, code,
             Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
             float(scale), -1 if k_past is None else int(k_past), 0, ws.data_ptr(), ws.numel(),
-            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+            _status_word(Q.device).data_ptr(), _raw_stream(Q.device)))
     if out_dtype is not None and out_dtype != out.dtype:
         out = out.to(out_dtype)
     return out
@@ -278,14 +310,14 @@ def colsum_statistics(query_rows: torch.Tensor, key: torch.Tensor, scale: float,
     Q, K, code = _prepare(query_rows, key)
     B, H, rows, D = Q.shape
     Sk = K.shape[2]
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         lse = torch.full((B * H, statistics_rows(rows)), float("-inf"), dtype=torch.float32, device=Q.device)
         ws = _workspace(lib, Q.device, B, H, rows, Sk, D, False)
         _check(lib.fcs_colsum_statistics(
             Q.data_ptr(), K.data_ptr(), lse.data_ptr(), B, H, rows, Sk, D, code,
             Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
             float(scale), int(norm_rows), int(h_norm), ws.data_ptr(), ws.numel(),
-            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+            _status_word(Q.device).data_ptr(), _raw_stream(Q.device)))
     return lse
 
 
@@ -302,14 +334,14 @@ def colsum_columns(query: torch.Tensor, key_rows: torch.Tensor, neg_lse: torch.T
     if (neg_lse.dtype != torch.float32 or not neg_lse.is_contiguous()
             or tuple(neg_lse.shape) != (B * H, statistics_rows(rows))):
         raise ValueError(f"neg_lse must be contiguous fp32 of shape {(B * H, statistics_rows(rows))}")
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         out = torch.empty((B, k_rows), device=Q.device, dtype=torch.float32)
         ws = _workspace(lib, Q.device, B, H, rows, k_rows, D, False)
         _check(lib.fcs_colsum_columns(
             Q.data_ptr(), K.data_ptr(), neg_lse.data_ptr(), out.data_ptr(), k_rows, B, H, rows, k_rows, D, code,
             Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
             float(scale), ws.data_ptr(), ws.numel(),
-            _status_word(Q.device).data_ptr(), torch.cuda.current_stream(Q.device).cuda_stream))
+            _status_word(Q.device).data_ptr(), _raw_stream(Q.device)))
     return out
 
 
@@ -330,11 +362,11 @@ def topk_columns(colsum: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tens
     if colsum.stride(1) != 1:
         colsum = colsum.contiguous()
     lib = _cabi.load()
-    with torch.cuda.device(colsum.device):
+    with _on_device(colsum.device):
         idx = torch.empty((B, k), dtype=torch.int32, device=colsum.device)
         val = torch.empty((B, k), dtype=torch.float32, device=colsum.device)
         _check(lib.fcs_select_topk(colsum.data_ptr(), colsum.stride(0), B, S, int(k), idx.data_ptr(),
-                                   val.data_ptr(), torch.cuda.current_stream(colsum.device).cuda_stream))
+                                   val.data_ptr(), _raw_stream(colsum.device)))
     return val, idx
 
 
