@@ -370,6 +370,13 @@ def test_batched_causal_and_explicit_k_past(fc):
         assert fc.device_status() == 0
         assert_parity(got, naive_colsum_f64(q, k, is_causal=True, k_past=k_past), f"k_past {k_past}")
         np.testing.assert_allclose(got.sum(axis=1), 1.0, rtol=1e-4)
+    # explicit K_past over a long key axis (the column pass streams key tiles head by head)
+    wl = Workload("k_past_long", 1, 4, 100, 2500, 128, "fp16", is_causal=True, seed=9)
+    ql, kl = make_inputs(wl)
+    for k_past in (2100, 2400, 2450, 5000):
+        got = fc.flash_colsum_causal(ql.cuda(), kl.cuda(), k_past=k_past).cpu().numpy()
+        assert fc.device_status() == 0
+        assert_parity(got, naive_colsum_f64(ql, kl, is_causal=True, k_past=k_past), f"long k_past {k_past}")
     default = fc.flash_colsum_causal(q.cuda(), k.cuda())
     # same kernels, same masks; only the order of the atomic adds differs between calls
     torch.testing.assert_close(default, fc.flash_colsum_causal(q.cuda(), k.cuda(), k_past=300), rtol=1e-5, atol=0)
@@ -415,7 +422,9 @@ def test_passes_run_apart_reproduce_the_call(fc):
     from flash_colsum_b200 import ops
     from flash_colsum_b200.sharded import work_shares
     for (B, H, S, D, dtype, cls, world) in [(1, 3, 1500, 64, "fp16", None, 3), (2, 2, 700, 128, "bf16", None, 2),
-                                            (1, 2, 1100, 64, "fp16", 600, 4), (1, 1, 300, 64, "fp16", None, 8)]:
+                                            (1, 2, 1100, 64, "fp16", 600, 4), (1, 1, 300, 64, "fp16", None, 8),
+                                            # few rows over many keys: the column shares take the short-query modes
+                                            (1, 2, 4200, 64, "fp16", 400, 2), (1, 2, 4200, 128, "bf16", 100, 2)]:
         w = Workload("apart", B, H, S, S, D, dtype, cls_len=cls, seed=S + world)
         q, k = make_inputs(w)
         qc, kc = q.cuda(), k.cuda()
