@@ -80,6 +80,9 @@ SHAPES = [
     (1, 3, 256, 3000, 128, "fp16", True, None),
     (2, 4, 2100, 2100, 64, "fp16", False, 200),
     (1, 40, 70, 2200, 128, "bf16", True, None),      # a head change every few tiles
+    (1, 6, 48, 2300, 128, "fp16", True, None),       # at most 64 queries: half of each tile's columns are padding
+    (1, 3, 64, 2177, 64, "bf16", True, None),
+    (2, 4, 2100, 2100, 64, "fp16", False, 40),
     # two query blocks, both resident in shared memory next to the ring of key tiles
     (1, 3, 400, 2500, 128, "bf16", True, None),
     (1, 5, 512, 2304, 64, "fp16", True, None),
@@ -457,7 +460,8 @@ def test_head_shards_accumulate_into_one_buffer(fc):
     unsharded result -- on the short-query column modes, whose consumer groups combine their sums
     in shared memory before the one add per key that this entry issues."""
     from flash_colsum_b200 import ops
-    for (H, Sq, Sk, D, dtype) in [(6, 100, 2500, 64, "bf16"),      # one query block, two key tiles per step
+    for (H, Sq, Sk, D, dtype) in [(4, 33, 2300, 128, "fp16"),      # a third of a tile's columns
+                                  (6, 100, 2500, 64, "bf16"),      # one query block, two key tiles per step
                                   (4, 256, 3000, 128, "fp16"),     # one query block, one key tile per step
                                   (6, 400, 2500, 128, "bf16"),     # two resident query blocks
                                   (4, 130, 2177, 64, "fp16")]:     # ragged: an odd number of key tiles

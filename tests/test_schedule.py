@@ -74,6 +74,8 @@ CASES = [
     (1, 3, 128, 2300, 8, True, None, 148),
     (2, 2, 100, 2100, 8, True, None, 5),        # runs cut through heads and batch entries
     (1, 2, 2100, 2100, 4, False, 200, 7),
+    (1, 3, 48, 2300, 8, True, None, 148),      # at most 64 queries: half of each tile's columns are padding
+    (2, 2, 64, 2177, 8, True, None, 5),
     # two query blocks, both resident
     (1, 3, 400, 2500, 8, True, None, 148),
     (2, 2, 512, 2304, 8, True, None, 5),
