@@ -4,13 +4,14 @@ from __future__ import annotations
 
 import ctypes
 import os
+import warnings
 from typing import Optional
 
 from . import build as _build
 
 # every symbol the header declares
 EXPORTED_SYMBOLS = (
-    "fcs_version", "fcs_last_error", "fcs_workspace_bytes",
+    "fcs_version", "fcs_last_error", "fcs_workspace_bytes", "fcs_call_workspace_bytes",
     "fcs_colsum_batched", "fcs_colsum_non_batched", "fcs_colsum_causal",
     "fcs_set_profiling", "fcs_last_pass_ms", "fcs_plan_info",
     "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate",
@@ -19,6 +20,7 @@ EXPORTED_SYMBOLS = (
     "fcs_statistics_rows", "fcs_colsum_statistics", "fcs_colsum_columns",
 )
 
+ABI_VERSION = 200   # fcs_version() of the library these argument lists were written for
 FCS_OK = 0
 FCS_DTYPE_FP16 = 0
 FCS_DTYPE_BF16 = 1
@@ -55,13 +57,20 @@ def load() -> ctypes.CDLL:
                 raise LibraryMissing(
                     f"{path} is missing and could not be built ({exc}); "
                     "run `python -m flash_colsum_b200.build` where nvcc is available") from exc
+            # an older build is all there is: it is used only if it speaks this binding's ABI (below)
+            warnings.warn(f"flash_colsum_b200: {path} is older than its sources and could not be rebuilt ({exc})")
     lib = ctypes.CDLL(path)
     lib.fcs_version.restype = _i
     lib.fcs_version.argtypes = []
+    if lib.fcs_version() != ABI_VERSION:
+        raise LibraryMissing(f"{path} reports version {lib.fcs_version()}, this binding needs {ABI_VERSION}; "
+                             "rebuild it with `python -m flash_colsum_b200.build --force`")
     lib.fcs_last_error.restype = ctypes.c_char_p
     lib.fcs_last_error.argtypes = []
     lib.fcs_workspace_bytes.restype = _sz
     lib.fcs_workspace_bytes.argtypes = [_i] * 6
+    lib.fcs_call_workspace_bytes.restype = _i
+    lib.fcs_call_workspace_bytes.argtypes = [_i] * 7 + [ctypes.POINTER(_sz)]
     lib.fcs_colsum_batched.restype = _i
     lib.fcs_colsum_batched.argtypes = [_p, _p, _p, _i64, _i, _i, _i, _i, _i] + [_i64] * 6 + \
         [_f, _i, _i, _p, _sz, _p, _p]
@@ -135,6 +144,25 @@ def set_single_pass(mode: int) -> None:
     """Kernel choice for short non-causal calls (`fcs_set_single_pass`)."""
     if load().fcs_set_single_pass(int(mode)) != FCS_OK:
         raise ValueError(f"single-pass mode must be 0, 1 or 2, got {mode}")
+    _call_workspace.clear()   # the scratch a call uses follows the kernel it takes
+
+
+_call_workspace: dict = {}   # (sizes, k_past) -> fcs_call_workspace_bytes; host arithmetic, cached per shape
+
+
+def call_workspace_bytes(B: int, H: int, sq_rows: int, Sk: int, D: int, is_causal: bool, k_past: int = -1) -> int:
+    """Scratch bytes the call with exactly these arguments uses (0: none, pass no workspace)."""
+    key = (B, H, sq_rows, Sk, D, bool(is_causal), k_past)
+    n = _call_workspace.get(key)
+    if n is None:
+        out = _sz(0)
+        if load().fcs_call_workspace_bytes(B, H, sq_rows, Sk, D, int(is_causal), int(k_past),
+                                           ctypes.byref(out)) != FCS_OK:
+            raise RuntimeError(f"flash_colsum_b200: {last_error()}")
+        n = int(out.value)
+        if len(_call_workspace) < 4096:
+            _call_workspace[key] = n
+    return n
 
 
 def last_pass_ms():

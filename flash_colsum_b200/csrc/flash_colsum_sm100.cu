@@ -1082,15 +1082,6 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     Problem p;
     memset(&p, 0, sizeof(p));
     plan(p, B, H, Sq, Sk, causal, k_past, sms, COL_INTERLEAVE_MIN_ROWS, /*head_major_ok=*/use_ext);
-    size_t part_off = 0, ext_off = 0;
-    const size_t need = workspace_layout(p, &part_off, &ext_off);
-    if (!workspace || workspace_bytes < need)
-        return fail(FCS_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
-    if (reinterpret_cast<uintptr_t>(workspace) % 256)
-        return fail(FCS_ERR_WORKSPACE, "workspace must be 256-byte aligned");
-    p.neg_lse = passes == PASSES_BOTH ? reinterpret_cast<float*>(workspace) : shared_lse;
-    p.part = reinterpret_cast<uint8_t*>(workspace) + part_off;
-    p.ext = reinterpret_cast<uint8_t*>(workspace) + ext_off;
     p.ext_bf16 = dtype == FCS_DTYPE_BF16 ? 1 : 0;
     p.out = out;
     p.out_ld = out_ld;
@@ -1127,6 +1118,16 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
             return rc;
         }
     }
+    // the two streaming passes are the only kernels that use scratch memory
+    size_t part_off = 0, ext_off = 0;
+    const size_t need = workspace_layout(p, &part_off, &ext_off);
+    if (!workspace || workspace_bytes < need)
+        return fail(FCS_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256)
+        return fail(FCS_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    p.neg_lse = passes == PASSES_BOTH ? reinterpret_cast<float*>(workspace) : shared_lse;
+    p.part = reinterpret_cast<uint8_t*>(workspace) + part_off;
+    p.ext = reinterpret_cast<uint8_t*>(workspace) + ext_off;
     CUtensorMap text = tq_b;   // placeholder when the extension is not used
     if (use_ext && (rc = make_ext_tensor_map(&text, p.ext, dtype, (long long)B * H, p.lse_rows)) != FCS_OK) return rc;
 
@@ -1234,7 +1235,7 @@ static int static_scratch_address(void** out_ptr) {
 // ---------------------------------------------------------------------------
 extern "C" {
 
-int fcs_version(void) { return 100; }
+int fcs_version(void) { return 200; }
 
 const char* fcs_last_error(void) { return fcs::g_err; }
 
@@ -1296,11 +1297,36 @@ int fcs_plan_info(int B, int H, int sq_rows, int Sk, int is_causal, int* nsplit,
 
 size_t fcs_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_causal) {
     if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0 || (D != 64 && D != 128)) return 0;
+    // An upper bound for every k_past and every kernel choice: the layout of the two streaming
+    // passes with the key range of the statistics pass split as far as any k_past allows (the
+    // split grows with the keys the first query tile sees, and k_past = Sk shows it all of them).
     fcs::Problem p;
     memset(&p, 0, sizeof(p));
-    const int k_past = Sk > sq_rows ? Sk - sq_rows : 0;
-    fcs::plan(p, B, H, sq_rows, Sk, is_causal ? 1 : 0, k_past, fcs::num_sms());
+    fcs::plan(p, B, H, sq_rows, Sk, is_causal ? 1 : 0, is_causal ? Sk : 0, fcs::num_sms());
     return fcs::workspace_layout(p, nullptr);
+}
+
+int fcs_call_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_causal, int k_past,
+                             size_t* bytes) {
+    fcs::g_err[0] = 0;
+    if (!bytes) return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "bytes is NULL");
+    *bytes = 0;
+    if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0)
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "sizes must be positive (B=%d H=%d Sq=%d Sk=%d)", B, H, sq_rows, Sk);
+    if (D != 64 && D != 128) return fcs::fail(FCS_ERR_UNSUPPORTED, "head dimension must be 64 or 128, got %d", D);
+    const int causal = is_causal ? 1 : 0;
+    // the same decisions, in the same order, as the call itself
+    if (sq_rows <= fcs::SMALLQ_MAX_ROWS && fcs::smallq_smem_bytes(sq_rows, Sk, D) <= fcs::SMALLQ_MAX_SMEM)
+        return FCS_OK;   // few-row kernel: no scratch
+    if (fcs::single_pass_applies(B, H, sq_rows, Sk, D, causal) &&
+        fcs::single_pass_max_clusters(fcs::single_pass_cluster_size(Sk)) > 0)
+        return FCS_OK;   // single-pass kernel: no scratch
+    if (causal && k_past < 0) k_past = Sk > sq_rows ? Sk - sq_rows : 0;
+    fcs::Problem p;
+    memset(&p, 0, sizeof(p));
+    fcs::plan(p, B, H, sq_rows, Sk, causal, causal ? k_past : 0, fcs::num_sms());
+    *bytes = fcs::workspace_layout(p, nullptr);
+    return FCS_OK;
 }
 
 int fcs_colsum_batched(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int S, int D,
@@ -1391,8 +1417,11 @@ int fcs_colsum_batched_static_scratch(const void* q, const void* k, float* out, 
     if (B <= 0 || H <= 0 || S <= 0 || (D != 64 && D != 128))
         return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "bad sizes (B=%d H=%d S=%d D=%d)", B, H, S, D);
     const int rows = (cls_n > 0 && cls_n < S) ? cls_n : S;
-    const size_t need = fcs_workspace_bytes(B, H, rows, S, D, 0);
-    if (need == 0 || need > (size_t)FCS_STATIC_SCRATCH_BYTES)
+    // what this call will really use: nothing when it takes the few-row or the single-pass kernel
+    size_t need = 0;
+    const int qrc = fcs_call_workspace_bytes(B, H, rows, S, D, 0, 0, &need);
+    if (qrc != FCS_OK) return qrc;
+    if (need > (size_t)FCS_STATIC_SCRATCH_BYTES)
         return fcs::fail(FCS_ERR_WORKSPACE,
                          "this call needs %zu bytes of scratch but the built-in scratch holds %zu; "
                          "use fcs_colsum_batched with a caller-provided workspace",

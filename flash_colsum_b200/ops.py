@@ -88,18 +88,35 @@ def _prepare(query: torch.Tensor, key: torch.Tensor) -> Tuple[torch.Tensor, torc
     return _tma_ready(query), _tma_ready(key), _DTYPE_CODE[query.dtype]
 
 
-_workspace_bytes: Dict[tuple, int] = {}   # (sizes) -> fcs_workspace_bytes, pure host arithmetic
+class _NoWorkspace:
+    """Stands in for the scratch tensor of a call that uses none."""
+
+    @staticmethod
+    def data_ptr() -> int:
+        return 0
+
+    @staticmethod
+    def numel() -> int:
+        return 0
 
 
-def _workspace(lib, device, B, H, rows, Sk, D, causal) -> torch.Tensor:
-    key = (B, H, rows, Sk, D, causal)
-    n = _workspace_bytes.get(key)
-    if n is None:
-        n = lib.fcs_workspace_bytes(B, H, rows, Sk, D, int(causal))
-        if n == 0:
-            raise RuntimeError("flash_colsum_b200: fcs_workspace_bytes rejected the sizes")
-        if len(_workspace_bytes) < 4096:
-            _workspace_bytes[key] = n
+_NO_WORKSPACE = _NoWorkspace()
+
+
+def _workspace(lib, device, B, H, rows, Sk, D, causal, k_past: int = -1):
+    """Scratch for exactly this call: nothing is allocated when the call takes the few-row or
+    the single-pass kernel, and a causal call is sized for the ``k_past`` it passes."""
+    n = _cabi.call_workspace_bytes(B, H, rows, Sk, D, causal, k_past)
+    if n == 0:
+        return _NO_WORKSPACE
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+def _workspace_two_pass(lib, device, B, H, rows, Sk, D) -> torch.Tensor:
+    """Scratch for an entry point that always runs a streaming pass (the passes run apart)."""
+    n = lib.fcs_workspace_bytes(B, H, rows, Sk, D, 0)
+    if n == 0:
+        raise RuntimeError("flash_colsum_b200: fcs_workspace_bytes rejected the sizes")
     return torch.empty(n, dtype=torch.uint8, device=device)
 
 
@@ -158,7 +175,7 @@ def _flash_colsum_causal(Q: torch.Tensor, K: torch.Tensor, scale: float, K_past:
             if out.dtype != torch.float32 or out.numel() != K_len or not out.is_contiguous():
                 raise ValueError("accumulate_into must be a contiguous fp32 tensor with K_len elements")
             entry = lib.fcs_colsum_causal_accumulate
-        ws = _workspace(lib, Q.device, 1, H, Q_len, K_len, D, True)
+        ws = _workspace(lib, Q.device, 1, H, Q_len, K_len, D, True, -1 if K_past is None else int(K_past))
         _check(entry(
             Q.data_ptr(), K.data_ptr(), out.data_ptr(), H, Q_len, K_len, D, code,
             Q.stride(1), Q.stride(2), K.stride(1), K.stride(2),
@@ -280,7 +297,7 @@ def flash_colsum_causal(
     K_len = K.shape[2]
     with _on_device(Q.device):
         out = torch.empty((B, K_len), device=Q.device, dtype=torch.float32)
-        ws = _workspace(lib, Q.device, B, H, Q_len, K_len, D, True)
+        ws = _workspace(lib, Q.device, B, H, Q_len, K_len, D, True, -1 if k_past is None else int(k_past))
         _check(lib.fcs_colsum_causal_batched(
             Q.data_ptr(), K.data_ptr(), out.data_ptr(), K_len, B, H, Q_len, K_len, D, code,
             Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
@@ -312,7 +329,7 @@ def colsum_statistics(query_rows: torch.Tensor, key: torch.Tensor, scale: float,
     Sk = K.shape[2]
     with _on_device(Q.device):
         lse = torch.full((B * H, statistics_rows(rows)), float("-inf"), dtype=torch.float32, device=Q.device)
-        ws = _workspace(lib, Q.device, B, H, rows, Sk, D, False)
+        ws = _workspace_two_pass(lib, Q.device, B, H, rows, Sk, D)
         _check(lib.fcs_colsum_statistics(
             Q.data_ptr(), K.data_ptr(), lse.data_ptr(), B, H, rows, Sk, D, code,
             Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),
@@ -336,7 +353,7 @@ def colsum_columns(query: torch.Tensor, key_rows: torch.Tensor, neg_lse: torch.T
         raise ValueError(f"neg_lse must be contiguous fp32 of shape {(B * H, statistics_rows(rows))}")
     with _on_device(Q.device):
         out = torch.empty((B, k_rows), device=Q.device, dtype=torch.float32)
-        ws = _workspace(lib, Q.device, B, H, rows, k_rows, D, False)
+        ws = _workspace_two_pass(lib, Q.device, B, H, rows, k_rows, D)
         _check(lib.fcs_colsum_columns(
             Q.data_ptr(), K.data_ptr(), neg_lse.data_ptr(), out.data_ptr(), k_rows, B, H, rows, k_rows, D, code,
             Q.stride(0), Q.stride(1), Q.stride(2), K.stride(0), K.stride(1), K.stride(2),

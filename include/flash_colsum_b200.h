@@ -17,7 +17,8 @@
  *   - h_norm: number of heads the mean is taken over.  Pass H, or the global
  *     head count when this call sees only a shard of the heads and the partial
  *     results are summed afterwards.
- *   - workspace: device scratch of at least fcs_workspace_bytes(...) bytes,
+ *   - workspace: device scratch of at least fcs_call_workspace_bytes(...) bytes
+ *     (fcs_workspace_bytes(...) is an upper bound that needs no k_past),
  *     256-byte aligned, owned by the caller, not preserved between calls.
  *   - status: optional device int (may be NULL), zeroed by the caller once.  A
  *     device-side wait that ran out of time stores a non-zero code there; the
@@ -57,11 +58,27 @@ int fcs_version(void);
 const char *fcs_last_error(void);
 
 /*
- * Scratch bytes a call with these sizes needs on the current device.
- * `sq_rows` is the number of query rows that enter the mean (S, or
- * min(cls_len, S)).  Returns 0 on invalid sizes.
+ * Scratch bytes that are enough for ANY call with these sizes on the current
+ * device: every k_past a causal call may pass, and whichever kernel the call
+ * takes.  `sq_rows` is the number of query rows that enter the mean (S, or
+ * min(cls_len, S)).  Returns 0 on invalid sizes.  The reference's launchers
+ * allocate their own scratch with torch (flash_colsum/kernel_causal.py:104);
+ * here the caller owns it.
  */
 size_t fcs_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_causal);
+
+/*
+ * Scratch bytes the call with exactly these arguments will use, written to
+ * *bytes: 0 when it takes the few-row kernel (at most four query rows) or the
+ * single-pass kernel (see fcs_set_single_pass), which use none -- such a call
+ * may pass workspace = NULL -- otherwise the layout of the two streaming passes
+ * for this k_past (k_past < 0: the inferred max(0, Sk - sq_rows); ignored when
+ * not causal).  The answer follows the kernel choice in force when it is asked:
+ * ask again after fcs_set_single_pass.  Never more than fcs_workspace_bytes().
+ * Returns FCS_OK or an FCS_ERR_* code for sizes no call accepts.
+ */
+int fcs_call_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_causal, int k_past,
+                             size_t *bytes);
 
 /*
  * Batched non-causal column mean: out[b, k] = mean over h and over the first
@@ -156,8 +173,10 @@ int fcs_colsum_causal_accumulate(const void *q, const void *k, float *out,
  *
  * Same arguments and result as fcs_colsum_batched, minus the workspace.
  *   - Limit: the call must need no more than FCS_STATIC_SCRATCH_BYTES of
- *     scratch (fcs_workspace_bytes(B, H, rows, S, D, 0)); larger problems are
- *     rejected with FCS_ERR_WORKSPACE and a message, nothing is launched.
+ *     scratch (fcs_call_workspace_bytes(B, H, rows, S, D, 0, 0, &n): calls
+ *     that take the few-row or the single-pass kernel need none and are never
+ *     refused); larger problems are rejected with FCS_ERR_WORKSPACE and a
+ *     message, nothing is launched.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current) and caches it.  Make
  *     that first call outside any stream capture.

@@ -296,3 +296,14 @@ extern "C" int check_tile_ranges(long long units, int NQ, int H, int clusters, i
     }
     return expect == units * NQ ? 0 : -9;
 }
+
+// Scratch bytes the two streaming passes use for a call planned with this k_past on `sms`
+// SMs: the plan and the layout of the kernels' own header, as the library's call computes them.
+extern "C" long long scratch_need(int B, int H, int Sq, int Sk, int causal, int k_past, int sms, int* nsplit_out) {
+    if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    plan(p, B, H, Sq, Sk, causal, k_past, sms);
+    if (nsplit_out) *nsplit_out = p.nsplit;
+    return (long long)workspace_layout(p, nullptr);
+}

@@ -21,7 +21,7 @@ def test_library_builds_and_exports_every_declared_symbol():
     assert declared == set(_cabi.EXPORTED_SYMBOLS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.fcs_version() >= 100
+    assert lib.fcs_version() == _cabi.ABI_VERSION
     assert os.path.samefile(os.path.dirname(build.LIB_PATH), os.path.join(ROOT, "flash_colsum_b200", "_lib"))
 
 

@@ -245,6 +245,32 @@ def _torch_fp32_reference(q, k, causal, cls_len, head_chunk):
     return (acc / (H * rows)).cpu().numpy()
 
 
+def test_full_size_reference_agrees_with_the_pinned_checker(fc, golden):
+    """The materialising evaluation the full-size tests compare with is itself checked here: on
+    stored outputs of the reference's naive_colsum and against the C checker, non-causal, causal
+    and with a CLS prefix, so that the full-size comparisons hang off the pinned oracle."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        cases, arrays = golden
+        ran = 0
+        for w, _ in cases:
+            if w.dtype == "fp32" or w.B * w.H * w.Sq * w.Sk > (1 << 24):
+                continue
+            if w.is_causal and w.Sk < w.Sq:
+                continue     # the full-size shapes all have K_len >= Q_len
+            q, k = make_inputs(w)
+            got = _torch_fp32_reference(q.cuda(), k.cuda(), w.is_causal, w.cls_len, 2)
+            rel, mx = parity_errors(got, arrays[w.name])
+            assert rel <= 1e-5 and mx <= 1e-5, (w.name, rel, mx)
+            rel, mx = parity_errors(got, c_oracle.colsum_c(q, k, is_causal=w.is_causal, cls_len=w.cls_len))
+            assert rel <= 1e-5 and mx <= 1e-5, (w.name, rel, mx)
+            ran += 1
+        assert ran >= 8
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
 @pytest.mark.parametrize("name,chunk", [("c2", 4), ("c2_kq", 4), ("c3", 16), ("c4", 32)])
 def test_headline_workloads_full_size(fc, name, chunk):
     prev = torch.backends.cuda.matmul.allow_tf32
@@ -380,6 +406,14 @@ def test_batched_causal_and_explicit_k_past(fc):
         got = fc.flash_colsum_causal(ql.cuda(), kl.cuda(), k_past=k_past).cpu().numpy()
         assert fc.device_status() == 0
         assert_parity(got, naive_colsum_f64(ql, kl, is_causal=True, k_past=k_past), f"long k_past {k_past}")
+    # explicit K_past that splits the key range of the statistics pass further than the inferred
+    # value would (the scratch is sized for the K_past the call passes), and one beyond the keys
+    for (H, Sq, Sk, k_past) in ((1, 300, 400, 300), (1, 512, 400, 1000), (8, 1024, 1024, 1024)):
+        ws = Workload("k_past_scratch", 1, H, Sq, Sk, 128, "bf16", is_causal=True, seed=10)
+        qs, ks = make_inputs(ws)
+        got = fc.flash_colsum_causal(qs.cuda(), ks.cuda(), k_past=k_past).cpu().numpy()
+        assert fc.device_status() == 0
+        assert_parity(got, naive_colsum_f64(qs, ks, is_causal=True, k_past=k_past), f"scratch k_past {H} {Sq} {Sk} {k_past}")
     default = fc.flash_colsum_causal(q.cuda(), k.cuda())
     # same kernels, same masks; only the order of the atomic adds differs between calls
     torch.testing.assert_close(default, fc.flash_colsum_causal(q.cuda(), k.cuda(), k_past=300), rtol=1e-5, atol=0)

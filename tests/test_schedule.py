@@ -30,6 +30,8 @@ def emu():
     lib.emulate_colsum.restype = ctypes.c_int
     lib.emulate_colsum.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 5 + [ctypes.c_float] + \
         [ctypes.c_int] * 5 + [ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
+    lib.scratch_need.restype = ctypes.c_longlong
+    lib.scratch_need.argtypes = [ctypes.c_int] * 7 + [ctypes.c_void_p]
     return lib
 
 
@@ -159,3 +161,57 @@ def test_explicit_k_past_and_negative_scale_and_head_norm(emu):
 ])
 def test_single_pass_work_split_covers_every_tile_once(emu, units, NQ, H, clusters, flush_units):
     assert emu.check_tile_ranges(units, NQ, H, clusters, flush_units) == 0
+
+
+def test_scratch_queries_cover_every_k_past(emu):
+    """Walk (B, H, Sq, Sk, k_past) on the host: the library's upper bound is never below what the
+    plan of any k_past lays out, and the per-call query returns exactly that layout (shapes that
+    take a kernel without scratch are asked with more than four query rows and 128 head dims, so
+    that the streaming passes are what runs).  An explicit k_past shows the first query tile
+    more keys than the inferred one, which can split its key range further."""
+    from flash_colsum_b200 import _cabi
+    lib = _cabi.load()
+    sms = _cabi.plan_info(1, 1, 128, 128, False)["sms"]
+    need = ctypes.c_size_t(0)
+    walked = shortfalls = grew = 0
+    for B in (1, 2, 5):
+        for H in (1, 3, 8, 32):
+            for Sq in (5, 100, 128, 300, 512, 1024, 1500):
+                for Sk in (40, 400, 1024, 4096, 20000):
+                    bound = lib.fcs_workspace_bytes(B, H, Sq, Sk, 128, 1)
+                    inferred = emu.scratch_need(B, H, Sq, Sk, 1, -1, sms, None)
+                    for k_past in (0, 1, 100, 255, 300, 1000, Sk - 1, Sk, Sk + 77, 3 * Sk, max(0, Sk - Sq)):
+                        truth = emu.scratch_need(B, H, Sq, Sk, 1, k_past, sms, None)
+                        walked += 1
+                        grew += truth > inferred
+                        shortfalls += truth > bound
+                        assert lib.fcs_call_workspace_bytes(B, H, Sq, Sk, 128, 1, k_past, ctypes.byref(need)) == 0
+                        assert need.value == truth, (B, H, Sq, Sk, k_past)
+                    assert lib.fcs_call_workspace_bytes(B, H, Sq, Sk, 128, 1, -1, ctypes.byref(need)) == 0
+                    assert need.value == inferred
+                    # non-causal: one layout
+                    assert lib.fcs_workspace_bytes(B, H, Sq, Sk, 128, 0) == emu.scratch_need(B, H, Sq, Sk, 0, 0, sms, None)
+    assert shortfalls == 0, f"{shortfalls} of {walked} combinations need more scratch than the bound"
+    assert grew > 0          # the walk does reach plans that an inferred k_past would have undersized
+    # the combination that first showed the gap: one more key range at k_past = 300
+    n_inf, n_exp = ctypes.c_int(0), ctypes.c_int(0)
+    a = emu.scratch_need(1, 1, 300, 400, 1, -1, sms, ctypes.addressof(n_inf))
+    b = emu.scratch_need(1, 1, 300, 400, 1, 300, sms, ctypes.addressof(n_exp))
+    assert (n_inf.value, n_exp.value) == (1, 2) and b > a
+    assert lib.fcs_workspace_bytes(1, 1, 300, 400, 128, 1) >= b
+
+
+def test_calls_that_take_a_kernel_without_scratch_ask_for_none():
+    from flash_colsum_b200 import _cabi
+    lib = _cabi.load()
+    need = ctypes.c_size_t(7)
+    # CLS prefix of the CLIP-style shape: the few-row kernel
+    assert lib.fcs_call_workspace_bytes(32, 16, 1, 577, 64, 0, 0, ctypes.byref(need)) == 0 and need.value == 0
+    # four decode queries over a long key axis, causal
+    assert lib.fcs_call_workspace_bytes(1, 32, 4, 8192, 128, 1, -1, ctypes.byref(need)) == 0 and need.value == 0
+    # five rows: the streaming passes
+    assert lib.fcs_call_workspace_bytes(1, 32, 5, 8192, 128, 1, -1, ctypes.byref(need)) == 0 and need.value > 0
+    # sizes no call accepts
+    assert lib.fcs_call_workspace_bytes(1, 1, 1, 1, 96, 0, 0, ctypes.byref(need)) == -2
+    assert lib.fcs_call_workspace_bytes(0, 1, 1, 1, 64, 0, 0, ctypes.byref(need)) == -1
+    assert lib.fcs_call_workspace_bytes(1, 1, 1, 1, 64, 0, 0, None) == -1
