@@ -12,7 +12,11 @@ D=128, bf16) with its 32 heads split over the ranks and one NCCL all-reduce of
 the fp32 per-key partials (strong scaling) under "causal_long_context", and the reference's
 batched sweep shape (B=128 H=16 S=1024 per GPU), which takes the single-pass cluster kernel,
 next to the two-pass kernels on the same inputs under "short_key_axis", and a point of the
-reference's causal sweep (H=32 Q=128 K=65536 D=128), which is bound by HBM, under "causal_suffix".
+reference's causal sweep (H=32 Q=128 K=65536 D=128), which is bound by HBM, under "causal_suffix",
+the CLIP-style CLS call (B=32 H=16 S=577, cls_len=1; bound by HBM) under "cls_prefix" and the
+decode-suffix call (H=32 Q=128 K=4096 D=128; bound by launches) under "causal_short".  The
+long-context leg carries a "parity" object: its result against a materialising fp32 evaluation
+of all heads (every rank evaluates its own heads, the sums meet in one NCCL all-reduce).
 
 Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
 the reference's materialising implementation on the host cores instead.
@@ -114,10 +118,6 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def workload_call(fc, w: Workload, q, k, h_norm_fn=None):
-    return fc.flash_colsum(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
-
-
 def time_steps(fn, steps, warmup, flush_buf, barrier=None):
     """Per-step CUDA-event timing with an untimed L2 flush before every step."""
     for _ in range(warmup):
@@ -140,29 +140,74 @@ def time_steps(fn, steps, warmup, flush_buf, barrier=None):
     return [s.elapsed_time(e) for s, e in zip(starts, ends)]
 
 
-def cpu_port_tflops(w: Workload, budget_s: float, batch_entries: int):
-    """The CPU restatement of the reference on a bounded sample of `w`."""
+def cpu_implementation():
+    """The materialising CPU implementation to time: the reference's own ``naive_colsum`` when an
+    install of the reference sits in baseline/_ref (flash_colsum/baselines.py:13-78, unmodified),
+    else this repository's restatement of it under oracle/."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if os.path.isdir(os.path.join(ref_dir, "flash_colsum")):
+        try:
+            if ref_dir not in sys.path:
+                sys.path.append(ref_dir)
+            from flash_colsum.baselines import naive_colsum
+            return naive_colsum, "reference", "naive_colsum of the reference installed in baseline/_ref"
+        except Exception:
+            pass
     from oracle.naive_colsum import naive_colsum_torch
+    return naive_colsum_torch, "port", "CPU restatement of naive_colsum (oracle/naive_colsum.py)"
+
+
+def cpu_port_tflops(w: Workload, budget_s: float, batch_entries: int):
+    """The CPU implementation of the reference on a bounded sample of `w`."""
+    fn, kind, what = cpu_implementation()
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     sample = Workload(w.name + "_sample", min(batch_entries, w.B), w.H, w.Sq, w.Sk, w.D, w.dtype,
                       w.is_causal, w.cls_len, w.key_outliers, w.key_is_query, w.seed)
     q, k = make_inputs(sample)
     q, k = q.float(), k.float()
-    naive_colsum_torch(q, k, is_causal=w.is_causal, cls_len=w.cls_len)   # warm-up
+    fn(q, k, is_causal=w.is_causal, cls_len=w.cls_len)   # warm-up
     times = []
     t_end = time.perf_counter() + budget_s
     while True:
         t0 = time.perf_counter()
-        naive_colsum_torch(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
+        fn(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
         times.append(time.perf_counter() - t0)
         if time.perf_counter() > t_end or len(times) >= 50:
             break
     best = statistics.median(times)
     return {"value": sample.flop / best / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),
-            "kind": "port",
-            "sample": (f"{sample.B} of {w.B} batch entries of {w.name} in fp32, "
+            "kind": kind,
+            "sample": (f"{what}: {sample.B} of {w.B} batch entries of {w.name} in fp32, "
                        f"median of {len(times)} calls of {best * 1e3:.1f} ms; host has "
                        f"{os.cpu_count()} logical cores")}, best, sample
+
+
+def reference_gpu_same_box(w: Workload, steps: int):
+    """The reference's own Triton `flash_colsum` (flash_colsum/ops.py:13) on this box's GPU, from
+    the install in baseline/_ref: context for the CPU figure, not part of it.  Returns a dict with
+    `ms_per_call` and `value`, or with `unavailable`."""
+    try:
+        if not torch.cuda.is_available():
+            return {"unavailable": "no CUDA device"}
+        ref_dir = os.path.join(ROOT, "baseline", "_ref")
+        if not os.path.isdir(os.path.join(ref_dir, "flash_colsum")):
+            return {"unavailable": "no install of the reference in baseline/_ref"}
+        if ref_dir not in sys.path:
+            sys.path.append(ref_dir)
+        from flash_colsum import flash_colsum as ref_flash_colsum
+        dev = torch.device("cuda", 0)
+        q, k = (t.to(dev) for t in make_inputs(w))
+        flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            ref_flash_colsum(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
+        torch.cuda.synchronize()
+        n = max(3, min(steps, 20))
+        t = time_steps(lambda: ref_flash_colsum(q, k, is_causal=w.is_causal, cls_len=w.cls_len), n, 1, flush)
+        ms = sum(t) / len(t)
+        return {"what": "reference Triton flash_colsum on cuda:0, same inputs, L2 flushed per call",
+                "ms_per_call": ms, "value": w.flop / (ms * 1e-3) / 1e12, "unit": UNIT, "steps": n}
+    except Exception as exc:   # Triton could not compile or run here
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
 
 
 def run_reference_arm(args):
@@ -170,20 +215,20 @@ def run_reference_arm(args):
     if rank != 0:
         return
     w = WORKLOADS["c2"]
-    from oracle.naive_colsum import naive_colsum_torch
+    fn, kind, what = cpu_implementation()
     # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1 to its ranks)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     sample = Workload("c2_sample", 1, w.H, w.Sq, w.Sk, w.D, w.dtype, seed=w.seed)
     q, k = make_inputs(sample)
     q, k = q.float(), k.float()
     for _ in range(max(1, min(args.warmup, 2))):
-        naive_colsum_torch(q, k)
+        fn(q, k)
     times = []
     # one step = one batch entry on the host cores; bounded so that the run ends in minutes
     t_stop = time.perf_counter() + 120.0
     for _ in range(args.steps):
         t0 = time.perf_counter()
-        naive_colsum_torch(q, k)
+        fn(q, k)
         times.append(time.perf_counter() - t0)
         if time.perf_counter() > t_stop:
             break
@@ -197,11 +242,13 @@ def run_reference_arm(args):
         "config": {"workload": WORKLOAD_LABEL, "flop_count": "4*B*H*Sq*Sk*D (two passes)",
                    "step": "one batch entry (B=1) of the workload per step, fp32 on the host cores",
                    "l2": "host run"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": "1 of 8 batch entries per step, CPU restatement of naive_colsum in fp32"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": f"1 of 8 batch entries per step, {what} in fp32"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if not args.no_gpu_reference:
+        line["reference_gpu_same_box"] = reference_gpu_same_box(w, args.steps)
     print(json.dumps(line), flush=True)
 
 
@@ -250,6 +297,67 @@ def kernel_only(args, fc, _cabi, dev, flush_buf, peaks):
         "status": fc.device_status()}), flush=True)
 
 
+def long_context_parity(q5, k5, w5, out5, world, rank, dev, dist, used_peer, nccl_call):
+    """The head-sharded long-context result against a materialising fp32 evaluation of ALL heads:
+    every rank evaluates its own heads (two at a time), the un-normalised sums meet in one NCCL
+    all-reduce, rank 0 compares.  With the in-kernel peer-memory reduce, also that result
+    against the NCCL all-reduce of the same partials."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        h_local, Sq, Sk, D = q5.shape[1], q5.shape[2], k5.shape[2], q5.shape[3]
+        acc = torch.zeros(Sk, dtype=torch.float64, device=dev)
+        vis = (torch.arange(Sk, device=dev)[None, :] <= (Sk - Sq + torch.arange(Sq, device=dev))[:, None])
+        for h0 in range(0, h_local, 2):
+            s = torch.matmul(q5[0, h0:h0 + 2].float(), k5[0, h0:h0 + 2].float().transpose(-1, -2)) / D ** 0.5
+            s.masked_fill_(~vis, float("-inf"))
+            acc += torch.softmax(s, dim=-1).sum(dim=(0, 1), dtype=torch.float64)
+            del s
+        if dist is not None:
+            dist.all_reduce(acc)
+        want = acc / (w5.H * Sq)
+        got = out5.reshape(-1).double()
+        res = {"vs": "fp32 materialised, all heads", "n_gpus": world,
+               "rel_l2": float(((got - want).norm() / want.norm()).item()),
+               "max_abs": float(((got - want).abs().max() / want.max()).item()),
+               "max_abs_unit": "fraction of the largest column mean", "tolerance": 1e-3}
+        if used_peer:
+            via_nccl = nccl_call().reshape(-1).double()
+            res["peer_reduce_vs_nccl_all_reduce"] = {
+                "rel_l2": float(((got - via_nccl).norm() / via_nccl.norm()).item()),
+                "max_abs": float(((got - via_nccl).abs().max() / via_nccl.max()).item())}
+        # only rank 0's figures are printed; with the peer-memory reduce only rank 0 holds the result
+        return res
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def small_call_leg(fc, _cabi, w, q, k, steps, flush_buf, barrier, max_over_ranks, peaks):
+    """One of the short calls through the public operator: ms per call (L2 flushed before each),
+    back-to-back issue rate, and the library's own event times of the device passes."""
+    call = lambda: fc.flash_colsum(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
+    t = time_steps(call, steps, 3, flush_buf, barrier)
+    ms = max_over_ranks(sum(t) / len(t))
+    # back to back, no flush: what a caller issuing many such calls sees (host-bound if above the kernel time)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(200):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    b2b = e0.elapsed_time(e1) / 200
+    _cabi.set_profiling(True)
+    rows = []
+    for _ in range(max(5, steps)):
+        flush_buf.zero_()
+        call()
+        rows.append(_cabi.last_pass_ms())
+    _cabi.set_profiling(False)
+    st, mg, col = (sum(r[i] for r in rows) / len(rows) for i in range(3))
+    return ms, b2b, st, mg, col
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -258,6 +366,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
     ap.add_argument("--skip-long-context", action="store_true")
+    ap.add_argument("--no-gpu-reference", action="store_true",
+                    help="reference arm: do not also time the reference's Triton kernels on the GPU")
     ap.add_argument("--nccl-reduce", action="store_true",
                     help="reduce the head-sharded partials with an NCCL all-reduce instead of peer-memory atomics")
     ap.add_argument("--kernel-only", action="store_true",
@@ -348,6 +458,9 @@ def main():
         "bound": "tensor", "kernel": "colsum_stream_kernel<64, statistics pass>",
         "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
         "peak_source": f"{peaks['source']} bf16 burst", "traffic": load_traffic("stats_pass_c2"),
+        "traffic_source": ("constant from profiles/dram_traffic.json: one ncu capture of this kernel at "
+                           "batch 2 of the same shape, scaled by 4 to the batch of 8 (the traffic is the "
+                           "inputs once per pass and grows with the batch)"),
         "launch_ms": stats_avg, "flop_per_launch": pass_flop,
         "other_kernels": {"column pass": {"launch_ms": col_avg,
                                           "achieved": pass_flop / (col_avg * 1e-3) / 1e12,
@@ -406,11 +519,13 @@ def main():
         ms5 = max_over_ranks(sum(t5) / len(t5))
         out5 = long_step()
         torch.cuda.synchronize()
+        parity5 = long_context_parity(q5, k5, w5, out5, world, rank, dev, dist, peer is not None,
+                                      lambda: flash_colsum_head_sharded(q5, k5, w5.H, is_causal=True, peer=None))
         long_ctx = {"workload": "c5: causal H=32 Q=512 K=131072 D=128 bf16, outlier keys",
                     "parallelism": f"heads sharded over {world} GPU(s); reduce: {reduce_kind}",
                     "scaling": "strong", "ms_per_call": ms5, "value": w5.flop / (ms5 * 1e-3) / 1e12,
                     "unit": UNIT, "frac_of_peak": w5.flop / (ms5 * 1e-3) / 1e12 / peaks["tflops"],
-                    "row_sum_on_rank0": float(out5.sum().item())}
+                    "row_sum_on_rank0": float(out5.sum().item()), "parity": parity5}
         del q5, k5
     assert fc.device_status() == 0
 
@@ -459,6 +574,40 @@ def main():
         del qq, kq
     assert fc.device_status() == 0
 
+    # ------------------------------------------------------------ CLS prefix (C3) and decode suffix (C4)
+    cls_prefix = causal_short = None
+    if not args.skip_long_context:
+        n_small = max(10, min(args.steps // 2, 50))
+        w3 = WORKLOADS["c3"]
+        q3, k3 = (t.to(dev) for t in make_inputs(Workload(w3.name, w3.B, w3.H, w3.Sq, w3.Sk, w3.D, w3.dtype,
+                                                          cls_len=w3.cls_len, seed=w3.seed + rank)))
+        ms3, b2b3, _, _, kern3 = small_call_leg(fc, _cabi, w3, q3, k3, n_small, flush_buf, barrier, max_over_ranks, peaks)
+        bytes3 = w3.min_bytes     # the keys once, the CLS query rows, the output
+        cls_prefix = {"workload": "c3: non-causal B=32 H=16 S=577 D=64 fp16, cls_len=1, per GPU",
+                      "kernel": "colsum_small_q_kernel (clusters over key ranges, bulk-copy ring) behind clear_rows_kernel",
+                      "ms_per_call": ms3, "ms_per_call_back_to_back": b2b3, "kernel_ms": kern3,
+                      "tflops_rows_used": w3.flop_rows_used / (ms3 * 1e-3) / 1e12,
+                      "roofline": {"bound": "hbm", "achieved": bytes3 / (kern3 * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                                   "unit": "GB/s", "frac": bytes3 / (kern3 * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                   "bytes_per_launch": bytes3,
+                                   "bytes": "every key once + the CLS rows + the output; event time of the two kernels of the call",
+                                   "frac_of_call": bytes3 / (ms3 * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
+        del q3, k3
+        w4 = WORKLOADS["c4"]
+        q4, k4 = (t.to(dev) for t in make_inputs(Workload(w4.name, w4.B, w4.H, w4.Sq, w4.Sk, w4.D, w4.dtype,
+                                                          is_causal=True, seed=w4.seed + rank)))
+        ms4, b2b4, st4, mg4, col4 = small_call_leg(fc, _cabi, w4, q4, k4, n_small, flush_buf, barrier, max_over_ranks, peaks)
+        causal_short = {"workload": "c4: causal H=32 Q=128 K=4096 D=128 fp16 per GPU",
+                        "ms_per_call": ms4, "ms_per_call_back_to_back": b2b4,
+                        "pass_ms": {"statistics": st4, "merge": mg4, "columns": col4},
+                        "value": w4.flop / (ms4 * 1e-3) / 1e12, "unit": UNIT,
+                        "roofline": {"bound": "tensor", "achieved": w4.flop / (ms4 * 1e-3) / 1e12, "peak": peaks["tflops"],
+                                     "unit": UNIT, "frac": w4.flop / (ms4 * 1e-3) / 1e12 / peaks["tflops"],
+                                     "note": ("launch-bound: three kernels of a few microseconds each, chained by programmatic "
+                                              "dependent launch; 8.6 GFLOP would take 5 us at the peak")}}
+        del q4, k4
+    assert fc.device_status() == 0
+
     # ------------------------------------------------------------ CPU baseline (rank 0, one GPU only)
     cpu = None
     if rank == 0 and world == 1:
@@ -484,6 +633,8 @@ def main():
             "causal_long_context": long_ctx,
             "short_key_axis": short_keys,
             "causal_suffix": suffix,
+            "cls_prefix": cls_prefix,
+            "causal_short": causal_short,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -855,9 +855,11 @@ static int check_operand(const char* name, const void* ptr, int64_t sb, int64_t 
     return FCS_OK;
 }
 
-// Few query rows: the matrix-vector kernel (memset of the output, then one launch).
+// Few query rows: the matrix-vector kernel (a kernel that clears the output, then the
+// clustered kernel as its programmatic dependent).
 template <int D, bool BF16, int RMAX>
-static cudaError_t launch_small_q_r(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream) {
+static cudaError_t launch_small_q_r(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream,
+                                    bool after_clear) {
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -867,39 +869,68 @@ static cudaError_t launch_small_q_r(const SmallQParams& sp, int grid, size_t sme
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    kern<<<grid, SMALLQ_THREADS, smem, stream>>>(sp);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(SMALLQ_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = (unsigned)sp.CL;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    // behind the clearing kernel: start at once, wait for it only before the adds
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = after_clear ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, sp);
 }
 
 template <int D, bool BF16>
-static cudaError_t launch_small_q_t(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream) {
-    if (sp.R == 1) return launch_small_q_r<D, BF16, 1>(sp, grid, smem, stream);
-    if (sp.R == 2) return launch_small_q_r<D, BF16, 2>(sp, grid, smem, stream);
-    return launch_small_q_r<D, BF16, 4>(sp, grid, smem, stream);
+static cudaError_t launch_small_q_t(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream,
+                                    bool after_clear) {
+    if (sp.R == 1) return launch_small_q_r<D, BF16, 1>(sp, grid, smem, stream, after_clear);
+    if (sp.R == 2) return launch_small_q_r<D, BF16, 2>(sp, grid, smem, stream, after_clear);
+    return launch_small_q_r<D, BF16, 4>(sp, grid, smem, stream, after_clear);
 }
 
 static int launch_small_q(const void* q, const void* k, float* out, int64_t out_ld, int B, int H, int R, int Sk,
                           int D, int dtype, int64_t qsb, int64_t qsh, int64_t qss, int64_t ksb, int64_t ksh,
                           int64_t kss, float scale, int causal, int k_past, int h_norm, bool clear_out,
-                          cudaStream_t stream) {
-    cudaError_t e = cudaSuccess;
-    if (clear_out)
-        e = cudaMemset2DAsync(out, (size_t)out_ld * sizeof(float), 0, (size_t)Sk * sizeof(float), (size_t)B, stream);
-    if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "clearing the output failed: %s", cudaGetErrorString(e));
+                          int* status, cudaStream_t stream) {
+    const int sms = num_sms();
+    if (clear_out) {
+        long long blocks = ((long long)B * Sk + 1023) / 1024;
+        if (blocks > sms) blocks = sms;
+        clear_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(out, (long long)out_ld, B, Sk);
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "clearing the output failed: %s", cudaGetErrorString(e));
+    }
     SmallQParams sp;
+    memset(&sp, 0, sizeof(sp));
     sp.q = q; sp.k = k; sp.out = out; sp.out_ld = out_ld;
     sp.H = H; sp.R = R; sp.Sk = Sk;
     sp.qsb = qsb; sp.qsh = qsh; sp.qss = qss; sp.ksb = ksb; sp.ksh = ksh; sp.kss = kss;
     sp.c = scale * 1.4426950408889634f;
     sp.causal = causal; sp.k_past = causal ? k_past : 0;
     sp.inv_norm = 1.0f / ((float)h_norm * (float)R);
-    const size_t smem = smallq_smem_bytes(R, Sk, D);
-    const int grid = B * H;
+    sp.status = status;
+    // keys past the last query's horizon are seen by no row: not read, their columns stay zero
+    long long keys = Sk;
+    if (causal && (long long)k_past + R < keys) keys = (long long)k_past + R;
+    sp.keys = (int)keys;
+    size_t smem = 0;
+    smallq_plan(B * H, R, sp.keys, D, sms, &sp.CL, &sp.range_rows, &sp.stages, &smem);
+    if (smem > SMALLQ_MAX_SMEM) return fail(FCS_ERR_UNSUPPORTED, "few-row kernel: %d keys do not fit", Sk);
+    const int grid = B * H * sp.CL;
     const bool bf16 = dtype == FCS_DTYPE_BF16;
-    e = (D == 64) ? (bf16 ? launch_small_q_t<64, true>(sp, grid, smem, stream)
-                          : launch_small_q_t<64, false>(sp, grid, smem, stream))
-                  : (bf16 ? launch_small_q_t<128, true>(sp, grid, smem, stream)
-                          : launch_small_q_t<128, false>(sp, grid, smem, stream));
+    const cudaError_t e =
+        (D == 64) ? (bf16 ? launch_small_q_t<64, true>(sp, grid, smem, stream, clear_out)
+                          : launch_small_q_t<64, false>(sp, grid, smem, stream, clear_out))
+                  : (bf16 ? launch_small_q_t<128, true>(sp, grid, smem, stream, clear_out)
+                          : launch_small_q_t<128, false>(sp, grid, smem, stream, clear_out));
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "few-row kernel launch failed: %s", cudaGetErrorString(e));
     return FCS_OK;
 }
@@ -1062,7 +1093,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
-    if (passes == PASSES_BOTH && Sq <= SMALLQ_MAX_ROWS && smallq_smem_bytes(Sq, Sk, D) <= SMALLQ_MAX_SMEM) {
+    if (passes == PASSES_BOTH && smallq_fits(Sq, Sk, D)) {
         // reported as a call whose statistics and merge passes take no time
         PassTimers* tms = g_profiling ? timers_for_current_device() : nullptr;
         if (tms) {
@@ -1070,7 +1101,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
             for (int i = 0; i < 3; ++i) cudaEventRecord(tms->ev[i], stream);
         }
         rc = launch_small_q(q, k, out, out_ld, B, H, Sq, Sk, D, dtype, qsb, qsh, qss, ksb, ksh, kss, scale,
-                            causal, k_past, h_norm, clear_out, stream);
+                            causal, k_past, h_norm, clear_out, status, stream);
         if (rc == FCS_OK && tms) { cudaEventRecord(tms->ev[3], stream); tms->recorded = true; }
         return rc;
     }
@@ -1316,7 +1347,7 @@ int fcs_call_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_ca
     if (D != 64 && D != 128) return fcs::fail(FCS_ERR_UNSUPPORTED, "head dimension must be 64 or 128, got %d", D);
     const int causal = is_causal ? 1 : 0;
     // the same decisions, in the same order, as the call itself
-    if (sq_rows <= fcs::SMALLQ_MAX_ROWS && fcs::smallq_smem_bytes(sq_rows, Sk, D) <= fcs::SMALLQ_MAX_SMEM)
+    if (fcs::smallq_fits(sq_rows, Sk, D))
         return FCS_OK;   // few-row kernel: no scratch
     if (fcs::single_pass_applies(B, H, sq_rows, Sk, D, causal) &&
         fcs::single_pass_max_clusters(fcs::single_pass_cluster_size(Sk)) > 0)

@@ -101,6 +101,53 @@ def test_shapes_match_checker(fc, B, H, Sq, Sk, D, dtype, causal, cls):
     np.testing.assert_allclose(got.sum(axis=1), 1.0, atol=2e-3)
 
 
+FEW_ROWS = [
+    # B, H, R (cls_len, or query rows when causal), Sk, D, dtype, causal
+    (1, 32, 1, 32768, 128, "fp16", True),     # one decode query over 32 heads: eight key ranges per head
+    (1, 8, 4, 50000, 128, "bf16", True),      # ranges longer than the ring: stages are refilled
+    (1, 4, 1, 200000, 64, "fp16", True),      # the longest range whose scores still fit
+    (2, 3, 3, 1000, 64, "bf16", False),       # three rows (kernel built for four)
+    (32, 16, 1, 577, 64, "fp16", False),      # the CLIP-style CLS call
+    (1, 2, 2, 31, 128, "fp16", False),        # fewer keys than one range wants
+    (3, 2, 4, 64, 64, "fp16", True),          # R = 4 queries at the end of 64 keys
+    (1, 1, 4, 3, 64, "bf16", True),           # fewer keys than queries
+]
+
+
+@pytest.mark.parametrize("B,H,R,Sk,D,dtype,causal", FEW_ROWS)
+def test_few_query_rows_match_checker(fc, B, H, R, Sk, D, dtype, causal):
+    """At most four query rows: the clustered matrix-vector kernel (key ranges over the CTAs of a
+    cluster, rows staged by bulk copies, one exchange of (maximum, sum) per call)."""
+    Sq = R if causal else Sk
+    w = Workload("few", B, H, Sq, Sk, D, dtype, is_causal=causal, cls_len=None if causal else R, seed=R + Sk + D)
+    q, k = make_inputs(w)
+    got = run_gpu(fc, w, q, k)
+    want = c_oracle.colsum_c(q, k, is_causal=causal, cls_len=w.cls_len)
+    assert_parity(got, want, (B, H, R, Sk, D, dtype, causal))
+    np.testing.assert_allclose(got.sum(axis=1), 1.0, atol=2e-3)
+
+
+def test_few_query_rows_strided_keys_and_explicit_k_past(fc):
+    """Key rows that are not contiguous are copied row by row; an explicit K_past below the key
+    length leaves the trailing columns at zero without reading their keys."""
+    from oracle.naive_colsum import naive_colsum_f64
+    w = Workload("few_strided", 2, 3, 700, 700, 64, "fp16", cls_len=2, seed=77)
+    q, k = make_inputs(w)
+    kc = torch.empty(2, 3, 700, 80, dtype=torch.float16, device="cuda")[..., :64]   # row stride 80 elements
+    kc.copy_(k)
+    got = fc.flash_colsum(q.cuda(), kc, cls_len=2)
+    torch.cuda.synchronize()
+    assert_parity(got.cpu().numpy(), c_oracle.colsum_c(q, k, cls_len=2), "strided keys")
+    w = Workload("few_k_past", 1, 4, 3, 5000, 128, "bf16", is_causal=True, seed=78)
+    q, k = make_inputs(w)
+    for k_past in (0, 100, 4997, 9000):
+        got = fc.flash_colsum_causal(q.cuda(), k.cuda(), k_past=k_past).cpu().numpy()
+        assert fc.device_status() == 0
+        assert_parity(got, naive_colsum_f64(q, k, is_causal=True, k_past=k_past), f"few rows k_past {k_past}")
+        if k_past + 3 < 5000:
+            assert (got[:, k_past + 3:] == 0).all()
+
+
 def test_key_equal_to_query_and_outlier_keys(fc):
     w = Workload("kq", 2, 4, 512, 512, 64, "fp16", key_is_query=True, seed=21)
     q, k = make_inputs(w)
