@@ -2,24 +2,25 @@
 // decode queries): per (batch, head) the work is R dot products per key, i.e. a
 // matrix-vector product that reads every key once.  That is bound by HBM, not by
 // the tensor cores, so it is not reshaped into a GEMM; what matters is that every
-// SM keeps enough bytes in flight and that short calls have no dependent rounds.
+// SM streams keys without pause.
 //
-//   * The key axis of a (batch, head) is cut into up to eight ranges, one CTA each,
-//     the CTAs of a (batch, head) forming a thread-block cluster: a decode query over
-//     32 heads then fills the device instead of 32 SMs, and a CLS call runs as many
-//     small CTAs that the block scheduler balances.
-//   * A CTA's key rows arrive through a ring of 16 KiB shared-memory stages filled by
-//     bulk asynchronous copies (cp.async.bulk, completion counted on an mbarrier --
-//     no tensor map, no multicast): all stages are requested when the CTA starts, so
-//     a range of up to six stages is one round trip to memory.
-//   * Scores of the range stay in shared memory between the sweeps (scores and maximum
-//     while the rows arrive; exp2 and sum; weights and the add into the output).
-//   * Each CTA posts its (maximum, sum) per query row into the shared memory of every
-//     CTA of its cluster; after one cluster barrier each CTA has the row's global
-//     normaliser and adds its keys' share into the output.
+//   * Persistent CTAs, one per SM, grouped into thread-block clusters of 1..8.  A
+//     cluster walks a list of (batch, head) units; CTA r of the cluster owns the r-th
+//     range of every unit's key axis.  The cluster size is chosen so that the busiest
+//     SM has the least to read: a decode query over 32 heads is cut eight ways and
+//     fills the device, a CLS call over 512 units is cut in two for balance.
+//   * One warp issues bulk asynchronous copies (cp.async.bulk, completion counted on
+//     an mbarrier -- no tensor map, no multicast) of 16 KiB runs of key rows into a
+//     ring of up to ten shared-memory stages, and runs ahead of the consumers across
+//     unit boundaries: the epilogue of one unit overlaps the loads of the next.
+//   * Eight consumer warps compute the scores of a unit's range as the stages land
+//     (D/8 lanes share a key row), keep them in shared memory, take maximum, exp2 and
+//     sum, and post (maximum, sum) per query row into every CTA of the cluster with
+//     st.async, counted on the receiver's mbarrier -- no cluster-wide barrier per unit.
+//     With all ranges' values in, each CTA adds its keys' share into the output.
 //   * The output is cleared by a small kernel launched just before; this kernel is a
-//     programmatic dependent of it and waits for it only right before its adds, so
-//     the clear costs no time on the device.
+//     programmatic dependent of it and waits for it only before its first add, so the
+//     clear costs no time on the device.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -31,10 +32,12 @@
 namespace fcs {
 
 constexpr int SMALLQ_MAX_ROWS = 4;
-constexpr int SMALLQ_CONSUMER_WARPS = 8;
-constexpr int SMALLQ_THREADS = 32 * (SMALLQ_CONSUMER_WARPS + 1);   // + one warp that issues the copies
+constexpr int SMALLQ_CONSUMER_WARPS = 8;     // most consumer warps of a CTA (+ one warp that issues the copies)
+constexpr int SMALLQ_WIDE_WARPS = 4;         // consumer warps of a CTA when four CTAs share an SM
+constexpr int SMALLQ_WIDE_STAGES = 3;        // ... and their ring
 constexpr int SMALLQ_STAGE_BYTES = 16 * 1024;
-constexpr int SMALLQ_MAX_STAGES = 6;
+constexpr int SMALLQ_MAX_STAGES = 10;
+constexpr int SMALLQ_MIN_STAGES = 3;
 constexpr int SMALLQ_MAX_CLUSTER = 8;
 constexpr size_t SMALLQ_MAX_SMEM = 200 * 1024;
 
@@ -44,10 +47,14 @@ struct SmallQParams {
     float* out;
     long long out_ld;
     int H, R, Sk;
+    int units;        // (batch, head) pairs
     int keys;         // keys that some row sees (causal: min(Sk, k_past + R)); the rest stay zero
-    int CL;           // CTAs (key ranges) per (batch, head) = cluster size
+    int CL;           // CTAs (key ranges) per unit = cluster size
+    int clusters;     // clusters in the grid; cluster i takes units i, i + clusters, ...
     int range_rows;   // key rows per CTA (the last range may be shorter or empty)
     int stages;       // ring stages in use
+    int bufs;         // score buffers (2 when a cluster walks more than one unit)
+    int wide;         // 1: four CTAs of four consumer warps per SM (many short units), 0: one CTA of eight
     long long qsb, qsh, qss, ksb, ksh, kss;   // strides in elements
     float c;          // scale * log2(e), sign included
     int causal, k_past;
@@ -55,45 +62,80 @@ struct SmallQParams {
     int* status;
 };
 
-// Shared-memory layout: [ring: stages x 16 KiB][scores: R x range_rows fp32][fixed part]
-constexpr int SMALLQ_FIXED_BYTES = 2 * SMALLQ_MAX_STAGES * 8                       // full / empty barriers
+// Shared-memory layout: [ring: stages x 16 KiB][scores: bufs x R x range_rows fp32][fixed part]
+constexpr int SMALLQ_XCH_FLOATS = 2 * SMALLQ_MAX_CLUSTER * SMALLQ_MAX_ROWS * 2;    // two units in flight
+constexpr int SMALLQ_RED_FLOATS = 2 * SMALLQ_CONSUMER_WARPS * SMALLQ_MAX_ROWS * 2; // (max, sum) per warp, two units
+constexpr int SMALLQ_FIXED_BYTES = (2 * SMALLQ_MAX_STAGES + 2) * 8                 // full / empty / exchange barriers
                                    + 16                                            // abort flag
-                                   + (SMALLQ_THREADS / 32) * SMALLQ_MAX_ROWS * 4  // reduction staging
-                                   + SMALLQ_MAX_ROWS * 4                           // reduction result
-                                   + SMALLQ_MAX_CLUSTER * SMALLQ_MAX_ROWS * 8;     // (max, sum) of every CTA of the cluster
+                                   + SMALLQ_RED_FLOATS * 4
+                                   + SMALLQ_XCH_FLOATS * 4;                        // (max, sum) of every CTA of the cluster
 
-inline size_t smallq_smem_for(int R, int range_rows, int stages) {
-    return (size_t)stages * SMALLQ_STAGE_BYTES + (size_t)R * range_rows * 4 + SMALLQ_FIXED_BYTES + 128;
+// `bufs`: score buffers -- two when a cluster walks more than one unit (a unit is finished
+// while the next one's scores are computed), else one.
+inline size_t smallq_smem_for(int R, int range_rows, int stages, int bufs) {
+    return (size_t)stages * SMALLQ_STAGE_BYTES + (size_t)bufs * R * range_rows * 4 + SMALLQ_FIXED_BYTES + 128;
 }
 
-// Whether the few-row kernel takes a call with R rows and Sk keys at all: the scores of a key
-// range (an eighth of the keys at least) must fit next to a ring of two stages.
-inline bool smallq_fits(int R, int Sk, int D) {
-    (void)D;
-    if (R < 1 || R > SMALLQ_MAX_ROWS) return false;
-    const int range_rows = (Sk + SMALLQ_MAX_CLUSTER - 1) / SMALLQ_MAX_CLUSTER;
-    return smallq_smem_for(R, range_rows, 2) <= SMALLQ_MAX_SMEM;
+// Cluster size, grid and ring depth.
+// Many short units (at least two per SM, each at most 160 KiB of keys): four CTAs per SM, four
+// consumer warps and a ring of three stages each, no key split -- the units in flight on an SM
+// hide each other's latency chains.
+// Otherwise one persistent CTA per SM with eight consumer warps and a deep ring; a cluster size
+// cl gives sms / cl clusters, the busiest CTA reads ceil(units / clusters) ranges of
+// ceil(keys / cl) rows, and the size with the least such rows wins (ties: the smaller cluster).
+// Returns false when no cluster size holds the scores of a key range next to the shortest ring.
+inline bool smallq_plan(int units, int R, int keys, int D, int sms, int* CL, int* clusters, int* range_rows,
+                        int* stages, int* bufs, int* wide, size_t* smem) {
+    if (R < 1 || R > SMALLQ_MAX_ROWS || units < 1 || keys < 1) return false;
+    if (units >= 2 * sms && (long long)keys * 2 * D <= 160 * 1024) {
+        const int ncl = units < 4 * sms ? units : 4 * sms;
+        const int nb = units > ncl ? 2 : 1;
+        const size_t need = smallq_smem_for(R, keys, SMALLQ_WIDE_STAGES, nb);
+        if (need <= 55 * 1024) {   // four such CTAs (plus 1 KiB each that the system reserves) fit an SM
+            if (CL) *CL = 1;
+            if (clusters) *clusters = ncl;
+            if (range_rows) *range_rows = keys;
+            if (stages) *stages = SMALLQ_WIDE_STAGES;
+            if (bufs) *bufs = nb;
+            if (wide) *wide = 1;
+            if (smem) *smem = need;
+            return true;
+        }
+    }
+    int best_cl = 0;
+    long long best_rows = 0;
+    for (int cl = 1; cl <= SMALLQ_MAX_CLUSTER; ++cl) {
+        const int rr = (keys + cl - 1) / cl;
+        if (cl > 1 && rr < 32) break;     // ranges this short are all overhead
+        int ncl = sms / cl;
+        if (ncl < 1) ncl = 1;
+        if (ncl > units) ncl = units;
+        if (smallq_smem_for(R, rr, SMALLQ_MIN_STAGES, units > ncl ? 2 : 1) > SMALLQ_MAX_SMEM) continue;
+        const long long rows = (long long)((units + ncl - 1) / ncl) * rr;
+        if (best_cl == 0 || rows < best_rows) { best_cl = cl; best_rows = rows; }
+    }
+    if (best_cl == 0) return false;
+    const int cl = best_cl;
+    const int rr = (keys + cl - 1) / cl;
+    int ncl = sms / cl;
+    if (ncl < 1) ncl = 1;
+    if (ncl > units) ncl = units;
+    const int nb = units > ncl ? 2 : 1;
+    int st = SMALLQ_MAX_STAGES;
+    while (st > SMALLQ_MIN_STAGES && smallq_smem_for(R, rr, st, nb) > SMALLQ_MAX_SMEM) --st;
+    if (CL) *CL = cl;
+    if (clusters) *clusters = ncl;
+    if (range_rows) *range_rows = rr;
+    if (stages) *stages = st;
+    if (bufs) *bufs = nb;
+    if (wide) *wide = 0;
+    if (smem) *smem = smallq_smem_for(R, rr, st, nb);
+    return true;
 }
 
-// Cut of the key axis: as many ranges as give every CTA about 40 KiB of keys, more (down to
-// 32 rows each) while the grid is below two CTAs per SM, never more than eight.
-inline void smallq_plan(int units, int R, int keys, int D, int sms, int* CL, int* range_rows, int* stages,
-                        size_t* smem) {
-    const int row_bytes = 2 * D;
-    const long long unit_bytes = (long long)keys * row_bytes;
-    int cl = (int)((unit_bytes + 40 * 1024 - 1) / (40 * 1024));
-    if (cl < 1) cl = 1;
-    while (cl < SMALLQ_MAX_CLUSTER && (long long)units * cl < 2ll * sms && keys / (cl + 1) >= 32) ++cl;
-    if (cl > SMALLQ_MAX_CLUSTER) cl = SMALLQ_MAX_CLUSTER;
-    int rr = (keys + cl - 1) / cl;
-    while (cl < SMALLQ_MAX_CLUSTER && smallq_smem_for(R, rr, 2) > SMALLQ_MAX_SMEM) { ++cl; rr = (keys + cl - 1) / cl; }
-    const int rows_per_stage = SMALLQ_STAGE_BYTES / row_bytes;
-    int st = (rr + rows_per_stage - 1) / rows_per_stage;
-    if (st > SMALLQ_MAX_STAGES) st = SMALLQ_MAX_STAGES;
-    if (st < 1) st = 1;
-    while (st > 2 && smallq_smem_for(R, rr, st) > SMALLQ_MAX_SMEM) --st;
-    *CL = cl; *range_rows = rr; *stages = st;
-    *smem = smallq_smem_for(R, rr, st);
+// Whether the few-row kernel takes a call with R rows, Sk keys and `units` (batch, head) pairs.
+inline bool smallq_fits(int R, int Sk, int D, int units, int sms) {
+    return smallq_plan(units, R, Sk, D, sms, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
 }
 
 template <bool BF16>
@@ -107,52 +149,44 @@ __device__ __forceinline__ float2 unpack16x2(uint32_t v) {
 }
 
 // ---------------------------------------------------------------- cluster helpers
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
+__device__ __forceinline__ uint32_t smallq_cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ void cluster_arrive_relaxed() {
-    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+__device__ __forceinline__ uint32_t smallq_cluster_id() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
 }
-__device__ __forceinline__ void cluster_arrive_release() {
+__device__ __forceinline__ void smallq_cluster_arrive() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void cluster_wait_acquire() {
+__device__ __forceinline__ void smallq_cluster_wait() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Store one fp32 into the shared memory of CTA `rank` of this cluster, at the address that
-// `local_smem_addr` has in this CTA.
-__device__ __forceinline__ void st_cluster_f32(uint32_t local_smem_addr, uint32_t rank, float v) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+// Asynchronous store of (a, b) to the shared memory of CTA `rank` of this cluster, at the address
+// `local_addr` has in this CTA; its 8 bytes are counted on that CTA's barrier at `local_bar`.
+__device__ __forceinline__ void smallq_post(uint32_t local_addr, uint32_t local_bar, uint32_t rank, float a, float b) {
+    uint32_t addr, bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(local_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(local_bar), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];"
+                 ::"r"(addr), "f"(a), "f"(b), "r"(bar)
+                 : "memory");
+}
+// Barrier among the consumer warps only (the copy warp runs ahead on its own).
+template <int W>
+__device__ __forceinline__ void smallq_consumer_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * W) : "memory");
 }
 
-// max or sum over all warps of the CTA of R per-thread values; result in red_out[0..R)
-template <bool IS_MAX>
-__device__ __forceinline__ void smallq_reduce(float (&v)[SMALLQ_MAX_ROWS], float* red, float* red_out) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int r = 0; r < SMALLQ_MAX_ROWS; ++r) {
-        float x = v[r];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float y = __shfl_xor_sync(0xffffffffu, x, o);
-            x = IS_MAX ? fmaxf(x, y) : x + y;
-        }
-        if (lane == 0) red[warp * SMALLQ_MAX_ROWS + r] = x;
-    }
-    __syncthreads();
-    if (threadIdx.x < SMALLQ_MAX_ROWS) {
-        float x = IS_MAX ? -INFINITY : 0.f;
-        for (int w = 0; w < SMALLQ_THREADS / 32; ++w) {
-            const float y = red[w * SMALLQ_MAX_ROWS + threadIdx.x];
-            x = IS_MAX ? fmaxf(x, y) : x + y;
-        }
-        red_out[threadIdx.x] = x;
-    }
-    __syncthreads();
+// (maximum, sum of exp2 relative to it) of two sets of scores -> of their union
+__device__ __forceinline__ void smallq_merge(float& m, float& l, float mo, float lo) {
+    const float mn = fmaxf(m, mo);
+    const float ms = (mn == -INFINITY) ? 0.f : mn;
+    l = l * ex2_approx(m - ms) + lo * ex2_approx(mo - ms);
+    m = mn;
 }
 
 // Zero the B x S valid entries of `out`; lets the kernel behind it in the stream start at once.
@@ -166,181 +200,243 @@ __global__ void clear_rows_kernel(float* out, long long out_ld, int B, int S) {
     }
 }
 
-// RMAX: compile-time bound on the query rows (1, 2 or 4).
-template <int D, bool BF16, int RMAX>
-__global__ void __launch_bounds__(SMALLQ_THREADS, RMAX == 4 ? 2 : 4)
+// RMAX: compile-time bound on the query rows (1, 2 or 4); W: consumer warps (8, or 4 with four CTAs per SM).
+template <int D, bool BF16, int RMAX, int W>
+__global__ void __launch_bounds__(32 * (W + 1), W == SMALLQ_WIDE_WARPS ? 4 : 1)
 colsum_small_q_kernel(const SmallQParams p) {
+    constexpr int SMALLQ_CONSUMER_THREADS = 32 * W;
     extern __shared__ __align__(128) uint8_t smallq_smem[];
     uint8_t* ring = smallq_smem;
-    float* sc = reinterpret_cast<float*>(ring + (size_t)p.stages * SMALLQ_STAGE_BYTES);   // [R][range_rows]
-    uint8_t* fixed = reinterpret_cast<uint8_t*>(sc + (size_t)p.R * p.range_rows);
+    float* sc_base = reinterpret_cast<float*>(ring + (size_t)p.stages * SMALLQ_STAGE_BYTES);   // [bufs][R][range_rows]
+    const size_t sc_buf = (size_t)p.R * p.range_rows;
+    uint8_t* fixed = reinterpret_cast<uint8_t*>(sc_base + (size_t)p.bufs * sc_buf);
     fixed = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fixed) + 15) & ~static_cast<uintptr_t>(15));
-    const uint32_t bars = smem_u32(fixed);                                   // full[stages], empty[stages]
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(fixed + 2 * SMALLQ_MAX_STAGES * 8);
-    float* red = reinterpret_cast<float*>(fixed + 2 * SMALLQ_MAX_STAGES * 8 + 16);
-    float* red_out = red + (SMALLQ_THREADS / 32) * SMALLQ_MAX_ROWS;
-    float* xch = red_out + SMALLQ_MAX_ROWS;                                  // [CL][MAX_ROWS][2]
+    const uint32_t bars = smem_u32(fixed);                    // full[MAX_STAGES], empty[MAX_STAGES], exchange[2]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(fixed + (2 * SMALLQ_MAX_STAGES + 2) * 8);
+    float* red = reinterpret_cast<float*>(fixed + (2 * SMALLQ_MAX_STAGES + 2) * 8 + 16);   // [2][warps][MAX_ROWS][2]
+    float* xch = red + SMALLQ_RED_FLOATS;                                                  // [2][MAX_CLUSTER][MAX_ROWS][2]
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (SMALLQ_MAX_STAGES + s); };
+    auto xch_bar = [&](int i) { return bars + 8u * (2 * SMALLQ_MAX_STAGES + i); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t cr = cluster_cta_rank();
-    const int unit = blockIdx.x / p.CL;
-    const int b = unit / p.H, h = unit % p.H;
-    const uint16_t* qb = reinterpret_cast<const uint16_t*>(p.q) + b * p.qsb + h * p.qsh;
-    const uint16_t* kb = reinterpret_cast<const uint16_t*>(p.k) + b * p.ksb + h * p.ksh;
+    const uint32_t cr = smallq_cluster_rank();
+    const int cluster = (int)smallq_cluster_id();
     int k0 = (int)cr * p.range_rows, k1 = k0 + p.range_rows;
     if (k0 > p.keys) k0 = p.keys;
     if (k1 > p.keys) k1 = p.keys;
     const int rows = k1 - k0;
     constexpr int ROW_BYTES = 2 * D;
     constexpr int STAGE_ROWS = SMALLQ_STAGE_BYTES / ROW_BYTES;
-    const int chunks = (rows + STAGE_ROWS - 1) / STAGE_ROWS;
+    const int chunks = (rows + STAGE_ROWS - 1) / STAGE_ROWS;     // per unit
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), SMALLQ_CONSUMER_WARPS); }
+        for (int s = 0; s < p.stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), W); }
+        mbar_init(xch_bar(0), 1);
+        mbar_init(xch_bar(1), 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
     __syncthreads();
-    // every CTA of the cluster is running once this barrier completes; it is waited for only
+    // every CTA of the cluster has set up its barriers once this completes; it is waited for
     // before the first store into another CTA's shared memory
-    cluster_arrive_relaxed();
+    smallq_cluster_arrive();
 
-    float vmax[SMALLQ_MAX_ROWS];
-#pragma unroll
-    for (int r = 0; r < SMALLQ_MAX_ROWS; ++r) vmax[r] = -INFINITY;
-
-    if (warp == SMALLQ_CONSUMER_WARPS) {
-        // ------------------------------------------------ copy issuer
+    if (warp == W) {
+        // ------------------------------------------------ copy issuer: runs ahead across units
         // contiguous key rows: one copy per stage; strided rows: one copy per row, dealt over the lanes
         const bool dense = p.kss == D;
         bool ok = true;
-        for (int ch = 0; ch < chunks && ok; ++ch) {
-            const int s = ch % p.stages;
-            if (ch >= p.stages) {
-                ok = mbar_wait(empty_bar(s), ((ch / p.stages) & 1) ^ 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-            }
-            const int r0 = k0 + ch * STAGE_ROWS;
-            const int n = min(STAGE_ROWS, k1 - r0);
-            const uint32_t dst = smem_u32(ring + (size_t)s * SMALLQ_STAGE_BYTES);
-            if (lane == 0) mbar_arrive_expect_tx(full_bar(s), (uint32_t)n * ROW_BYTES);
-            __syncwarp();
-            if (dense) {
-                if (lane == 0) bulk_load(dst, kb + (long long)r0 * p.kss, (uint32_t)n * ROW_BYTES, full_bar(s));
-            } else {
-                for (int i = lane; i < n; i += 32)
-                    bulk_load(dst + i * ROW_BYTES, kb + (long long)(r0 + i) * p.kss, ROW_BYTES, full_bar(s));
+        int n = 0;      // stages filled so far
+        for (int unit = cluster; unit < p.units && ok; unit += p.clusters) {
+            const int b = unit / p.H, h = unit % p.H;
+            const uint16_t* kb = reinterpret_cast<const uint16_t*>(p.k) + b * p.ksb + h * p.ksh;
+            for (int ch = 0; ch < chunks; ++ch, ++n) {
+                const int s = n % p.stages;
+                if (n >= p.stages) {
+                    ok = mbar_wait(empty_bar(s), ((n / p.stages) & 1) ^ 1, abort_flag, p.status, FCS_STATUS_WAIT_PRODUCER);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                }
+                const int r0 = k0 + ch * STAGE_ROWS;
+                const int cnt = min(STAGE_ROWS, k1 - r0);
+                const uint32_t dst = smem_u32(ring + (size_t)s * SMALLQ_STAGE_BYTES);
+                if (lane == 0) mbar_arrive_expect_tx(full_bar(s), (uint32_t)cnt * ROW_BYTES);
+                __syncwarp();
+                if (dense) {
+                    if (lane == 0) bulk_load(dst, kb + (long long)r0 * p.kss, (uint32_t)cnt * ROW_BYTES, full_bar(s));
+                } else {
+                    for (int i = lane; i < cnt; i += 32)
+                        bulk_load(dst + i * ROW_BYTES, kb + (long long)(r0 + i) * p.kss, ROW_BYTES, full_bar(s));
+                }
             }
         }
+        smallq_cluster_wait();
     } else {
-        // ------------------------------------------------ sweep 1: scores (log2 domain) and their maximum
-        // D/8 adjacent lanes share a key row, 16 bytes each; partial dot products meet by shuffles
-        constexpr int LPR = D / 8;            // lanes per key row
-        constexpr int RPW = 32 / LPR;         // key rows per warp and step
+        // ------------------------------------------------ consumers
+        // A warp takes 32 key rows at a time.  D/8 adjacent lanes share a row, 16 bytes each, over
+        // D/8 passes; the partial dot products are then transposed and summed with D/8 - 1
+        // shuffles, after which every lane holds the score of one row.
+        constexpr int LPR = D / 8;            // lanes per key row = passes per 32 rows
+        constexpr int RPW = 32 / LPR;         // key rows per pass
+        constexpr int GROUPS = STAGE_ROWS / 32;
         const int piece = lane % LPR, sub = lane / LPR;
-        float qreg[RMAX][8];
+        auto load_q = [&](int unit, uint4 (&raw)[RMAX]) {
+            const int b = unit / p.H, h = unit % p.H;
+            const uint16_t* qb = reinterpret_cast<const uint16_t*>(p.q) + b * p.qsb + h * p.qsh;
 #pragma unroll
-        for (int r = 0; r < RMAX; ++r) {
-            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-            if (r < p.R) raw = __ldg(reinterpret_cast<const uint4*>(qb + r * p.qss) + piece);
-            const float2 f0 = unpack16x2<BF16>(raw.x), f1 = unpack16x2<BF16>(raw.y);
-            const float2 f2 = unpack16x2<BF16>(raw.z), f3 = unpack16x2<BF16>(raw.w);
-            qreg[r][0] = f0.x * p.c; qreg[r][1] = f0.y * p.c; qreg[r][2] = f1.x * p.c; qreg[r][3] = f1.y * p.c;
-            qreg[r][4] = f2.x * p.c; qreg[r][5] = f2.y * p.c; qreg[r][6] = f3.x * p.c; qreg[r][7] = f3.y * p.c;
-        }
-        bool ok = true;
-        for (int ch = 0; ch < chunks && ok; ++ch) {
-            const int s = ch % p.stages;
-            ok = mbar_wait(full_bar(s), (ch / p.stages) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+            for (int r = 0; r < RMAX; ++r)
+                raw[r] = (r < p.R) ? __ldg(reinterpret_cast<const uint4*>(qb + r * p.qss) + piece)
+                                   : make_uint4(0u, 0u, 0u, 0u);
+        };
+        // A wait that runs out raises the abort flag (later waits then give up at once) but does not
+        // end the loops: all eight warps keep meeting at the named barrier, the results are void and
+        // the status word says so.
+        bool ok = true, peers_up = false, out_clear = false;
+
+        // unit `u` (the uc-th of this cluster) is finished one unit late, behind the scores of the
+        // next one: by then every range's (maximum, sum) has long arrived
+        auto finish = [&](int unit, int uc) {
+            const int xb = uc & 1;
+            ok = ok && mbar_wait(xch_bar(xb), (uc >> 1) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            const uint4* st = reinterpret_cast<const uint4*>(ring + (size_t)s * SMALLQ_STAGE_BYTES);
-            const int n = min(STAGE_ROWS, rows - ch * STAGE_ROWS);
-#pragma unroll 2
-            for (int i0 = 0; i0 < n; i0 += SMALLQ_CONSUMER_WARPS * RPW) {
-                const int i = i0 + warp * RPW + sub;
-                uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-                if (i < n) raw = st[i * LPR + piece];
-                const float2 f0 = unpack16x2<BF16>(raw.x), f1 = unpack16x2<BF16>(raw.y);
-                const float2 f2 = unpack16x2<BF16>(raw.z), f3 = unpack16x2<BF16>(raw.w);
-                const int kl = ch * STAGE_ROWS + i;       // row within the range
+            const float* xv = xch + (size_t)xb * SMALLQ_MAX_CLUSTER * SMALLQ_MAX_ROWS * 2;
+            float M[SMALLQ_MAX_ROWS], w[SMALLQ_MAX_ROWS];
 #pragma unroll
-                for (int r = 0; r < RMAX; ++r) {
-                    if (r < p.R) {      // uniform across the CTA
-                        float d = f0.x * qreg[r][0] + f0.y * qreg[r][1] + f1.x * qreg[r][2] + f1.y * qreg[r][3] +
-                                  f2.x * qreg[r][4] + f2.y * qreg[r][5] + f3.x * qreg[r][6] + f3.y * qreg[r][7];
+            for (int r = 0; r < SMALLQ_MAX_ROWS; ++r) {
+                M[r] = 0.f; w[r] = 0.f;
+                if (r < p.R) {
+                    float mm = -INFINITY, ll = 0.f;
+                    for (int i = 0; i < p.CL; ++i)
+                        smallq_merge(mm, ll, xv[(i * SMALLQ_MAX_ROWS + r) * 2], xv[(i * SMALLQ_MAX_ROWS + r) * 2 + 1]);
+                    M[r] = mm;
+                    w[r] = ok ? p.inv_norm / ll : 0.f;
+                }
+            }
+            if (!out_clear) { grid_dependency_wait(); out_clear = true; }   // the output has been cleared
+            const float* sc = sc_base + (size_t)(p.bufs == 2 ? xb : 0) * sc_buf;
+            float* ob = p.out + (long long)(unit / p.H) * p.out_ld + k0;
+            for (int kl = threadIdx.x; kl < rows; kl += SMALLQ_CONSUMER_THREADS) {
+                float v = 0.f;
 #pragma unroll
-                        for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                        if (piece == 0 && i < n) {
-                            const bool visible = !p.causal || (k0 + kl <= p.k_past + r);
-                            const float sv = visible ? d : -INFINITY;
-                            sc[(size_t)r * p.range_rows + kl] = sv;
-                            vmax[r] = fmaxf(vmax[r], sv);
+                for (int r = 0; r < SMALLQ_MAX_ROWS; ++r)
+                    if (r < p.R) v += ex2_approx(sc[(size_t)r * p.range_rows + kl] - M[r]) * w[r];
+                atomicAdd_system(ob + kl, v);   // `out` may live on another GPU
+            }
+        };
+
+        uint4 qnext[RMAX];
+        if (cluster < p.units) load_q(cluster, qnext);
+        int n = 0, ucount = 0, prev_unit = -1;
+        for (int unit = cluster; unit < p.units; unit += p.clusters, ++ucount) {
+            float qreg[RMAX][8];
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) {
+                const float2 f0 = unpack16x2<BF16>(qnext[r].x), f1 = unpack16x2<BF16>(qnext[r].y);
+                const float2 f2 = unpack16x2<BF16>(qnext[r].z), f3 = unpack16x2<BF16>(qnext[r].w);
+                qreg[r][0] = f0.x * p.c; qreg[r][1] = f0.y * p.c; qreg[r][2] = f1.x * p.c; qreg[r][3] = f1.y * p.c;
+                qreg[r][4] = f2.x * p.c; qreg[r][5] = f2.y * p.c; qreg[r][6] = f3.x * p.c; qreg[r][7] = f3.y * p.c;
+            }
+            if (unit + p.clusters < p.units) load_q(unit + p.clusters, qnext);   // lands during this unit
+            const int xb = ucount & 1;
+            if (threadIdx.x == 0) mbar_arrive_expect_tx(xch_bar(xb), (uint32_t)p.CL * SMALLQ_MAX_ROWS * 8);
+            float* sc = sc_base + (size_t)(p.bufs == 2 ? xb : 0) * sc_buf;
+
+            // scores (log2 domain) of this range, with a running (maximum, sum) per thread
+            float tm[RMAX], tl[RMAX];
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) { tm[r] = -INFINITY; tl[r] = 0.f; }
+            for (int ch = 0; ch < chunks; ++ch, ++n) {
+                const int s = n % p.stages;
+                ok = ok && mbar_wait(full_bar(s), (n / p.stages) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
+                ok = __all_sync(0xffffffffu, ok);
+                const uint4* st = reinterpret_cast<const uint4*>(ring + (size_t)s * SMALLQ_STAGE_BYTES);
+                const int cnt = min(STAGE_ROWS, rows - ch * STAGE_ROWS);
+                // the 32-row groups of the stages go round the warps
+                for (int g = (warp - n * GROUPS) & (W - 1); g < GROUPS; g += W) {
+                    if (g * 32 >= cnt) break;
+                    float part[RMAX][LPR];
+#pragma unroll
+                    for (int j = 0; j < LPR; ++j) {
+                        const int row = g * 32 + j * RPW + sub;
+                        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+                        if (row < cnt) raw = st[row * LPR + piece];
+                        const float2 f0 = unpack16x2<BF16>(raw.x), f1 = unpack16x2<BF16>(raw.y);
+                        const float2 f2 = unpack16x2<BF16>(raw.z), f3 = unpack16x2<BF16>(raw.w);
+#pragma unroll
+                        for (int r = 0; r < RMAX; ++r)
+                            part[r][j] = ((f0.x * qreg[r][0] + f0.y * qreg[r][1]) + (f1.x * qreg[r][2] + f1.y * qreg[r][3])) +
+                                         ((f2.x * qreg[r][4] + f2.y * qreg[r][5]) + (f3.x * qreg[r][6] + f3.y * qreg[r][7]));
+                    }
+                    // transpose and sum over the lanes of a row: afterwards part[r][0] is the score of
+                    // the row of pass j = piece
+#pragma unroll
+                    for (int half = LPR / 2; half >= 1; half >>= 1) {
+                        const bool up = (piece & half) != 0;
+#pragma unroll
+                        for (int r = 0; r < RMAX; ++r) {
+#pragma unroll
+                            for (int t = 0; t < half; ++t) {
+                                const float send = up ? part[r][t] : part[r][t + half];
+                                const float keep = up ? part[r][t + half] : part[r][t];
+                                part[r][t] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+                            }
+                        }
+                    }
+                    const int row = g * 32 + piece * RPW + sub;
+                    if (row < cnt) {
+                        const int kl = ch * STAGE_ROWS + row;       // row within the range
+#pragma unroll
+                        for (int r = 0; r < RMAX; ++r) {
+                            if (r < p.R) {
+                                const bool visible = !p.causal || (k0 + kl <= p.k_past + r);
+                                const float sv = visible ? part[r][0] : -INFINITY;
+                                sc[(size_t)r * p.range_rows + kl] = sv;
+                                if (sv > tm[r]) { tl[r] = tl[r] * ex2_approx(tm[r] - sv) + 1.f; tm[r] = sv; }
+                                else if (sv != -INFINITY) tl[r] += ex2_approx(sv - tm[r]);
+                            }
                         }
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar(s));    // the stage may be refilled
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty_bar(s));
-        }
-    }
-    smallq_reduce<true>(vmax, red, red_out);
-    float m[SMALLQ_MAX_ROWS];
-#pragma unroll
-    for (int r = 0; r < SMALLQ_MAX_ROWS; ++r) m[r] = red_out[r];
-    __syncthreads();
 
-    // sweep 2: exp2 relative to this range's maximum, and their sum
-    float vsum[SMALLQ_MAX_ROWS] = {0.f, 0.f, 0.f, 0.f};
-    for (int kl = threadIdx.x; kl < rows; kl += SMALLQ_THREADS) {
+            // the unit before this one: its exchange has completed while the scores above were computed
+            if (prev_unit >= 0) finish(prev_unit, ucount - 1);
+
+            // (maximum, sum) of the range: over the warp by shuffles, over the warps through shared
+            // memory (one barrier; the staging buffer alternates between units)
+            float* rb = red + (size_t)xb * SMALLQ_CONSUMER_WARPS * SMALLQ_MAX_ROWS * 2;
 #pragma unroll
-        for (int r = 0; r < SMALLQ_MAX_ROWS; ++r) {
-            if (r < p.R) {
-                const float ms = (m[r] == -INFINITY) ? 0.f : m[r];
-                const float e = ex2_approx(sc[(size_t)r * p.range_rows + kl] - ms);
-                sc[(size_t)r * p.range_rows + kl] = e;
-                vsum[r] += e;
+            for (int r = 0; r < RMAX; ++r) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float mo = __shfl_xor_sync(0xffffffffu, tm[r], o);
+                    const float lo = __shfl_xor_sync(0xffffffffu, tl[r], o);
+                    smallq_merge(tm[r], tl[r], mo, lo);
+                }
+                if (lane == 0) { rb[(warp * SMALLQ_MAX_ROWS + r) * 2] = tm[r]; rb[(warp * SMALLQ_MAX_ROWS + r) * 2 + 1] = tl[r]; }
             }
+            smallq_consumer_sync<W>();   // also orders this unit's score stores, and the finish above before the next unit's
+            if (!peers_up) { smallq_cluster_wait(); peers_up = true; }
+            if (threadIdx.x < p.CL * SMALLQ_MAX_ROWS) {
+                const int dst = threadIdx.x / SMALLQ_MAX_ROWS, r = threadIdx.x % SMALLQ_MAX_ROWS;
+                float mm = -INFINITY, ll = 0.f;
+                if (r < RMAX && r < p.R)
+                    for (int w = 0; w < W; ++w)
+                        smallq_merge(mm, ll, rb[(w * SMALLQ_MAX_ROWS + r) * 2], rb[(w * SMALLQ_MAX_ROWS + r) * 2 + 1]);
+                const uint32_t slot = smem_u32(xch + ((size_t)(xb * SMALLQ_MAX_CLUSTER + cr) * SMALLQ_MAX_ROWS + r) * 2);
+                smallq_post(slot, xch_bar(xb), (uint32_t)dst, mm, ll);
+            }
+            prev_unit = unit;
         }
+        if (prev_unit >= 0) finish(prev_unit, ucount - 1);
+        if (!peers_up) smallq_cluster_wait();
     }
-    smallq_reduce<false>(vsum, red, red_out);
-
-    // every CTA of the cluster gets every range's (maximum, sum)
-    cluster_wait_acquire();   // (the barrier entered at the start: all CTAs are up)
-    if (threadIdx.x < p.CL * SMALLQ_MAX_ROWS) {
-        const int dst = threadIdx.x / SMALLQ_MAX_ROWS, r = threadIdx.x % SMALLQ_MAX_ROWS;
-        const uint32_t slot = smem_u32(xch + ((size_t)cr * SMALLQ_MAX_ROWS + r) * 2);
-        st_cluster_f32(slot, (uint32_t)dst, m[r]);
-        st_cluster_f32(slot + 4, (uint32_t)dst, red_out[r]);
-    }
-    cluster_arrive_release();
-    cluster_wait_acquire();
-    float w[SMALLQ_MAX_ROWS];
-#pragma unroll
-    for (int r = 0; r < SMALLQ_MAX_ROWS; ++r) {
-        float M = -INFINITY;
-        for (int i = 0; i < p.CL; ++i) M = fmaxf(M, xch[(i * SMALLQ_MAX_ROWS + r) * 2]);
-        float L = 0.f;
-        for (int i = 0; i < p.CL; ++i) {
-            const float mi = xch[(i * SMALLQ_MAX_ROWS + r) * 2];
-            if (mi != -INFINITY) L += xch[(i * SMALLQ_MAX_ROWS + r) * 2 + 1] * ex2_approx(mi - M);
-        }
-        w[r] = (r < p.R && m[r] != -INFINITY) ? p.inv_norm * ex2_approx(m[r] - M) / L : 0.f;
-    }
-
-    // sweep 3: this range's share of the column means, once the output has been cleared
-    grid_dependency_wait();
-    float* ob = p.out + (long long)b * p.out_ld + k0;
-    for (int kl = threadIdx.x; kl < rows; kl += SMALLQ_THREADS) {
-        float v = 0.f;
-#pragma unroll
-        for (int r = 0; r < SMALLQ_MAX_ROWS; ++r)
-            if (r < p.R) v += sc[(size_t)r * p.range_rows + kl] * w[r];
-        atomicAdd_system(ob + kl, v);   // `out` may live on another GPU
-    }
+    // nobody leaves while a peer may still store into its shared memory
+    smallq_cluster_arrive();
+    smallq_cluster_wait();
 }
 
 }  // namespace fcs

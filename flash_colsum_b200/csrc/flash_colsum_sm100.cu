@@ -857,13 +857,13 @@ static int check_operand(const char* name, const void* ptr, int64_t sb, int64_t 
 
 // Few query rows: the matrix-vector kernel (a kernel that clears the output, then the
 // clustered kernel as its programmatic dependent).
-template <int D, bool BF16, int RMAX>
-static cudaError_t launch_small_q_r(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream,
+template <int D, bool BF16, int RMAX, int W>
+static cudaError_t launch_small_q_w(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream,
                                     bool after_clear) {
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kern = colsum_small_q_kernel<D, BF16, RMAX>;
+    auto kern = colsum_small_q_kernel<D, BF16, RMAX, W>;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMALLQ_MAX_SMEM);
         if (e != cudaSuccess) return e;
@@ -872,7 +872,7 @@ static cudaError_t launch_small_q_r(const SmallQParams& sp, int grid, size_t sme
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(SMALLQ_THREADS);
+    cfg.blockDim = dim3(32 * (W + 1));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
@@ -886,6 +886,13 @@ static cudaError_t launch_small_q_r(const SmallQParams& sp, int grid, size_t sme
     cfg.attrs = attrs;
     cfg.numAttrs = after_clear ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kern, sp);
+}
+
+template <int D, bool BF16, int RMAX>
+static cudaError_t launch_small_q_r(const SmallQParams& sp, int grid, size_t smem, cudaStream_t stream,
+                                    bool after_clear) {
+    if (sp.wide) return launch_small_q_w<D, BF16, RMAX, SMALLQ_WIDE_WARPS>(sp, grid, smem, stream, after_clear);
+    return launch_small_q_w<D, BF16, RMAX, SMALLQ_CONSUMER_WARPS>(sp, grid, smem, stream, after_clear);
 }
 
 template <int D, bool BF16>
@@ -922,9 +929,10 @@ static int launch_small_q(const void* q, const void* k, float* out, int64_t out_
     if (causal && (long long)k_past + R < keys) keys = (long long)k_past + R;
     sp.keys = (int)keys;
     size_t smem = 0;
-    smallq_plan(B * H, R, sp.keys, D, sms, &sp.CL, &sp.range_rows, &sp.stages, &smem);
-    if (smem > SMALLQ_MAX_SMEM) return fail(FCS_ERR_UNSUPPORTED, "few-row kernel: %d keys do not fit", Sk);
-    const int grid = B * H * sp.CL;
+    sp.units = B * H;
+    if (!smallq_plan(sp.units, R, sp.keys, D, sms, &sp.CL, &sp.clusters, &sp.range_rows, &sp.stages, &sp.bufs, &sp.wide, &smem))
+        return fail(FCS_ERR_UNSUPPORTED, "few-row kernel: %d keys do not fit", Sk);
+    const int grid = sp.clusters * sp.CL;
     const bool bf16 = dtype == FCS_DTYPE_BF16;
     const cudaError_t e =
         (D == 64) ? (bf16 ? launch_small_q_t<64, true>(sp, grid, smem, stream, clear_out)
@@ -1093,7 +1101,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
-    if (passes == PASSES_BOTH && smallq_fits(Sq, Sk, D)) {
+    if (passes == PASSES_BOTH && smallq_fits(Sq, Sk, D, B * H, num_sms())) {
         // reported as a call whose statistics and merge passes take no time
         PassTimers* tms = g_profiling ? timers_for_current_device() : nullptr;
         if (tms) {
@@ -1347,7 +1355,7 @@ int fcs_call_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_ca
     if (D != 64 && D != 128) return fcs::fail(FCS_ERR_UNSUPPORTED, "head dimension must be 64 or 128, got %d", D);
     const int causal = is_causal ? 1 : 0;
     // the same decisions, in the same order, as the call itself
-    if (fcs::smallq_fits(sq_rows, Sk, D))
+    if (fcs::smallq_fits(sq_rows, Sk, D, B * H, fcs::num_sms()))
         return FCS_OK;   // few-row kernel: no scratch
     if (fcs::single_pass_applies(B, H, sq_rows, Sk, D, causal) &&
         fcs::single_pass_max_clusters(fcs::single_pass_cluster_size(Sk)) > 0)
