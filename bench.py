@@ -255,9 +255,9 @@ def run_reference_arm(args):
 def kernel_only(args, fc, _cabi, dev, flush_buf, peaks):
     """Device passes of one workload, per-pass durations; one JSON line."""
     w = WORKLOADS[args.workload]
-    if args.batch > 0 or args.keys > 0 or args.queries > 0:
+    if args.batch > 0 or args.keys > 0 or args.queries > 0 or args.heads > 0:
         sq = args.queries or (w.Sq if w.is_causal or not args.keys else args.keys)
-        w = Workload(w.name, args.batch or w.B, w.H, sq,
+        w = Workload(w.name, args.batch or w.B, args.heads or w.H, sq,
                      args.keys or w.Sk, w.D, w.dtype, w.is_causal, w.cls_len,
                      w.key_outliers, w.key_is_query, w.seed)
     g = torch.Generator(device=dev).manual_seed(w.seed)
@@ -376,6 +376,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (kernel-only mode)")
     ap.add_argument("--keys", type=int, default=0, help="override the key length (kernel-only mode)")
+    ap.add_argument("--heads", type=int, default=0, help="override the head count (kernel-only mode)")
     ap.add_argument("--queries", type=int, default=0, help="override the query length (kernel-only mode, causal workloads)")
     ap.add_argument("--no-l2-flush", action="store_true",
                     help="kernel-only mode: do not write the 256 MiB buffer between calls (inputs stay in L2)")

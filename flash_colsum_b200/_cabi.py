@@ -14,7 +14,7 @@ EXPORTED_SYMBOLS = (
     "fcs_version", "fcs_last_error", "fcs_workspace_bytes", "fcs_call_workspace_bytes",
     "fcs_colsum_batched", "fcs_colsum_non_batched", "fcs_colsum_causal",
     "fcs_set_profiling", "fcs_last_pass_ms", "fcs_plan_info",
-    "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate",
+    "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate", "fcs_colsum_causal_accumulate_and_clear",
     "fcs_set_single_pass", "fcs_single_pass_info", "fcs_single_pass_applies",
     "fcs_colsum_causal_batched", "fcs_select_topk",
     "fcs_statistics_rows", "fcs_colsum_statistics", "fcs_colsum_columns",
@@ -95,6 +95,9 @@ def load() -> ctypes.CDLL:
     lib.fcs_select_topk.argtypes = [_p, _i64, _i, _i, _i, _p, _p, _p]
     lib.fcs_colsum_causal_accumulate.restype = _i
     lib.fcs_colsum_causal_accumulate.argtypes = lib.fcs_colsum_causal.argtypes
+    lib.fcs_colsum_causal_accumulate_and_clear.restype = _i
+    lib.fcs_colsum_causal_accumulate_and_clear.argtypes = [_p, _p, _p, _p, _i, _i, _i, _i, _i] + [_i64] * 4 + \
+        [_f, _i, _i, _p, _sz, _p, _p]
     lib.fcs_colsum_batched_static_scratch.restype = _i
     lib.fcs_colsum_batched_static_scratch.argtypes = [_p, _p, _p, _i64, _i, _i, _i, _i, _i] + [_i64] * 6 + \
         [_f, _i, _i, _p, _p]

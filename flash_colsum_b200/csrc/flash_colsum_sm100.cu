@@ -51,14 +51,16 @@ constexpr int TMEM_COLS = 512;
 constexpr int NUM_LSE = 4;         // per-query-block log-sum-exp vectors in flight (column pass)
 // Consumer warps come in groups of four (a group covers the 128 tensor-memory
 // lanes); every group takes an equal run of the columns of each accumulator.
-constexpr int CONSUMER_GROUPS = 4;
+#ifndef FCS_GROUPS
+#define FCS_GROUPS 4
+#endif
+constexpr int CONSUMER_GROUPS = FCS_GROUPS;
 constexpr int GROUP_COLS = BLOCK / CONSUMER_GROUPS;
 constexpr int CONSUMER_WARPS = 4 * CONSUMER_GROUPS;
 constexpr int CONSUMER_THREADS = 32 * CONSUMER_WARPS;
 constexpr int PRODUCER_WARP = CONSUMER_WARPS;
 constexpr int MMA_WARP = CONSUMER_WARPS + 1;
 constexpr int THREADS = 32 * (CONSUMER_WARPS + 2);
-static_assert(GROUP_COLS == 64, "a group consumes one 64-column block per step");
 
 // Item-end partials of the statistics pass wait in one of these slots until a group
 // combines them; consumer groups are never more than two steps apart, so four
@@ -105,6 +107,9 @@ struct Layout {
 
 // A group's 64 columns of one accumulator.  `taddr`, `lim`, `thr`, `end` and
 // `nl` are relative to the group's first column.
+// One chunk of 32 columns is in flight from tensor memory while the chunk before it is in the
+// exp pipes.
+#if FCS_GROUPS == 4 && !defined(FCS_PREFETCH)
 template <bool MASKED>
 __device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, float& m, float& l) {
     uint32_t r[32];
@@ -116,18 +121,6 @@ __device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, flo
     stats_block32<MASKED>(r, lim - 32, c, m, l);
 }
 template <bool MASKED>
-__device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, int thr, int end, float c,
-                                            float (&acc)[4]) {
-    uint32_t r[32];
-    tmem_ld_x32(taddr, r);
-    tmem_ld_wait(r);
-    colsum_chunk<MASKED>(r, nl, thr, end, c, acc);
-    tmem_ld_x32(taddr + 32, r);
-    tmem_ld_wait(r);
-    colsum_chunk<MASKED>(r, nl + 8, thr - 32, end - 32, c, acc);
-}
-
-template <bool MASKED>
 __device__ __forceinline__ void colsum_tile_ext(uint32_t taddr, int thr, int end, float c, float (&acc)[4]) {
     uint32_t r[32];
     tmem_ld_x32(taddr, r);
@@ -136,6 +129,47 @@ __device__ __forceinline__ void colsum_tile_ext(uint32_t taddr, int thr, int end
     tmem_ld_x32(taddr + 32, r);
     tmem_ld_wait(r);
     colsum_chunk_ext<MASKED>(r, thr - 32, end - 32, c, acc);
+}
+#else
+template <bool MASKED>
+__device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, float& m, float& l) {
+    uint32_t ra[32], rb[32];
+    tmem_ld_x32(taddr, ra);
+#pragma unroll
+    for (int ch = 0; ch < GROUP_COLS / 32; ch += 2) {
+        tmem_ld_wait(ra);
+        tmem_ld_x32(taddr + 32 * (ch + 1), rb);
+        stats_block32<MASKED>(ra, lim - 32 * ch, c, m, l);
+        tmem_ld_wait(rb);
+        if (ch + 2 < GROUP_COLS / 32) tmem_ld_x32(taddr + 32 * (ch + 2), ra);
+        stats_block32<MASKED>(rb, lim - 32 * (ch + 1), c, m, l);
+    }
+}
+template <bool MASKED>
+__device__ __forceinline__ void colsum_tile_ext(uint32_t taddr, int thr, int end, float c, float (&acc)[4]) {
+    uint32_t ra[32], rb[32];
+    tmem_ld_x32(taddr, ra);
+#pragma unroll
+    for (int ch = 0; ch < GROUP_COLS / 32; ch += 2) {
+        tmem_ld_wait(ra);
+        tmem_ld_x32(taddr + 32 * (ch + 1), rb);
+        colsum_chunk_ext<MASKED>(ra, thr - 32 * ch, end - 32 * ch, c, acc);
+        tmem_ld_wait(rb);
+        if (ch + 2 < GROUP_COLS / 32) tmem_ld_x32(taddr + 32 * (ch + 2), ra);
+        colsum_chunk_ext<MASKED>(rb, thr - 32 * (ch + 1), end - 32 * (ch + 1), c, acc);
+    }
+}
+#endif
+template <bool MASKED>
+__device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, int thr, int end, float c,
+                                            float (&acc)[4]) {
+    uint32_t r[32];
+#pragma unroll
+    for (int ch = 0; ch < GROUP_COLS / 32; ++ch) {
+        tmem_ld_x32(taddr + 32 * ch, r);
+        tmem_ld_wait(r);
+        colsum_chunk<MASKED>(r, nl + 8 * ch, thr - 32 * ch, end - 32 * ch, c, acc);
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -446,6 +480,13 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
                 const long long bb = idx / p.Sk;
                 p.out[bb * p.out_ld + (idx - bb * p.Sk)] = 0.f;
             }
+        }
+
+        if (MODE == MODE_STATS && p.clear_extra) {
+            // a buffer the caller wants zeroed alongside this call (the target of its next call)
+            for (long long idx = (long long)blockIdx.x * CONSUMER_THREADS + threadIdx.x; idx < p.clear_extra_n;
+                 idx += (long long)gridDim.x * CONSUMER_THREADS)
+                p.clear_extra[idx] = 0.f;
         }
 
         Items it;
@@ -844,6 +885,8 @@ static cudaError_t launch_stream(const CUtensorMap& ta, const CUtensorMap& tb, c
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, text, p);
 }
 
+static long long sms_for_clear() { return num_sms(); }
+
 static int check_operand(const char* name, const void* ptr, int64_t sb, int64_t sh, int64_t ss) {
     if (!ptr) return fail(FCS_ERR_INVALID_ARGUMENT, "%s is NULL", name);
     if (reinterpret_cast<uintptr_t>(ptr) % 16)
@@ -1068,7 +1111,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
                        int64_t ksh, int64_t kss, float scale, int causal, int k_past, int cls_n, int h_norm,
                        void* workspace, size_t workspace_bytes, int* status, void* stream_v,
                        bool clear_out = true, int passes = PASSES_BOTH, float* shared_lse = nullptr,
-                       long long norm_rows = 0) {
+                       long long norm_rows = 0, float* clear_extra = nullptr, long long clear_extra_n = 0) {
     // passes: both, or one of the two for work split over devices (non-causal only) --
     // PASSES_STATS writes -(log-sum-exp + log2(h_norm * norm_rows)) of the given query rows to
     // `shared_lse`; PASSES_COLUMNS takes that vector for ALL query rows and the given keys.
@@ -1108,6 +1151,11 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
             tms->recorded = false;
             for (int i = 0; i < 3; ++i) cudaEventRecord(tms->ev[i], stream);
         }
+        if (clear_extra && clear_extra_n > 0) {
+            clear_rows_kernel<<<(unsigned)((clear_extra_n + 1023) / 1024 < sms_for_clear() ? (clear_extra_n + 1023) / 1024
+                                                                                          : sms_for_clear()),
+                                256, 0, stream>>>(clear_extra, clear_extra_n, 1, (int)clear_extra_n);
+        }
         rc = launch_small_q(q, k, out, out_ld, B, H, Sq, Sk, D, dtype, qsb, qsh, qss, ksb, ksh, kss, scale,
                             causal, k_past, h_norm, clear_out, status, stream);
         if (rc == FCS_OK && tms) { cudaEventRecord(tms->ev[3], stream); tms->recorded = true; }
@@ -1126,6 +1174,8 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     p.out_ld = out_ld;
     p.clear_out = (clear_out && passes == PASSES_BOTH) ? 1 : 0;   // (the statistics pass does the clearing)
     p.col_combine = clear_out ? 0 : 1;   // accumulating into a caller's buffer: it may be peer-mapped
+    p.clear_extra = clear_extra_n > 0 ? clear_extra : nullptr;
+    p.clear_extra_n = clear_extra_n;
     p.status = status;
     p.c = fabsf(scale) * 1.4426950408889634f;
     p.inv_c = use_ext ? (scale < 0.f ? -1.0f : 1.0f) / p.c : 0.f;
@@ -1480,6 +1530,17 @@ int fcs_colsum_causal_accumulate(const void* q, const void* k, float* out, int H
     return fcs::colsum_impl(q, k, out, k_len, 1, H, q_len, k_len, D, dtype, q_stride_h * H, q_stride_h,
                             q_stride_s, k_stride_h * H, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm,
                             workspace, workspace_bytes, status, stream, /*clear_out=*/false);
+}
+
+int fcs_colsum_causal_accumulate_and_clear(const void* q, const void* k, float* out, float* clear_buf, int H,
+                                           int q_len, int k_len, int D, int dtype, int64_t q_stride_h,
+                                           int64_t q_stride_s, int64_t k_stride_h, int64_t k_stride_s, float scale,
+                                           int k_past, int h_norm, void* workspace, size_t workspace_bytes,
+                                           int* status, void* stream) {
+    return fcs::colsum_impl(q, k, out, k_len, 1, H, q_len, k_len, D, dtype, q_stride_h * H, q_stride_h,
+                            q_stride_s, k_stride_h * H, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm,
+                            workspace, workspace_bytes, status, stream, /*clear_out=*/false, fcs::PASSES_BOTH, nullptr,
+                            0, clear_buf, clear_buf ? (long long)k_len : 0);
 }
 
 }  // extern "C"

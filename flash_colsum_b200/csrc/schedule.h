@@ -41,6 +41,8 @@ struct Problem {
     int NKC;            // key tiles that hold at least one visible key (column pass)
     int causal, k_past; // key j is visible to query i iff j <= k_past + i
     int clear_out;      // the statistics pass zeroes `out` before the column pass adds into it
+    float* clear_extra; // the statistics pass also zeroes these clear_extra_n floats (NULL: nothing)
+    long long clear_extra_n;
     int nsplit;         // key ranges per (b, h, query tile) in the statistics pass
     int kreg;           // leading key tiles that every query block contributes to
     int col_interleave; // column pass: COL_CONTIGUOUS steps, or (b, h, key tile) chunks dealt round-robin / in contiguous runs

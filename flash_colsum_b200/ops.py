@@ -155,29 +155,36 @@ def _flash_colsum_non_batched(Q: torch.Tensor, K: torch.Tensor, scale: float, CL
 
 
 def _flash_colsum_causal(Q: torch.Tensor, K: torch.Tensor, scale: float, K_past: Optional[int] = None,
-                         h_norm: int = 0, accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         h_norm: int = 0, accumulate_into: Optional[torch.Tensor] = None,
+                         clear_next: Optional[torch.Tensor] = None) -> torch.Tensor:
     """(1, K_len) fp32.  Counterpart of kernel_causal.py:94.
 
     With ``accumulate_into`` (fp32, contiguous, K_len elements, already cleared by
     the caller; may be a peer-mapped tensor of another GPU) the result is added
-    into that tensor instead of a fresh one.
+    into that tensor instead of a fresh one; ``clear_next`` (same form, local memory)
+    is zeroed by the same kernels, for a target that alternates between two buffers.
     """
     lib = _cabi.load()
     Q, K, code = _prepare(Q, K)
     _, H, Q_len, D = Q.shape
     K_len = K.shape[2]
     with _on_device(Q.device):
+        extra = ()
         if accumulate_into is None:
             out = torch.empty((1, K_len), device=Q.device, dtype=torch.float32)
             entry = lib.fcs_colsum_causal
         else:
             out = accumulate_into
-            if out.dtype != torch.float32 or out.numel() != K_len or not out.is_contiguous():
-                raise ValueError("accumulate_into must be a contiguous fp32 tensor with K_len elements")
+            for t in (out,) if clear_next is None else (out, clear_next):
+                if t.dtype != torch.float32 or t.numel() != K_len or not t.is_contiguous():
+                    raise ValueError("accumulate_into / clear_next must be contiguous fp32 tensors with K_len elements")
             entry = lib.fcs_colsum_causal_accumulate
+            if clear_next is not None:
+                entry = lib.fcs_colsum_causal_accumulate_and_clear
+                extra = (clear_next.data_ptr(),)
         ws = _workspace(lib, Q.device, 1, H, Q_len, K_len, D, True, -1 if K_past is None else int(K_past))
         _check(entry(
-            Q.data_ptr(), K.data_ptr(), out.data_ptr(), H, Q_len, K_len, D, code,
+            Q.data_ptr(), K.data_ptr(), out.data_ptr(), *extra, H, Q_len, K_len, D, code,
             Q.stride(1), Q.stride(2), K.stride(1), K.stride(2),
             float(scale), -1 if K_past is None else int(K_past), int(h_norm),
             ws.data_ptr(), ws.numel(),

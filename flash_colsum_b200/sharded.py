@@ -33,13 +33,16 @@ def shard_range(n: int, world_size: int, rank: int) -> Tuple[int, int]:
 
 
 class PeerAccumulator:
-    """One fp32 ``(1, S_k)`` buffer per rank in symmetric (peer-mapped) memory.
+    """Two fp32 ``(1, S_k)`` buffers per rank in symmetric (peer-mapped) memory.
 
-    Used to fold the reduce of the head-sharded causal call into the kernels: the
-    buffer of rank ``dst`` is cleared, every rank's column pass adds its per-key
-    sums straight into it over NVLink (plain system-scope atomic adds to a peer
-    address, no multicast), and a device-side barrier on each side of the
-    launches orders the clear, the adds and the read.  One process per GPU; the
+    Used to fold the reduce of the head-sharded causal call into the kernels: every
+    rank's column pass adds its per-key sums straight into a buffer of rank ``dst``
+    over NVLink (plain system-scope atomic adds to a peer address, no multicast), and
+    one device-side barrier after the launches tells rank ``dst`` that all adds have
+    landed.  Calls alternate between the two buffers: while call n adds into one,
+    rank ``dst`` zeroes the other inside its own kernels (no clearing kernel, no
+    barrier before the adds) -- nobody adds into it before passing the barrier of
+    call n, which rank ``dst`` enters after those kernels.  One process per GPU; the
     constructor is a collective over ``group``.
     """
 
@@ -51,20 +54,26 @@ class PeerAccumulator:
         self.k_len = int(k_len)
         self.dst = int(dst)
         self.rank = dist.get_rank(group)
-        self.local = symm_mem.empty((1, self.k_len), dtype=torch.float32, device=device)
+        self.local = symm_mem.empty((2, self.k_len), dtype=torch.float32, device=device)
         self.handle = symm_mem.rendezvous(self.local, group)
-        self.target = self.handle.get_buffer(self.dst, (1, self.k_len), torch.float32)
+        both = self.handle.get_buffer(self.dst, (2, self.k_len), torch.float32)
+        self.targets = (both[0], both[1])
         self.local.zero_()
+        self.parity = 0
+        torch.cuda.synchronize(device)
+        self.handle.barrier(channel=0)     # every rank's buffers are clear before the first add
 
-    def reduce(self, launch: Callable[[torch.Tensor], None]) -> torch.Tensor:
-        """Run ``launch(target)`` on every rank between two barriers; rank ``dst``
-        gets the summed result (its local buffer), the others their stale buffer."""
-        if self.rank == self.dst:
-            self.local.zero_()
-        self.handle.barrier(channel=0)
-        launch(self.target)
-        self.handle.barrier(channel=1)
-        return self.local
+    def reduce(self, launch: Callable[[torch.Tensor, Optional[torch.Tensor]], None]) -> torch.Tensor:
+        """Run ``launch(target, clear_next)`` on every rank, then one barrier; rank ``dst``
+        gets the summed result (a view of its local buffer, valid until the call after the
+        next one), the others a stale buffer.  ``clear_next`` is the buffer of the next call
+        on rank ``dst`` (to be zeroed by the launched kernels) and None elsewhere."""
+        p = self.parity
+        clear_next = self.local[p ^ 1] if self.rank == self.dst else None
+        launch(self.targets[p], clear_next)
+        self.handle.barrier(channel=p)
+        self.parity = p ^ 1
+        return self.local[p:p + 1]
 
 
 def _local_partial(query: torch.Tensor, key: torch.Tensor, scale: float, is_causal: bool,
@@ -118,9 +127,12 @@ def flash_colsum_head_sharded(
         if peer.k_len != key_shard.shape[2]:
             raise ValueError(f"peer buffer holds {peer.k_len} keys, the call has {key_shard.shape[2]}")
 
-        def launch(target: torch.Tensor) -> None:
+        def launch(target: torch.Tensor, clear_next: Optional[torch.Tensor]) -> None:
             if h_local > 0:
-                ops._flash_colsum_causal(query_shard, key_shard, scale, h_norm=h_total, accumulate_into=target)
+                ops._flash_colsum_causal(query_shard, key_shard, scale, h_norm=h_total, accumulate_into=target,
+                                         clear_next=clear_next)
+            elif clear_next is not None:
+                clear_next.zero_()
 
         return peer.reduce(launch)
     if h_local == 0:

@@ -159,6 +159,21 @@ int fcs_colsum_causal_accumulate(const void *q, const void *k, float *out,
                                  void *workspace, size_t workspace_bytes, int *status, void *stream);
 
 /*
+ * fcs_colsum_causal_accumulate that also zeroes `clear_buf` (k_len floats, local device
+ * memory, may be NULL) while it runs.  For a reduce target that alternates between two
+ * buffers: the rank that owns them passes the buffer of the NEXT call here, so that the
+ * clear costs no kernel of its own and one barrier per call (after the adds) is enough --
+ * every rank has passed that barrier before anyone adds into the freshly cleared buffer.
+ * No counterpart in the reference (single GPU only, flash_colsum/kernel_causal.py:94).
+ */
+int fcs_colsum_causal_accumulate_and_clear(const void *q, const void *k, float *out, float *clear_buf,
+                                           int H, int q_len, int k_len, int D, int dtype,
+                                           int64_t q_stride_h, int64_t q_stride_s,
+                                           int64_t k_stride_h, int64_t k_stride_s,
+                                           float scale, int k_past, int h_norm,
+                                           void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+/*
  * Batched non-causal column mean for callers that cannot give the library a
  * workspace.  It has no counterpart in the reference.
  *

@@ -562,3 +562,28 @@ def test_head_shards_accumulate_into_one_buffer(fc):
         assert fc.device_status() == 0
         got = target.cpu().numpy()[None, :]
         assert_parity(got, c_oracle.colsum_c(q, k, is_causal=True), f"accumulate {H}x{Sq}x{Sk}x{D}")
+
+
+def test_accumulate_entry_clears_the_buffer_of_the_next_call(fc):
+    """A reduce target that alternates between two buffers: every call adds into one and zeroes
+    the other inside its own kernels (streaming passes, and the few-row kernel), so that a run of
+    calls needs no clearing kernel.  The buffer of the next call starts out dirty here."""
+    from flash_colsum_b200 import ops
+    for (H, Sq, Sk, D, dtype) in [(4, 100, 2500, 128, "bf16"), (4, 3, 1500, 64, "fp16")]:
+        w = Workload("acc", 1, H, Sq, Sk, D, dtype, is_causal=True, seed=H + Sq + Sk)
+        q, k = make_inputs(w)
+        qd, kd = q.cuda(), k.cuda()
+        want = c_oracle.colsum_c(q, k, is_causal=True)
+        bufs = torch.full((2, Sk), 7.0, device="cuda", dtype=torch.float32)
+        bufs[0].zero_()
+        scale = 1.0 / D ** 0.5
+        for call in range(4):
+            p = call & 1
+            # two head shards meet in the buffer of this call; the first one clears the other buffer
+            ops._flash_colsum_causal(qd[:, :2], kd[:, :2], scale, h_norm=H, accumulate_into=bufs[p],
+                                     clear_next=bufs[p ^ 1])
+            ops._flash_colsum_causal(qd[:, 2:], kd[:, 2:], scale, h_norm=H, accumulate_into=bufs[p])
+            torch.cuda.synchronize()
+            assert fc.device_status() == 0
+            assert_parity(bufs[p].cpu().numpy()[None, :], want, f"alternating target, call {call}")
+            assert float(bufs[p ^ 1].abs().max().item()) == 0.0
