@@ -510,7 +510,8 @@ def main():
                     from flash_colsum_b200.sharded import PeerAccumulator
                     peer = PeerAccumulator(w5.Sk, dev, dst=0)
                     reduce_kind = ("column-pass atomics into rank 0's peer-mapped (1,131072) fp32 buffer over "
-                                   "NVLink, device barriers before and after (no collective)")
+                                   "NVLink; the target alternates between two buffers, rank 0 clears the next one "
+                                   "inside its kernels, one device barrier after the adds (no collective)")
                 except Exception as exc:   # symmetric memory not available: keep the collective
                     peer = None
                     reduce_kind += f" (peer-memory path unavailable: {type(exc).__name__})"
@@ -520,6 +521,18 @@ def main():
 
         t5 = time_steps(long_step, max(5, min(args.steps // 2, 30)), 3, flush_buf, barrier)
         ms5 = max_over_ranks(sum(t5) / len(t5))
+        breakdown5 = None
+        if world > 1:
+            # where the time of a sharded call goes: this rank's kernels alone (local output), and the
+            # device barrier alone
+            n_b = max(5, min(args.steps // 2, 30))
+            t_loc = time_steps(lambda: fc.ops._flash_colsum_causal(q5, k5, 1.0 / w5.D ** 0.5, h_norm=w5.H), n_b, 3,
+                               flush_buf, barrier)
+            bd = {"local_kernels_ms": max_over_ranks(sum(t_loc) / len(t_loc))}
+            if peer is not None:
+                t_bar = time_steps(lambda: peer.handle.barrier(channel=0), n_b, 3, flush_buf, barrier)
+                bd["barrier_alone_ms"] = max_over_ranks(sum(t_bar) / len(t_bar))
+            breakdown5 = bd
         out5 = long_step()
         torch.cuda.synchronize()
         parity5 = long_context_parity(q5, k5, w5, out5, world, rank, dev, dist, peer is not None,
@@ -528,7 +541,7 @@ def main():
                     "parallelism": f"heads sharded over {world} GPU(s); reduce: {reduce_kind}",
                     "scaling": "strong", "ms_per_call": ms5, "value": w5.flop / (ms5 * 1e-3) / 1e12,
                     "unit": UNIT, "frac_of_peak": w5.flop / (ms5 * 1e-3) / 1e12 / peaks["tflops"],
-                    "row_sum_on_rank0": float(out5.sum().item()), "parity": parity5}
+                    "row_sum_on_rank0": float(out5.sum().item()), "parity": parity5, "breakdown": breakdown5}
         del q5, k5
     assert fc.device_status() == 0
 

@@ -86,6 +86,7 @@ inline size_t smallq_smem_for(int R, int range_rows, int stages, int bufs) {
 // Returns false when no cluster size holds the scores of a key range next to the shortest ring.
 inline bool smallq_plan(int units, int R, int keys, int D, int sms, int* CL, int* clusters, int* range_rows,
                         int* stages, int* bufs, int* wide, size_t* smem) {
+    if (D != 64 && D != 128) return false;   // rows are dealt over D/8 lanes: a power of two
     if (R < 1 || R > SMALLQ_MAX_ROWS || units < 1 || keys < 1) return false;
     if (units >= 2 * sms && (long long)keys * 2 * D <= 160 * 1024) {
         const int ncl = units < 4 * sms ? units : 4 * sms;

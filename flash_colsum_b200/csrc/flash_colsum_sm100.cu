@@ -799,7 +799,9 @@ static int num_sms() {
 }
 
 // (D, S, H, B) view of a [B, H, S, D] tensor, boxes of `box_rows` rows x 64
-// elements, 128-byte swizzle, out-of-range rows read as zero.
+// elements, 128-byte swizzle, out-of-range rows read as zero -- and so do the columns
+// from D on when D is not a multiple of 64: the kernels contract 64 or 128 columns, the
+// padding adds nothing to a score.
 static int make_tensor_map(CUtensorMap* m, const void* base, int dtype, int B, int H, int S, int D,
                            int64_t sb, int64_t sh, int64_t ss, int box_rows) {
     EncodeTiledFn enc = encode_tiled_fn();
@@ -886,6 +888,10 @@ static cudaError_t launch_stream(const CUtensorMap& ta, const CUtensorMap& tb, c
 }
 
 static long long sms_for_clear() { return num_sms(); }
+
+// Rows of 16-byte multiples (what a tensor map and a bulk copy can address), at most two
+// 64-column slabs.
+static bool head_dim_ok(int D) { return D >= 8 && D <= 128 && D % 8 == 0; }
 
 static int check_operand(const char* name, const void* ptr, int64_t sb, int64_t sh, int64_t ss) {
     if (!ptr) return fail(FCS_ERR_INVALID_ARGUMENT, "%s is NULL", name);
@@ -996,7 +1002,7 @@ static int single_pass_cluster_size(int Sk) {
 }
 
 static bool single_pass_applies(int B, int H, int Sq, int Sk, int D, int causal) {
-    if (g_single_pass == 1 || causal || D != 64 || Sk > 256 * sp::MAX_CL) return false;
+    if (g_single_pass == 1 || causal || D > 64 || Sk > 256 * sp::MAX_CL) return false;   // (D < 64: zero-filled columns)
     if (g_single_pass == 2) return true;
     const int cl = single_pass_cluster_size(Sk);
     // measured at B=32 H=16 against the two passes: 1.2-1.3x at 400-1024 keys, 1.07-1.14x at
@@ -1118,9 +1124,11 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     g_err[0] = 0;
     if (B <= 0 || H <= 0 || Sq_full <= 0 || Sk <= 0)
         return fail(FCS_ERR_INVALID_ARGUMENT, "sizes must be positive (B=%d H=%d Sq=%d Sk=%d)", B, H, Sq_full, Sk);
-    if (D != 64 && D != 128) return fail(FCS_ERR_UNSUPPORTED, "head dimension must be 64 or 128, got %d", D);
+    if (!head_dim_ok(D))
+        return fail(FCS_ERR_UNSUPPORTED, "head dimension must be a multiple of 8 from 8 to 128, got %d", D);
     if (dtype != FCS_DTYPE_FP16 && dtype != FCS_DTYPE_BF16)
         return fail(FCS_ERR_UNSUPPORTED, "dtype must be FCS_DTYPE_FP16 or FCS_DTYPE_BF16, got %d", dtype);
+    const int DK = D <= 64 ? 64 : 128;   // columns the streaming kernels contract (zero-filled beyond D)
     if (passes != PASSES_STATS) {
         if (!out) return fail(FCS_ERR_INVALID_ARGUMENT, "out is NULL");
         if (out_ld < Sk)
@@ -1237,7 +1245,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
             e = cudaMemset2DAsync(out, (size_t)out_ld * sizeof(float), 0, (size_t)Sk * sizeof(float), (size_t)B, stream);
         if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "preparing the column pass failed: %s", cudaGetErrorString(e));
     } else {
-        e = (D == 64) ? launch_stream<64, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream, false)
+        e = (DK == 64) ? launch_stream<64, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream, false)
                       : launch_stream<128, MODE_STATS>(tq_a, tk_b, text, p, grid1, stream, false);
     }
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "statistics pass launch failed: %s", cudaGetErrorString(e));
@@ -1270,22 +1278,22 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
         p.idesc = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((BLOCK / 2) >> 3) << 17);
     const bool head_major = use_ext && p.col_interleave == COL_HEAD_MAJOR;
     if (head_major && p.col_combine && p.NQB == 2)
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT2_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained)
+        e = (DK == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT2_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM_EXT_SHORT2_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained);
     else if (head_major && p.col_combine)
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained)
+        e = (DK == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM_EXT_SHORT_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained);
     else if (head_major && p.NQB == 2)   // two resident query blocks per head
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT2>(tk_a, tq_b, text, p, grid2, stream, chained)
+        e = (DK == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT2>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM_EXT_SHORT2>(tk_a, tq_b, text, p, grid2, stream, chained);
     else if (head_major)   // one query block per head, many key tiles: the key tiles stream
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT>(tk_a, tq_b, text, p, grid2, stream, chained)
+        e = (DK == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM_EXT_SHORT>(tk_a, tq_b, text, p, grid2, stream, chained);
     else if (use_ext)
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, chained)
+        e = (DK == 64) ? launch_stream<64, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM_EXT>(tk_a, tq_b, text, p, grid2, stream, chained);
     else
-        e = (D == 64) ? launch_stream<64, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream, chained)
+        e = (DK == 64) ? launch_stream<64, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream, chained)
                       : launch_stream<128, MODE_COLSUM>(tk_a, tq_b, text, p, grid2, stream, chained);
     if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "column pass launch failed: %s", cudaGetErrorString(e));
     if (tm) { cudaEventRecord(tm->ev[3], stream); tm->recorded = true; }
@@ -1385,7 +1393,7 @@ int fcs_plan_info(int B, int H, int sq_rows, int Sk, int is_causal, int* nsplit,
 }
 
 size_t fcs_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_causal) {
-    if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0 || (D != 64 && D != 128)) return 0;
+    if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0 || !fcs::head_dim_ok(D)) return 0;
     // An upper bound for every k_past and every kernel choice: the layout of the two streaming
     // passes with the key range of the statistics pass split as far as any k_past allows (the
     // split grows with the keys the first query tile sees, and k_past = Sk shows it all of them).
@@ -1402,7 +1410,8 @@ int fcs_call_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_ca
     *bytes = 0;
     if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0)
         return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "sizes must be positive (B=%d H=%d Sq=%d Sk=%d)", B, H, sq_rows, Sk);
-    if (D != 64 && D != 128) return fcs::fail(FCS_ERR_UNSUPPORTED, "head dimension must be 64 or 128, got %d", D);
+    if (!fcs::head_dim_ok(D))
+        return fcs::fail(FCS_ERR_UNSUPPORTED, "head dimension must be a multiple of 8 from 8 to 128, got %d", D);
     const int causal = is_causal ? 1 : 0;
     // the same decisions, in the same order, as the call itself
     if (fcs::smallq_fits(sq_rows, Sk, D, B * H, fcs::num_sms()))
@@ -1497,13 +1506,28 @@ int fcs_select_topk(const float* colsum, int64_t ld, int B, int S, int k, int* i
     return FCS_OK;
 }
 
+int fcs_select_threshold(const float* colsum, int64_t ld, int B, int S, float threshold, int relative, int* indices,
+                         int* counts, void* stream) {
+    fcs::g_err[0] = 0;
+    if (!colsum || !indices || !counts)
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "colsum, indices and counts must not be NULL");
+    if (B <= 0 || S <= 0 || ld < S)
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "bad sizes (B=%d S=%d ld=%lld)", B, S, (long long)ld);
+    if (!(threshold == threshold)) return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "threshold is not a number");
+    fcs::select_threshold_kernel<<<B, fcs::TOPK_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        colsum, (long long)ld, S, threshold, relative ? 1 : 0, indices, counts);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fcs::fail(FCS_ERR_CUDA, "threshold selection launch failed: %s", cudaGetErrorString(e));
+    return FCS_OK;
+}
+
 int fcs_colsum_batched_static_scratch(const void* q, const void* k, float* out, int64_t out_ld, int B, int H,
                                       int S, int D, int dtype, int64_t q_stride_b, int64_t q_stride_h,
                                       int64_t q_stride_s, int64_t k_stride_b, int64_t k_stride_h,
                                       int64_t k_stride_s, float scale, int cls_n, int h_norm, int* status,
                                       void* stream) {
     fcs::g_err[0] = 0;
-    if (B <= 0 || H <= 0 || S <= 0 || (D != 64 && D != 128))
+    if (B <= 0 || H <= 0 || S <= 0 || !fcs::head_dim_ok(D))
         return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "bad sizes (B=%d H=%d S=%d D=%d)", B, H, S, D);
     const int rows = (cls_n > 0 && cls_n < S) ? cls_n : S;
     // what this call will really use: nothing when it takes the few-row or the single-pass kernel

@@ -110,4 +110,49 @@ select_topk_kernel(const float* __restrict__ colsum, long long ld, int S, int k,
     }
 }
 
+// The threshold form of the pruning step: per batch row, the positions whose column mean is at
+// least `threshold` (relative = 0) or at least `threshold` times the row's mean value
+// (relative = 1; the means of a row sum to one, so that is threshold / S), ascending, written to
+// indices[row][0 .. counts[row]); the rest of the row of `indices` is filled with -1.
+__global__ void __launch_bounds__(TOPK_THREADS)
+select_threshold_kernel(const float* __restrict__ colsum, long long ld, int S, float threshold, int relative,
+                        int* __restrict__ indices, int* __restrict__ counts) {
+    __shared__ unsigned warp_n[TOPK_THREADS / 32];
+    __shared__ unsigned run_out;
+    __shared__ float warp_sum[TOPK_THREADS / 32];
+    const float* row = colsum + (long long)blockIdx.x * ld;
+    int* out_idx = indices + (long long)blockIdx.x * S;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    float thr = threshold;
+    if (relative) {
+        float part = 0.f;
+        for (int i = tid; i < S; i += TOPK_THREADS) part += row[i];
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) warp_sum[wid] = part;
+        __syncthreads();
+        float total = 0.f;
+        for (int w = 0; w < TOPK_THREADS / 32; ++w) total += warp_sum[w];
+        thr = threshold * total / (float)S;
+    }
+    if (tid == 0) run_out = 0;
+    __syncthreads();
+    for (int base = 0; base < S; base += TOPK_THREADS) {
+        const int i = base + tid;
+        const bool take = i < S && row[i] >= thr;
+        const unsigned m = __ballot_sync(0xffffffffu, take);
+        if (lane == 0) warp_n[wid] = __popc(m);
+        __syncthreads();
+        unsigned before = 0;
+        for (int w = 0; w < wid; ++w) before += warp_n[w];
+        before += __popc(m & ((1u << lane) - 1u));
+        if (take) out_idx[run_out + before] = i;
+        __syncthreads();
+        if (tid == TOPK_THREADS - 1) run_out += before + (take ? 1u : 0u);
+        __syncthreads();
+    }
+    const unsigned n = run_out;
+    for (int i = (int)n + tid; i < S; i += TOPK_THREADS) out_idx[i] = -1;
+    if (tid == 0) counts[blockIdx.x] = (int)n;
+}
+
 }  // namespace fcs

@@ -76,15 +76,28 @@ def _check(rc: int) -> None:
         raise RuntimeError(f"flash_colsum_b200: {_cabi.last_error()} (code {rc})")
 
 
+def _round_fp32(query: torch.Tensor, key: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 inputs are rounded to 16 bits before the tensor cores see them: to fp16, whose ten
+    mantissa bits are those of the TF32 format the reference's ``tl.dot`` gives fp32 operands
+    (kernel_noncausal_batched.py:37,54), or to bf16 when a value lies outside fp16's range.
+    The range check reads one number back from the device (the call synchronises)."""
+    limit = 60000.0
+    big = max(float(query.abs().max()), float(key.abs().max())) if query.numel() and key.numel() else 0.0
+    dt = torch.float16 if big < limit else torch.bfloat16
+    return query.to(dt), key.to(dt)
+
+
 def _prepare(query: torch.Tensor, key: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, int]:
-    if query.dtype not in _DTYPE_CODE:
-        raise ValueError(f"flash_colsum supports float16 and bfloat16 inputs, got {query.dtype}")
     if key.dtype != query.dtype:
         raise ValueError(f"query and key must have the same dtype, got {query.dtype} and {key.dtype}")
     if key.device != query.device:
         raise ValueError(f"query and key must be on the same device, got {query.device} and {key.device}")
-    if query.shape[3] not in (64, 128):
-        raise ValueError(f"head_dim must be 64 or 128, got {query.shape[3]}")
+    if query.dtype == torch.float32:
+        query, key = _round_fp32(query, key)
+    if query.dtype not in _DTYPE_CODE:
+        raise ValueError(f"flash_colsum supports float16, bfloat16 and float32 inputs, got {query.dtype}")
+    if query.shape[3] % 8 or not 8 <= query.shape[3] <= 128:
+        raise ValueError(f"head_dim must be a multiple of 8 from 8 to 128, got {query.shape[3]}")
     return _tma_ready(query), _tma_ready(key), _DTYPE_CODE[query.dtype]
 
 
@@ -204,7 +217,9 @@ def flash_colsum(
     """Column means of the attention matrix.
 
     Args:
-        query: (B, H, S, D) for non-causal or (1, H, Q_len, D) for causal; fp16 or bf16.
+        query: (B, H, S, D) for non-causal or (1, H, Q_len, D) for causal; fp16 or bf16
+            (fp32 is accepted and rounded to fp16, or to bf16 when out of fp16's range);
+            D a multiple of 8 up to 128.
         key: same shape as query (non-causal) or (1, H, K_len, D) (causal).
         scale: score scale, default 1/sqrt(D).
         is_causal: queries are aligned to the end of the keys and key j is visible
@@ -394,6 +409,33 @@ def topk_columns(colsum: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tens
     return val, idx
 
 
+def threshold_columns(colsum: torch.Tensor, threshold: float, relative: bool = False
+                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The key positions of every row whose column mean reaches a threshold.
+
+    ``colsum``: (B, S) fp32 CUDA tensor.  A position is kept when its value is at least
+    ``threshold``, or -- with ``relative`` -- at least ``threshold`` times the row's average
+    value (1.0: more than a uniform share of the attention).  Returns ``(indices, counts)``:
+    ``indices`` (B, S) int32 holds the kept positions of row b, ascending, in its first
+    ``counts[b]`` entries and -1 after them; ``counts`` is (B,) int32.  Runs on the current
+    stream without synchronising (the number kept stays on the device).
+    """
+    if colsum.ndim != 2 or colsum.dtype != torch.float32 or colsum.device.type != "cuda":
+        raise ValueError("threshold_columns takes a 2-D fp32 CUDA tensor")
+    if threshold != threshold:
+        raise ValueError("threshold is not a number")
+    B, S = colsum.shape
+    if colsum.stride(1) != 1:
+        colsum = colsum.contiguous()
+    lib = _cabi.load()
+    with _on_device(colsum.device):
+        idx = torch.empty((B, S), dtype=torch.int32, device=colsum.device)
+        cnt = torch.empty((B,), dtype=torch.int32, device=colsum.device)
+        _check(lib.fcs_select_threshold(colsum.data_ptr(), colsum.stride(0), B, S, float(threshold), int(relative),
+                                        idx.data_ptr(), cnt.data_ptr(), _raw_stream(colsum.device)))
+    return idx, cnt
+
+
 _copy_streams: Dict[int, torch.cuda.Stream] = {}
 
 
@@ -451,4 +493,5 @@ def flash_colsum_host(
         return out.cpu()
 
 
-__all__ = ["flash_colsum", "flash_colsum_causal", "flash_colsum_host", "topk_columns", "device_status"]
+__all__ = ["flash_colsum", "flash_colsum_causal", "flash_colsum_host", "topk_columns", "threshold_columns",
+           "device_status"]

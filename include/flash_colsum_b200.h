@@ -11,7 +11,9 @@
  * Common conventions
  *   - q, k: device pointers to 16-bit elements (dtype: FCS_DTYPE_*), innermost
  *     (head-dim) stride 1; the other strides are given in elements and must be
- *     multiples of 8 (16 bytes); base addresses 16-byte aligned.  D is 64 or 128.
+ *     multiples of 8 (16 bytes); base addresses 16-byte aligned.  D is a multiple
+ *     of 8 from 8 to 128 (the kernels contract 64 or 128 columns; what lies
+ *     beyond D reads as zero).
  *   - out: device pointer to fp32, row stride `out_ld` elements.  It is
  *     overwritten (zeroed by the library, then accumulated).
  *   - h_norm: number of heads the mean is taken over.  Pass H, or the global
@@ -250,6 +252,17 @@ int fcs_colsum_columns(const void *q, const void *k, const float *neg_lse, float
  */
 int fcs_select_topk(const float *colsum, int64_t ld, int B, int S, int k,
                     int *indices, float *values, void *stream);
+
+/*
+ * The threshold form of the same step: per row the positions whose column mean is at least
+ * `threshold` (relative == 0), or at least `threshold` times the row's average value
+ * (relative != 0: the means of a row sum to one, so 1.0 keeps the keys that get more than a
+ * uniform share of the attention).  indices[B][S]: the kept positions of row b, ascending, in
+ * its first counts[b] entries, -1 in the rest.  Same stream rules as fcs_select_topk; no
+ * counterpart in the reference.
+ */
+int fcs_select_threshold(const float *colsum, int64_t ld, int B, int S, float threshold, int relative,
+                         int *indices, int *counts, void *stream);
 
 /*
  * Measurement aids.  No counterpart in the reference, which times whole calls

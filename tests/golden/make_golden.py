@@ -46,6 +46,15 @@ CASES = [
     Workload("causal_bf16_outlier_keys", 1, 4, 64, 2048, 128, "bf16", is_causal=True,
              key_outliers=True, seed=14),
     Workload("causal_q300_k700_d64", 1, 2, 300, 700, 64, "bf16", is_causal=True, seed=15),
+    # head dimensions other than 64 and 128 (the reference's naive_colsum defines every D)
+    Workload("noncausal_fp16_d32", 2, 3, 300, 300, 32, "fp16", seed=16),
+    Workload("causal_bf16_d80", 1, 3, 200, 900, 80, "bf16", is_causal=True, seed=17),
+    Workload("cls_fp16_d96", 2, 2, 577, 577, 96, "fp16", cls_len=1, seed=18),
+    Workload("noncausal_fp16_d72", 1, 4, 577, 577, 72, "fp16", seed=19),
+    Workload("causal_fp16_d8_long", 1, 2, 100, 2500, 8, "fp16", is_causal=True, seed=20),
+    # fp32 inputs
+    Workload("causal_fp32_d128", 1, 2, 128, 600, 128, "fp32", is_causal=True, seed=21),
+    Workload("noncausal_fp32_d80", 2, 2, 260, 260, 80, "fp32", seed=22),
 ]
 
 

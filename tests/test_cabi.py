@@ -32,7 +32,8 @@ def test_workspace_query_is_pure_host_arithmetic():
     assert lib.fcs_workspace_bytes(8, 16, 2048, 2048, 64, 0) == 8 * 16 * 2048 * (4 + 32)
     assert lib.fcs_workspace_bytes(32, 16, 1, 577, 64, 0) >= 32 * 16 * 256 * 4   # one padded query block
     assert lib.fcs_workspace_bytes(1, 32, 512, 131072, 128, 1) > 32 * 512 * 36   # key ranges split
-    assert lib.fcs_workspace_bytes(1, 1, 1, 1, 96, 0) == 0
+    assert lib.fcs_workspace_bytes(1, 1, 1, 1, 100, 0) == 0
+    assert lib.fcs_workspace_bytes(1, 1, 8, 8, 96, 0) > 0
     assert lib.fcs_workspace_bytes(0, 1, 1, 1, 64, 0) == 0
 
 
@@ -41,7 +42,7 @@ def test_argument_errors_come_back_as_codes_not_crashes():
     rc = lib.fcs_colsum_batched(None, None, None, 0, 1, 1, 1, 64, 0, 64, 64, 64, 64, 64, 64,
                                 1.0, -1, 0, None, 0, None, None)
     assert rc < 0 and _cabi.last_error()
-    rc = lib.fcs_colsum_causal(None, None, None, 1, 1, 1, 96, 0, 96, 96, 96, 96, 1.0, -1, 0,
+    rc = lib.fcs_colsum_causal(None, None, None, 1, 1, 1, 100, 0, 104, 104, 104, 104, 1.0, -1, 0,
                                None, 0, None, None)
     assert rc == -2 and "head dimension" in _cabi.last_error()
 
@@ -67,7 +68,7 @@ def test_argument_errors_of_the_added_entry_points():
     assert lib.fcs_colsum_columns(addr(buf), addr(buf), None, addr(buf), 300, 1, 1, 300, 300, 64, 0,
                                   64, 64, 64, 64, 64, 64, 1.0, None, 0, None, None) == -1
     assert "statistics vector" in _cabi.last_error()
-    assert lib.fcs_colsum_causal_batched(None, None, None, 0, 2, 1, 1, 1, 96, 0, 96, 96, 96, 96, 96, 96,
+    assert lib.fcs_colsum_causal_batched(None, None, None, 0, 2, 1, 1, 1, 100, 0, 104, 104, 104, 104, 104, 104,
                                          1.0, -1, 0, None, 0, None, None) < 0
 
 

@@ -41,14 +41,13 @@ def test_golden_cases_match_reference_outputs(fc, golden):
     cases, arrays = golden
     ran = 0
     for w, _ in cases:
-        if w.dtype == "fp32":
-            continue
         q, k = make_inputs(w)
+        # fp32 inputs are rounded to fp16 on the way in; the stored output is of the unrounded ones
         got = run_gpu(fc, w, q, k)
         assert got.shape == arrays[w.name].shape
         assert_parity(got, arrays[w.name], w.name)
         ran += 1
-    assert ran >= 14
+    assert ran >= 23
 
 
 def test_c1_shape_in_fp16_matches_checker(fc):
@@ -99,6 +98,46 @@ def test_shapes_match_checker(fc, B, H, Sq, Sk, D, dtype, causal, cls):
     want = c_oracle.colsum_c(q, k, is_causal=causal, cls_len=cls)
     assert_parity(got, want, (B, H, Sq, Sk, D, dtype, causal, cls))
     np.testing.assert_allclose(got.sum(axis=1), 1.0, atol=2e-3)
+
+
+def test_head_dimensions_that_are_not_64_or_128(fc):
+    """Any multiple of 8 up to 128: the tensor maps zero-fill the columns up to 64 or 128, which
+    add nothing to a score; the scale defaults to 1/sqrt of the real D.  Streaming passes (causal,
+    long), the single-pass kernel (D < 64, short non-causal) and a CLS prefix (few rows: streaming
+    passes too, the few-row kernel deals rows over D/8 lanes and takes D = 64 and 128 only)."""
+    for (B, H, Sq, Sk, D, dtype, causal, cls) in [
+            (2, 4, 512, 512, 32, "fp16", False, None),      # single-pass kernel, half the columns zero
+            (1, 3, 300, 2200, 80, "bf16", True, None),
+            (2, 2, 700, 700, 72, "fp16", False, None),
+            (2, 2, 700, 700, 120, "bf16", False, 2),
+            (1, 2, 128, 5000, 8, "fp16", True, None),
+            (1, 4, 4, 3000, 96, "fp16", True, None),
+            (1, 2, 2500, 2500, 40, "fp16", False, None)]:
+        w = Workload("d", B, H, Sq, Sk, D, dtype, is_causal=causal, cls_len=cls, seed=D + Sq)
+        q, k = make_inputs(w)
+        got = run_gpu(fc, w, q, k)
+        assert_parity(got, c_oracle.colsum_c(q, k, is_causal=causal, cls_len=cls), (B, H, Sq, Sk, D, dtype, causal, cls))
+    # sliced out of a wider tensor: the row stride is not the head dimension
+    wide = torch.randn(1, 2, 600, 128, device="cuda").half()
+    qv, kv = wide[..., :48], wide[..., 64:112]
+    got = fc.flash_colsum(qv, kv).cpu().numpy()
+    assert_parity(got, c_oracle.colsum_c(qv.cpu(), kv.cpu()), "strided D=48")
+
+
+def test_fp32_inputs_are_rounded_to_16_bits(fc):
+    """fp32 in: rounded to fp16 (bf16 beyond fp16's range).  Exact against the checker fed the
+    rounded values, and inside the bar against the checker fed the fp32 values themselves."""
+    w = Workload("f", 2, 4, 600, 600, 64, "fp32", seed=41)
+    q, k = make_inputs(w)
+    got = fc.flash_colsum(q.cuda(), k.cuda()).cpu().numpy()
+    assert_parity(got, c_oracle.colsum_c(q.half(), k.half()), "fp32 -> fp16, rounded inputs")
+    assert_parity(got, c_oracle.colsum_c(q, k), "fp32 -> fp16, fp32 inputs")
+    big = q * 1000.0            # |q| up to ~4000, q.k beyond fp16: still fine as fp16 operands
+    got = fc.flash_colsum(big.cuda(), k.cuda(), scale=1e-4).cpu().numpy()
+    assert_parity(got, c_oracle.colsum_c(big.half(), k.half(), scale=1e-4), "fp32 large")
+    huge = q * 1e6              # out of fp16's range: bf16
+    got = fc.flash_colsum(huge.cuda(), k.cuda(), scale=1e-7).cpu().numpy()
+    assert_parity(got, c_oracle.colsum_c(huge.bfloat16(), k.bfloat16(), scale=1e-7), "fp32 -> bf16")
 
 
 FEW_ROWS = [
@@ -271,9 +310,13 @@ def test_error_handling(fc):
     with pytest.raises(ValueError, match="4D"):
         fc.flash_colsum(Q[0], Q[0])
     with pytest.raises(ValueError, match="head_dim"):
-        fc.flash_colsum(Q[..., :32], Q[..., :32])
-    with pytest.raises(ValueError, match="float16 and bfloat16"):
-        fc.flash_colsum(Q.float(), Q.float())
+        fc.flash_colsum(Q[..., :36], Q[..., :36])
+    with pytest.raises(ValueError, match="head_dim"):
+        fc.flash_colsum(torch.cat([Q, Q, Q], dim=-1), torch.cat([Q, Q, Q], dim=-1))
+    with pytest.raises(ValueError, match="float16, bfloat16 and float32"):
+        fc.flash_colsum(Q.double(), Q.double())
+    with pytest.raises(ValueError, match="same dtype"):
+        fc.flash_colsum(Q, Q.float())
 
 
 # ------------------------------------------------------------------ full sizes
@@ -587,3 +630,25 @@ def test_accumulate_entry_clears_the_buffer_of_the_next_call(fc):
             assert fc.device_status() == 0
             assert_parity(bufs[p].cpu().numpy()[None, :], want, f"alternating target, call {call}")
             assert float(bufs[p ^ 1].abs().max().item()) == 0.0
+
+
+def test_threshold_columns_matches_a_plain_filter(fc):
+    """The threshold form of the pruning step: kept positions ascending, the count per row, -1 after."""
+    w = Workload("thr", 3, 4, 1500, 1500, 64, "fp16", seed=13)
+    q, k = make_inputs(w)
+    col = fc.flash_colsum(q.cuda(), k.cuda())
+    host = col.cpu().numpy()
+    for thr, rel in ((1.0 / 1500, False), (0.0, False), (1.0, True), (1.5, True), (10.0, False)):
+        idx, cnt = fc.threshold_columns(col, thr, relative=rel)
+        idx, cnt = idx.cpu().numpy(), cnt.cpu().numpy()
+        for b in range(3):
+            cut = np.float32(thr) * (host[b].sum(dtype=np.float32) / np.float32(1500)) if rel else np.float32(thr)
+            keep = np.nonzero(host[b] >= cut)[0]
+            if rel:     # the kernel's row sum is taken in another order: leave out values at the cut itself
+                margin = np.abs(host[b] - cut) < 1e-6 * cut
+                assert np.array_equal(idx[b, :cnt[b]][~margin[idx[b, :cnt[b]]]], keep[~margin[keep]])
+            else:
+                assert cnt[b] == len(keep) and np.array_equal(idx[b, :cnt[b]], keep)
+            assert (idx[b, cnt[b]:] == -1).all()
+    with pytest.raises(ValueError):
+        fc.threshold_columns(col.half(), 0.1)

@@ -212,6 +212,6 @@ def test_calls_that_take_a_kernel_without_scratch_ask_for_none():
     # five rows: the streaming passes
     assert lib.fcs_call_workspace_bytes(1, 32, 5, 8192, 128, 1, -1, ctypes.byref(need)) == 0 and need.value > 0
     # sizes no call accepts
-    assert lib.fcs_call_workspace_bytes(1, 1, 1, 1, 96, 0, 0, ctypes.byref(need)) == -2
+    assert lib.fcs_call_workspace_bytes(1, 1, 1, 1, 100, 0, 0, ctypes.byref(need)) == -2
     assert lib.fcs_call_workspace_bytes(0, 1, 1, 1, 64, 0, 0, ctypes.byref(need)) == -1
     assert lib.fcs_call_workspace_bytes(1, 1, 1, 1, 64, 0, 0, None) == -1
