@@ -264,7 +264,11 @@ def kernel_only(args, fc, _cabi, dev, flush_buf, peaks):
     q = torch.randn(w.B, w.H, w.Sq, w.D, generator=g, device=dev).to(w.torch_dtype)
     k = torch.randn(w.B, w.H, w.Sk, w.D, generator=g, device=dev).to(w.torch_dtype)
 
+    target = torch.zeros(w.Sk, dtype=torch.float32, device=dev) if args.accumulate else None
+
     def call():
+        if target is not None:   # the entry head-sharded ranks call: adds into a buffer that may be peer-mapped
+            return fc.ops._flash_colsum_causal(q, k, 1.0 / w.D ** 0.5, accumulate_into=target)
         return fc.flash_colsum(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
 
     _cabi.set_profiling(True)
@@ -376,6 +380,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (kernel-only mode)")
     ap.add_argument("--keys", type=int, default=0, help="override the key length (kernel-only mode)")
+    ap.add_argument("--accumulate", action="store_true",
+                    help="kernel-only mode, causal workloads: call the accumulate entry (combined adds) instead")
     ap.add_argument("--heads", type=int, default=0, help="override the head count (kernel-only mode)")
     ap.add_argument("--queries", type=int, default=0, help="override the query length (kernel-only mode, causal workloads)")
     ap.add_argument("--no-l2-flush", action="store_true",
