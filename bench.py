@@ -271,6 +271,8 @@ def kernel_only(args, fc, _cabi, dev, flush_buf, peaks):
             return fc.ops._flash_colsum_causal(q, k, 1.0 / w.D ** 0.5, accumulate_into=target)
         return fc.flash_colsum(q, k, is_causal=w.is_causal, cls_len=w.cls_len)
 
+    if args.two_pass:
+        _cabi.set_single_pass(_cabi.SINGLE_PASS_NEVER)
     _cabi.set_profiling(True)
     for _ in range(args.warmup):
         flush_buf.zero_()
@@ -380,6 +382,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (kernel-only mode)")
     ap.add_argument("--keys", type=int, default=0, help="override the key length (kernel-only mode)")
+    ap.add_argument("--two-pass", action="store_true",
+                    help="kernel-only mode: never take the single-pass kernel (time the two streaming passes)")
     ap.add_argument("--accumulate", action="store_true",
                     help="kernel-only mode, causal workloads: call the accumulate entry (combined adds) instead")
     ap.add_argument("--heads", type=int, default=0, help="override the head count (kernel-only mode)")
