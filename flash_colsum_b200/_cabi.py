@@ -17,7 +17,7 @@ EXPORTED_SYMBOLS = (
     "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate", "fcs_colsum_causal_accumulate_and_clear",
     "fcs_set_single_pass", "fcs_single_pass_info", "fcs_single_pass_applies",
     "fcs_colsum_causal_batched", "fcs_select_topk", "fcs_select_threshold",
-    "fcs_statistics_rows", "fcs_colsum_statistics", "fcs_colsum_columns",
+    "fcs_statistics_rows", "fcs_colsum_statistics", "fcs_colsum_columns", "fcs_selftest_wait_expiry",
 )
 
 ABI_VERSION = 200   # fcs_version() of the library these argument lists were written for
@@ -93,6 +93,8 @@ def load() -> ctypes.CDLL:
                                        _i64, _f, _p, _sz, _p, _p]
     lib.fcs_select_topk.restype = _i
     lib.fcs_select_topk.argtypes = [_p, _i64, _i, _i, _i, _p, _p, _p]
+    lib.fcs_selftest_wait_expiry.restype = _i
+    lib.fcs_selftest_wait_expiry.argtypes = [_p, _p, _p, _sz, _p, ctypes.c_double, _p]
     lib.fcs_select_threshold.restype = _i
     lib.fcs_select_threshold.argtypes = [_p, _i64, _i, _i, _f, _i, _p, _p, _p]
     lib.fcs_colsum_causal_accumulate.restype = _i

@@ -218,4 +218,26 @@ __device__ __forceinline__ void colsum_chunk_ext(const uint32_t (&r)[32], int fi
     }
 }
 
+// The unmasked column-pass chunk for 16 columns (pairs PAIR0 .. PAIR0 + 7 of the 16-pair pattern).
+template <int PAIR0>
+__device__ __forceinline__ void colsum_chunk16_ext(const uint32_t (&r)[16], float c, float (&acc)[4]) {
+    const f32x2 c2 = pack2(c, c);
+    f32x2 a01 = pack2(acc[0], acc[1]), a23 = pack2(acc[2], acc[3]);
+#pragma unroll
+    for (int j = 0; j < 16; j += 4) {
+        const f32x2 ta = mul2(pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), c2);
+        const f32x2 tb = mul2(pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), c2);
+        f32x2 ea, eb;
+        float u0, u1;
+        if (pair_uses_polynomial((PAIR0 + (j >> 1)) & 15)) { ea = ex2_poly2(ta); }
+        else { unpack2(ta, u0, u1); ea = pack2(ex2_approx(u0), ex2_approx(u1)); }
+        if (pair_uses_polynomial((PAIR0 + (j >> 1) + 1) & 15)) { eb = ex2_poly2(tb); }
+        else { unpack2(tb, u0, u1); eb = pack2(ex2_approx(u0), ex2_approx(u1)); }
+        a01 = add2(a01, ea);
+        a23 = add2(a23, eb);
+    }
+    unpack2(a01, acc[0], acc[1]);
+    unpack2(a23, acc[2], acc[3]);
+}
+
 }  // namespace fcs

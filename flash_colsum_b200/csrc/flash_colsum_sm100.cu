@@ -51,16 +51,14 @@ constexpr int TMEM_COLS = 512;
 constexpr int NUM_LSE = 4;         // per-query-block log-sum-exp vectors in flight (column pass)
 // Consumer warps come in groups of four (a group covers the 128 tensor-memory
 // lanes); every group takes an equal run of the columns of each accumulator.
-#ifndef FCS_GROUPS
-#define FCS_GROUPS 4
-#endif
-constexpr int CONSUMER_GROUPS = FCS_GROUPS;
+constexpr int CONSUMER_GROUPS = 4;
 constexpr int GROUP_COLS = BLOCK / CONSUMER_GROUPS;
 constexpr int CONSUMER_WARPS = 4 * CONSUMER_GROUPS;
 constexpr int CONSUMER_THREADS = 32 * CONSUMER_WARPS;
 constexpr int PRODUCER_WARP = CONSUMER_WARPS;
 constexpr int MMA_WARP = CONSUMER_WARPS + 1;
 constexpr int THREADS = 32 * (CONSUMER_WARPS + 2);
+static_assert(GROUP_COLS == 64, "a group consumes one 64-column block per step");
 
 // Item-end partials of the statistics pass wait in one of these slots until a group
 // combines them; consumer groups are never more than two steps apart, so four
@@ -107,9 +105,6 @@ struct Layout {
 
 // A group's 64 columns of one accumulator.  `taddr`, `lim`, `thr`, `end` and
 // `nl` are relative to the group's first column.
-// One chunk of 32 columns is in flight from tensor memory while the chunk before it is in the
-// exp pipes.
-#if FCS_GROUPS == 4 && !defined(FCS_PREFETCH)
 template <bool MASKED>
 __device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, float& m, float& l) {
     uint32_t r[32];
@@ -122,6 +117,23 @@ __device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, flo
 }
 template <bool MASKED>
 __device__ __forceinline__ void colsum_tile_ext(uint32_t taddr, int thr, int end, float c, float (&acc)[4]) {
+    if constexpr (!MASKED) {
+        // 16 columns at a time, the next 16 in flight from tensor memory while these are in the exp pipes
+        uint32_t ra[16], rb[16];
+        tmem_ld_16cols(taddr, ra);
+        tmem_wait_16cols(ra);
+        tmem_ld_16cols(taddr + 16, rb);
+        colsum_chunk16_ext<0>(ra, c, acc);
+        tmem_wait_16cols(rb);
+        tmem_ld_16cols(taddr + 32, ra);
+        colsum_chunk16_ext<8>(rb, c, acc);
+        tmem_wait_16cols(ra);
+        tmem_ld_16cols(taddr + 48, rb);
+        colsum_chunk16_ext<0>(ra, c, acc);
+        tmem_wait_16cols(rb);
+        colsum_chunk16_ext<8>(rb, c, acc);
+        return;
+    }
     uint32_t r[32];
     tmem_ld_x32(taddr, r);
     tmem_ld_wait(r);
@@ -130,36 +142,6 @@ __device__ __forceinline__ void colsum_tile_ext(uint32_t taddr, int thr, int end
     tmem_ld_wait(r);
     colsum_chunk_ext<MASKED>(r, thr - 32, end - 32, c, acc);
 }
-#else
-template <bool MASKED>
-__device__ __forceinline__ void stats_tile(uint32_t taddr, int lim, float c, float& m, float& l) {
-    uint32_t ra[32], rb[32];
-    tmem_ld_x32(taddr, ra);
-#pragma unroll
-    for (int ch = 0; ch < GROUP_COLS / 32; ch += 2) {
-        tmem_ld_wait(ra);
-        tmem_ld_x32(taddr + 32 * (ch + 1), rb);
-        stats_block32<MASKED>(ra, lim - 32 * ch, c, m, l);
-        tmem_ld_wait(rb);
-        if (ch + 2 < GROUP_COLS / 32) tmem_ld_x32(taddr + 32 * (ch + 2), ra);
-        stats_block32<MASKED>(rb, lim - 32 * (ch + 1), c, m, l);
-    }
-}
-template <bool MASKED>
-__device__ __forceinline__ void colsum_tile_ext(uint32_t taddr, int thr, int end, float c, float (&acc)[4]) {
-    uint32_t ra[32], rb[32];
-    tmem_ld_x32(taddr, ra);
-#pragma unroll
-    for (int ch = 0; ch < GROUP_COLS / 32; ch += 2) {
-        tmem_ld_wait(ra);
-        tmem_ld_x32(taddr + 32 * (ch + 1), rb);
-        colsum_chunk_ext<MASKED>(ra, thr - 32 * ch, end - 32 * ch, c, acc);
-        tmem_ld_wait(rb);
-        if (ch + 2 < GROUP_COLS / 32) tmem_ld_x32(taddr + 32 * (ch + 2), ra);
-        colsum_chunk_ext<MASKED>(rb, thr - 32 * (ch + 1), end - 32 * (ch + 1), c, acc);
-    }
-}
-#endif
 template <bool MASKED>
 __device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, int thr, int end, float c,
                                             float (&acc)[4]) {
@@ -260,7 +242,7 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
             it.init(p, blockIdx.x, gridDim.x);
             int a_cnt = 0, stage = 0, n = 0;
             uint32_t phase = 0;
-            bool ok = true;
+            bool ok = p.withhold_loads == 0;   // (self-test: nothing is loaded, every wait for data runs out)
             // which streamed block every stage holds: when a (batch, head) has no more blocks
             // than there are stages (short query axes in the column pass, short key axes in the
             // statistics pass), the next item finds its blocks still in shared memory and the
@@ -1503,6 +1485,50 @@ int fcs_select_topk(const float* colsum, int64_t ld, int B, int S, int k, int* i
         colsum, (long long)ld, S, k, indices, values);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fcs::fail(FCS_ERR_CUDA, "top-k selection launch failed: %s", cudaGetErrorString(e));
+    return FCS_OK;
+}
+
+int fcs_selftest_wait_expiry(const void* q, const void* k, void* workspace, size_t workspace_bytes, int* status,
+                              double limit_seconds, void* stream_v) {
+    fcs::g_err[0] = 0;
+    using namespace fcs;
+    if (!q || !k || !workspace || !status)
+        return fail(FCS_ERR_INVALID_ARGUMENT, "q, k, workspace and status must not be NULL");
+    if (!(limit_seconds > 0.0) || limit_seconds > 2.0)
+        return fail(FCS_ERR_INVALID_ARGUMENT, "limit_seconds must be in (0, 2]");
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+    // a statistics pass over one 128 x 256 tile of fp16 inputs with D = 64
+    const int B = 1, H = 1, Sq = TILE, Sk = BLOCK, D = 64;
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    plan(p, B, H, Sq, Sk, 0, 0, num_sms());
+    size_t part_off = 0, ext_off = 0;
+    const size_t need = workspace_layout(p, &part_off, &ext_off);
+    if (workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256)
+        return fail(FCS_ERR_WORKSPACE, "workspace too small or misaligned: need %zu bytes", need);
+    p.neg_lse = reinterpret_cast<float*>(workspace);
+    p.part = reinterpret_cast<uint8_t*>(workspace) + part_off;
+    p.ext = reinterpret_cast<uint8_t*>(workspace) + ext_off;
+    p.status = status;
+    p.c = 0.125f * 1.4426950408889634f;
+    p.inv_c = 1.0f / p.c;
+    p.log2_norm = log2f((float)Sq);
+    p.idesc = (1u << 4) | ((uint32_t)(BLOCK >> 3) << 17) | ((uint32_t)(TILE >> 4) << 24);
+    p.withhold_loads = 1;
+    CUtensorMap tq, tk;
+    int rc;
+    if ((rc = make_tensor_map(&tq, q, FCS_DTYPE_FP16, B, H, Sq, D, (int64_t)Sq * D, (int64_t)Sq * D, D, TILE)) != FCS_OK) return rc;
+    if ((rc = make_tensor_map(&tk, k, FCS_DTYPE_FP16, B, H, Sk, D, (int64_t)Sk * D, (int64_t)Sk * D, D, BLOCK)) != FCS_OK) return rc;
+    static long long short_limit, full_limit = kWaitLimitCycles;
+    short_limit = (long long)(limit_seconds * 1.9e9);
+    cudaError_t e = cudaMemcpyToSymbolAsync(g_wait_limit_cycles, &short_limit, sizeof(long long), 0,
+                                            cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = launch_stream<64, MODE_STATS>(tq, tk, tq, p, 1, stream, false);
+    const cudaError_t e2 = cudaMemcpyToSymbolAsync(g_wait_limit_cycles, &full_limit, sizeof(long long), 0,
+                                                   cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess || e2 != cudaSuccess)
+        return fail(FCS_ERR_CUDA, "wait-expiry self-test failed to launch: %s",
+                    cudaGetErrorString(e != cudaSuccess ? e : e2));
     return FCS_OK;
 }
 

@@ -64,6 +64,7 @@ struct Problem {
     long long out_ld;
     int* status;
     uint32_t idesc;
+    int withhold_loads; // self-test only: the producer issues no copies, so that the bounded waits run out
 };
 
 FCS_HD inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

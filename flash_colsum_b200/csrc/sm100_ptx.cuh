@@ -12,6 +12,8 @@ namespace fcs {
 // A wait that has not completed after this many SM cycles (about two seconds)
 // reports a status code and returns false instead of spinning forever.
 constexpr long long kWaitLimitCycles = 4000000000ll;
+// The limit in force (set to kWaitLimitCycles; the wait-expiry self-test lowers it for one launch).
+__constant__ long long g_wait_limit_cycles = kWaitLimitCycles;
 constexpr uint32_t kSuspendHintNs = 20000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -94,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 15u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > g_wait_limit_cycles) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, 0, code);
                 return false;
@@ -206,6 +208,23 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+// The same for 16 consecutive columns.
+__device__ __forceinline__ void tmem_ld_16cols(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_16cols(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
 }
 // Wait for the loads above.  The registers are passed through the statement so
 // that no use of them can be scheduled ahead of the wait.

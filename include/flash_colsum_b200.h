@@ -298,6 +298,21 @@ int fcs_single_pass_applies(int B, int H, int sq_rows, int Sk, int D, int is_cau
 int fcs_single_pass_info(int Sk, int *cluster_size, int *max_clusters);
 
 /*
+ * Self-test of the device status path.  Every wait inside the kernels (on an mbarrier that a
+ * copy, an MMA or another warp completes) is bounded: when it runs out, the CTA raises an abort
+ * flag, stores an FCS_STATUS_* code to *status, all its roles fall through to the teardown,
+ * tensor memory is freed and the kernel returns -- the context stays usable.  This entry runs one
+ * statistics pass (one 128 x 256 tile; q: 128 x 64 fp16, k: 256 x 64 fp16, both readable) whose
+ * producer issues no copies, with the limit lowered to `limit_seconds` (at most 2) for that
+ * launch, so that the waits for data do run out: afterwards *status is FCS_STATUS_WAIT_MMA or
+ * FCS_STATUS_WAIT_CONSUMER, and ordinary calls on the same stream work as before.  Nothing
+ * faults, traps or spins without bound.  workspace: fcs_workspace_bytes(1, 1, 128, 256, 64, 0)
+ * bytes.  No counterpart in the reference, whose kernels cannot fail softly.
+ */
+int fcs_selftest_wait_expiry(const void *q, const void *k, void *workspace, size_t workspace_bytes,
+                             int *status, double limit_seconds, void *stream);
+
+/*
  * How a call with these sizes is decomposed on the current device: key ranges
  * per query tile in the statistics pass, its work items, the 128x128 score
  * tiles of the column pass, and the SM count used for planning.  Host

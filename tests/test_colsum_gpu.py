@@ -652,3 +652,28 @@ def test_threshold_columns_matches_a_plain_filter(fc):
             assert (idx[b, cnt[b]:] == -1).all()
     with pytest.raises(ValueError):
         fc.threshold_columns(col.half(), 0.1)
+
+
+def test_a_wait_that_runs_out_reports_a_status_and_leaves_the_context_usable(fc):
+    """The bounded waits of the streaming kernel: a statistics pass whose producer issues no copies
+    (the flag nothing sets), with the limit lowered to 50 ms for that launch.  The waits for data
+    run out, the CTA aborts through its teardown (tensor memory freed), the status word says
+    which role gave up -- and the next ordinary call on the same stream is correct."""
+    from flash_colsum_b200 import _cabi
+    lib = _cabi.load()
+    q = torch.randn(128, 64, device="cuda").half()
+    k = torch.randn(256, 64, device="cuda").half()
+    ws = torch.empty(lib.fcs_workspace_bytes(1, 1, 128, 256, 64, 0), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.fcs_selftest_wait_expiry(q.data_ptr(), k.data_ptr(), ws.data_ptr(), ws.numel(), status.data_ptr(),
+                                        0.05, stream) == 0, _cabi.last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) in (2, 3)       # FCS_STATUS_WAIT_MMA or FCS_STATUS_WAIT_CONSUMER
+    assert lib.fcs_selftest_wait_expiry(q.data_ptr(), k.data_ptr(), ws.data_ptr(), ws.numel(), status.data_ptr(),
+                                        5.0, stream) == -1     # the limit is capped
+    # the library's own status word was not involved, and the kernels run as before
+    w = Workload("after", 2, 3, 700, 700, 64, "fp16", seed=99)
+    qq, kk = make_inputs(w)
+    got = run_gpu(fc, w, qq, kk)
+    assert_parity(got, c_oracle.colsum_c(qq, kk), "call after an expired wait")
