@@ -521,8 +521,7 @@ def main():
                     peer = PeerAccumulator(w5.Sk, dev, dst=0)
                     reduce_kind = ("column-pass atomics into rank 0's peer-mapped (1,131072) fp32 buffer over "
                                    "NVLink; the target alternates between two buffers, rank 0 clears the next one "
-                                   "inside its kernels; every rank then posts a flag on rank 0, which alone waits "
-                                   "(release/acquire flags in peer memory: no collective, no all-to-all barrier)")
+                                   "inside its kernels, one device barrier after the adds (no collective)")
                 except Exception as exc:   # symmetric memory not available: keep the collective
                     peer = None
                     reduce_kind += f" (peer-memory path unavailable: {type(exc).__name__})"
@@ -541,10 +540,8 @@ def main():
                                flush_buf, barrier)
             bd = {"local_kernels_ms": max_over_ranks(sum(t_loc) / len(t_loc))}
             if peer is not None:
-                # the flags of a call with nothing to add (rank 0 still clears the next buffer)
-                t_bar = time_steps(lambda: peer.reduce(lambda t, c: c.zero_() if c is not None else None), n_b, 3,
-                                   flush_buf, barrier)
-                bd["flags_alone_ms"] = max_over_ranks(sum(t_bar) / len(t_bar))
+                t_bar = time_steps(lambda: peer.handle.barrier(channel=0), n_b, 3, flush_buf, barrier)
+                bd["barrier_alone_ms"] = max_over_ranks(sum(t_bar) / len(t_bar))
             breakdown5 = bd
         out5 = long_step()
         torch.cuda.synchronize()

@@ -18,7 +18,6 @@ EXPORTED_SYMBOLS = (
     "fcs_set_single_pass", "fcs_single_pass_info", "fcs_single_pass_applies",
     "fcs_colsum_causal_batched", "fcs_select_topk", "fcs_select_threshold",
     "fcs_statistics_rows", "fcs_colsum_statistics", "fcs_colsum_columns", "fcs_selftest_wait_expiry",
-    "fcs_peer_post", "fcs_peer_wait",
 )
 
 ABI_VERSION = 200   # fcs_version() of the library these argument lists were written for
@@ -94,10 +93,6 @@ def load() -> ctypes.CDLL:
                                        _i64, _f, _p, _sz, _p, _p]
     lib.fcs_select_topk.restype = _i
     lib.fcs_select_topk.argtypes = [_p, _i64, _i, _i, _i, _p, _p, _p]
-    lib.fcs_peer_post.restype = _i
-    lib.fcs_peer_post.argtypes = [ctypes.POINTER(_p), _i, _i, _p]
-    lib.fcs_peer_wait.restype = _i
-    lib.fcs_peer_wait.argtypes = [_p, _i, _i, _p, _p]
     lib.fcs_selftest_wait_expiry.restype = _i
     lib.fcs_selftest_wait_expiry.argtypes = [_p, _p, _p, _sz, _p, ctypes.c_double, _p]
     lib.fcs_select_threshold.restype = _i

@@ -739,40 +739,6 @@ __global__ void merge_stats_kernel(const Problem p) {
 }
 
 // ---------------------------------------------------------------------------
-// Flags between the GPUs of a node (peer-mapped memory), for callers that order their
-// kernels across ranks without a collective: a release store per flag, and a bounded wait
-// until every flag has reached a value.
-// ---------------------------------------------------------------------------
-constexpr int PEER_FLAGS_MAX = 16;
-struct PeerFlagPointers { int* p[PEER_FLAGS_MAX]; };
-
-__global__ void peer_post_kernel(const PeerFlagPointers flags, int n, int value) {
-    if ((int)threadIdx.x < n) {
-        // everything the kernels before this one in the stream wrote (to any GPU) is visible to
-        // whoever reads this value with an acquire load
-        __threadfence_system();
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.p[threadIdx.x]), "r"(value) : "memory");
-    }
-}
-
-__global__ void peer_wait_kernel(const int* flags, int n, int value, int* status) {
-    if ((int)threadIdx.x < n) {
-        const long long t0 = clock64();
-        unsigned spins = 0;
-        while (true) {
-            int v;
-            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
-            if (v >= value) break;
-            if ((++spins & 63u) == 0u && clock64() - t0 > g_wait_limit_cycles) {
-                if (status) atomicCAS(status, 0, FCS_STATUS_WAIT_PEER);
-                break;
-            }
-            __nanosleep(100);
-        }
-    }
-}
-
-// ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
 static thread_local char g_err[512] = "";
@@ -1519,33 +1485,6 @@ int fcs_select_topk(const float* colsum, int64_t ld, int B, int S, int k, int* i
         colsum, (long long)ld, S, k, indices, values);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fcs::fail(FCS_ERR_CUDA, "top-k selection launch failed: %s", cudaGetErrorString(e));
-    return FCS_OK;
-}
-
-int fcs_peer_post(int* const* flags, int n_flags, int value, void* stream) {
-    fcs::g_err[0] = 0;
-    if (!flags || n_flags <= 0 || n_flags > fcs::PEER_FLAGS_MAX)
-        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "1 to %d flag pointers are expected, got %d", fcs::PEER_FLAGS_MAX, n_flags);
-    fcs::PeerFlagPointers fp;
-    memset(&fp, 0, sizeof(fp));
-    for (int i = 0; i < n_flags; ++i) {
-        if (!flags[i] || reinterpret_cast<uintptr_t>(flags[i]) % 4)
-            return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "flag %d is NULL or misaligned", i);
-        fp.p[i] = flags[i];
-    }
-    fcs::peer_post_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(fp, n_flags, value);
-    const cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fcs::fail(FCS_ERR_CUDA, "flag post launch failed: %s", cudaGetErrorString(e));
-    return FCS_OK;
-}
-
-int fcs_peer_wait(const int* flags, int n_flags, int value, int* status, void* stream) {
-    fcs::g_err[0] = 0;
-    if (!flags || n_flags <= 0 || n_flags > 32 || reinterpret_cast<uintptr_t>(flags) % 4)
-        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "1 to 32 consecutive, aligned flags are expected, got %d", n_flags);
-    fcs::peer_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flags, n_flags, value, status);
-    const cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fcs::fail(FCS_ERR_CUDA, "flag wait launch failed: %s", cudaGetErrorString(e));
     return FCS_OK;
 }
 

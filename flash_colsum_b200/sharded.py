@@ -33,90 +33,45 @@ def shard_range(n: int, world_size: int, rank: int) -> Tuple[int, int]:
 
 
 class PeerAccumulator:
-    """Two fp32 ``(1, S_k)`` buffers and a few flags per rank in symmetric (peer-mapped) memory.
+    """Two fp32 ``(1, S_k)`` buffers per rank in symmetric (peer-mapped) memory.
 
     Used to fold the reduce of the head-sharded causal call into the kernels: every
     rank's column pass adds its per-key sums straight into a buffer of rank ``dst``
-    over NVLink (plain system-scope atomic adds to a peer address, no multicast), then
-    stores a flag on rank ``dst`` (release, system scope); rank ``dst`` waits for the flags
-    of all ranks -- a bounded wait in a one-warp kernel -- and has the sum.  No collective and
-    no all-to-all barrier: only rank ``dst`` waits for the others.  Calls alternate between
-    the two buffers: while call n adds into one, rank ``dst`` zeroes the other inside its
-    own kernels and then tells every rank so (a second flag); a rank starts the adds of call
-    n + 1 only after it has seen that flag of call n.  One process per GPU; the constructor
-    is a collective over ``group``.
+    over NVLink (plain system-scope atomic adds to a peer address, no multicast), and
+    one device-side barrier after the launches tells rank ``dst`` that all adds have
+    landed.  Calls alternate between the two buffers: while call n adds into one,
+    rank ``dst`` zeroes the other inside its own kernels (no clearing kernel, no
+    barrier before the adds) -- nobody adds into it before passing the barrier of
+    call n, which rank ``dst`` enters after those kernels.  One process per GPU; the
+    constructor is a collective over ``group``.
     """
 
     def __init__(self, k_len: int, device: torch.device, group=None, dst: int = 0):
         # peer mappings only: keep NVLink multicast objects out of it
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        import ctypes
         import torch.distributed._symmetric_memory as symm_mem
-        from . import _cabi
         group = group if group is not None else dist.group.WORLD
         self.k_len = int(k_len)
         self.dst = int(dst)
         self.rank = dist.get_rank(group)
-        self.world = dist.get_world_size(group)
-        if self.world > 16:
-            raise ValueError("the peer-memory reduce is built for the GPUs of one node (at most 16 ranks)")
         self.local = symm_mem.empty((2, self.k_len), dtype=torch.float32, device=device)
         self.handle = symm_mem.rendezvous(self.local, group)
         both = self.handle.get_buffer(self.dst, (2, self.k_len), torch.float32)
         self.targets = (both[0], both[1])
         self.local.zero_()
-        # flags: [0, world) "rank r has finished call n" (read on rank dst), [32] "the buffer of the
-        # next call is clear" (written by rank dst on every rank)
-        self.flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
-        self.flag_handle = symm_mem.rendezvous(self.flags, group)
-        self.flags.zero_()
-        self._lib = _cabi.load()
-        self._device = device
-        done_on_dst = self.flag_handle.get_buffer(self.dst, (64,), torch.int32)
-        self._keep = [done_on_dst]
-        if self.rank == self.dst:
-            peers = [self.flag_handle.get_buffer(r, (64,), torch.int32) for r in range(self.world) if r != self.dst]
-            self._keep += peers
-            self._post = (ctypes.c_void_p * max(1, len(peers)))(*[t.data_ptr() + 32 * 4 for t in peers])
-            self._n_post = len(peers)
-        else:
-            self._post = (ctypes.c_void_p * 1)(done_on_dst.data_ptr() + 4 * self.rank)
-            self._n_post = 1
-        self.calls = 0
         self.parity = 0
         torch.cuda.synchronize(device)
-        self.handle.barrier(channel=0)     # every rank's buffers and flags are clear before the first add
-        torch.cuda.synchronize(device)
+        self.handle.barrier(channel=0)     # every rank's buffers are clear before the first add
 
     def reduce(self, launch: Callable[[torch.Tensor, Optional[torch.Tensor]], None]) -> torch.Tensor:
-        """Run ``launch(target, clear_next)`` on every rank; rank ``dst`` gets the summed result
-        (a view of its local buffer, valid until the call after the next one), the others a stale
-        buffer.  ``clear_next`` is the buffer of the next call on rank ``dst`` (to be zeroed by
-        the launched kernels) and None elsewhere."""
-        from . import ops
-        self.calls += 1
-        n, p = self.calls, self.parity
-        lib, dev = self._lib, self._device
-        stream = ops._raw_stream(dev)
-        status = ops._status_word(dev).data_ptr()
-        with ops._on_device(dev):
-            if self.rank != self.dst:
-                # the buffer this call adds into was cleared during call n - 1
-                ops._check(lib.fcs_peer_wait(self.flags.data_ptr() + 32 * 4, 1, n - 1, status, stream))
-            launch(self.targets[p], self.local[p ^ 1] if self.rank == self.dst else None)
-            if self.rank == self.dst:
-                if self._n_post:
-                    ops._check(lib.fcs_peer_post(self._post, self._n_post, n, stream))
-                    others = [r for r in range(self.world) if r != self.dst]
-                    lo, hi = min(others), max(others)
-                    # (rank dst's own slot is never posted: wait on the slots before and after it)
-                    if lo < self.dst:
-                        ops._check(lib.fcs_peer_wait(self.flags.data_ptr() + 4 * lo, self.dst - lo, n, status, stream))
-                    if hi > self.dst:
-                        ops._check(lib.fcs_peer_wait(self.flags.data_ptr() + 4 * (self.dst + 1), hi - self.dst, n,
-                                                     status, stream))
-            else:
-                ops._check(lib.fcs_peer_post(self._post, 1, n, stream))
+        """Run ``launch(target, clear_next)`` on every rank, then one barrier; rank ``dst``
+        gets the summed result (a view of its local buffer, valid until the call after the
+        next one), the others a stale buffer.  ``clear_next`` is the buffer of the next call
+        on rank ``dst`` (to be zeroed by the launched kernels) and None elsewhere."""
+        p = self.parity
+        clear_next = self.local[p ^ 1] if self.rank == self.dst else None
+        launch(self.targets[p], clear_next)
+        self.handle.barrier(channel=p)
         self.parity = p ^ 1
         return self.local[p:p + 1]
 

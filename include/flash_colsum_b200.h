@@ -52,7 +52,6 @@ extern "C" {
 #define FCS_STATUS_WAIT_PRODUCER 1
 #define FCS_STATUS_WAIT_MMA 2
 #define FCS_STATUS_WAIT_CONSUMER 3
-#define FCS_STATUS_WAIT_PEER 4
 
 /* Library version, as major * 10000 + minor * 100 + patch. */
 int fcs_version(void);
@@ -175,20 +174,6 @@ int fcs_colsum_causal_accumulate_and_clear(const void *q, const void *k, float *
                                            int64_t k_stride_h, int64_t k_stride_s,
                                            float scale, int k_past, int h_norm,
                                            void *workspace, size_t workspace_bytes, int *status, void *stream);
-
-/*
- * Flags between the GPUs of a node, for ordering the calls above across ranks without a
- * collective (one process per GPU; the flags live in peer-mapped memory).  fcs_peer_post
- * stores `value` to each of the n_flags (at most 16) addresses with release semantics at system
- * scope, on `stream`: everything the kernels before it in that stream wrote -- adds into another
- * GPU's buffer included -- is visible to a rank that has seen the value.  fcs_peer_wait holds
- * `stream` until each of the n_flags (at most 32) consecutive ints at `flags` (local memory) is
- * at least `value`, reading with acquire semantics; the wait is bounded (about two seconds), after
- * which FCS_STATUS_WAIT_PEER is stored to *status and the stream moves on.  A rank that waits
- * never runs on the same GPU as the rank it waits for.  No counterpart in the reference.
- */
-int fcs_peer_post(int *const *flags, int n_flags, int value, void *stream);
-int fcs_peer_wait(const int *flags, int n_flags, int value, int *status, void *stream);
 
 /*
  * Batched non-causal column mean for callers that cannot give the library a
