@@ -83,6 +83,29 @@ def test_validation_order_and_messages_without_a_gpu():
         f(torch.randn(1, 8, 128, 64), torch.randn(1, 8, 128, 64), cls_len=0)
 
 
+def test_argument_errors_of_the_pruning_and_self_test_entries():
+    """The threshold selection and the wait-expiry self-test refuse bad arguments before any launch;
+    the product package does not import the reference install either."""
+    lib = _cabi.load()
+    buf = (ctypes.c_float * 64)()
+    idx = (ctypes.c_int * 64)()
+    addr = ctypes.addressof
+    assert lib.fcs_select_threshold(None, 8, 1, 8, 0.5, 0, None, None, None) == -1
+    assert lib.fcs_select_threshold(addr(buf), 4, 1, 8, 0.5, 0, addr(idx), addr(idx), None) == -1     # ld < S
+    assert lib.fcs_select_threshold(addr(buf), 8, 1, 8, float("nan"), 0, addr(idx), addr(idx), None) == -1
+    assert "not a number" in _cabi.last_error()
+    assert lib.fcs_selftest_wait_expiry(None, None, None, 0, None, 0.05, None) == -1
+    assert lib.fcs_selftest_wait_expiry(addr(buf), addr(buf), addr(buf), 0, addr(idx), 3.0, None) == -1
+    assert "limit_seconds" in _cabi.last_error()
+    assert lib.fcs_colsum_causal_accumulate_and_clear(None, None, None, None, 1, 1, 1, 64, 0, 64, 64, 64, 64, 1.0, -1,
+                                                      0, None, 0, None, None) < 0
+    pkg = os.path.join(ROOT, "flash_colsum_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for fn in files:
+            if fn.endswith(".py"):
+                assert "baseline/_ref" not in open(os.path.join(dirpath, fn)).read(), fn
+
+
 def test_no_cpu_fallback_in_the_product_package():
     """The package never imports the CPU checkers."""
     pkg = os.path.join(ROOT, "flash_colsum_b200")
