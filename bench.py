@@ -615,7 +615,8 @@ def main():
                       "tflops_rows_used": w3.flop_rows_used / (ms3 * 1e-3) / 1e12,
                       "roofline": {"bound": "hbm", "achieved": bytes3 / (kern3 * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                                    "unit": "GB/s", "frac": bytes3 / (kern3 * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                                   "bytes_per_launch": bytes3,
+                                   "bytes_per_launch": bytes3, "traffic": load_traffic("small_q_c3"),
+                                   "traffic_source": "constant from profiles/dram_traffic.json: one ncu capture of this kernel at full size",
                                    "bytes": "every key once + the CLS rows + the output; event time of the two kernels of the call",
                                    "frac_of_call": bytes3 / (ms3 * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
         del q3, k3
