@@ -150,6 +150,10 @@ FEW_ROWS = [
     (1, 2, 2, 31, 128, "fp16", False),        # fewer keys than one range wants
     (3, 2, 4, 64, 64, "fp16", True),          # R = 4 queries at the end of 64 keys
     (1, 1, 4, 3, 64, "bf16", True),           # fewer keys than queries
+    (25, 8, 1, 577, 64, "fp16", False),       # 200 units on 148 persistent CTAs: a unit is finished behind the next one's scores
+    (10, 20, 3, 1500, 128, "bf16", False),    # the same with three rows and clusters of two
+    (40, 16, 2, 300, 64, "fp16", False),      # 640 short units: four CTAs per SM, more than one unit each
+    (37, 8, 4, 257, 128, "bf16", False),      # 296 short units of four rows
 ]
 
 
