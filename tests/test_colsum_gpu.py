@@ -681,3 +681,31 @@ def test_a_wait_that_runs_out_reports_a_status_and_leaves_the_context_usable(fc)
     qq, kk = make_inputs(w)
     got = run_gpu(fc, w, qq, kk)
     assert_parity(got, c_oracle.colsum_c(qq, kk), "call after an expired wait")
+
+
+def test_agrees_with_the_reference_kernels_where_they_are_exact(fc):
+    """Against the reference's own Triton kernels (an unmodified install of the reference in
+    baseline/_ref; skipped when there is none) on shapes where those kernels follow
+    ``naive_colsum``: head dimension 64 and key lengths that are multiples of their tiles.
+    Their result is fp16, so the bar is wider than against the checker."""
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref_dir = os.path.join(root, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "flash_colsum")):
+        pytest.skip("no install of the reference in baseline/_ref")
+    if ref_dir not in sys.path:
+        sys.path.append(ref_dir)
+    try:
+        from flash_colsum import flash_colsum as ref_flash_colsum
+    except Exception as exc:      # Triton missing or not importable here
+        pytest.skip(f"the reference does not import: {exc}")
+    for (B, H, Sq, Sk, causal) in [(4, 8, 1024, 1024, False), (1, 8, 2048, 2048, False), (1, 8, 128, 4096, True)]:
+        w = Workload("ref", B, H, Sq, Sk, 64, "fp16", is_causal=causal, seed=B + Sk)
+        q, k = make_inputs(w)
+        qd, kd = q.cuda(), k.cuda()
+        theirs = ref_flash_colsum(qd, kd, is_causal=causal).float()
+        ours = fc.flash_colsum(qd, kd, is_causal=causal)
+        torch.cuda.synchronize()
+        rel = float(((ours - theirs).norm() / ours.norm()).item())
+        assert theirs.shape == ours.shape and rel <= 3e-3, (B, H, Sq, Sk, causal, rel)
