@@ -4,20 +4,25 @@
 // the tensor cores, so it is not reshaped into a GEMM; what matters is that every
 // SM streams keys without pause.
 //
-//   * Persistent CTAs, one per SM, grouped into thread-block clusters of 1..8.  A
-//     cluster walks a list of (batch, head) units; CTA r of the cluster owns the r-th
-//     range of every unit's key axis.  The cluster size is chosen so that the busiest
-//     SM has the least to read: a decode query over 32 heads is cut eight ways and
-//     fills the device, a CLS call over 512 units is cut in two for balance.
-//   * One warp issues bulk asynchronous copies (cp.async.bulk, completion counted on
-//     an mbarrier -- no tensor map, no multicast) of 16 KiB runs of key rows into a
-//     ring of up to ten shared-memory stages, and runs ahead of the consumers across
-//     unit boundaries: the epilogue of one unit overlaps the loads of the next.
-//   * Eight consumer warps compute the scores of a unit's range as the stages land
-//     (D/8 lanes share a key row), keep them in shared memory, take maximum, exp2 and
-//     sum, and post (maximum, sum) per query row into every CTA of the cluster with
-//     st.async, counted on the receiver's mbarrier -- no cluster-wide barrier per unit.
-//     With all ranges' values in, each CTA adds its keys' share into the output.
+//   * Few units over long key axes (a decode query over 32 heads): persistent CTAs, one per
+//     SM, grouped into thread-block clusters of 1..8.  A cluster walks a list of (batch, head)
+//     units; CTA r of the cluster owns the r-th range of every unit's key axis.  The cluster
+//     size is the one with which the busiest CTA has the least to read (32 heads over 32768
+//     keys: clusters of four, 128 CTAs of 2 MiB each).
+//   * Many short units (a CLS call over 512 units of 74 KB): four CTAs per SM, one unit each,
+//     no cut -- the units in flight on an SM hide each other's latency chains.
+//   * One warp per CTA issues bulk asynchronous copies (cp.async.bulk, completion counted on an
+//     mbarrier -- no tensor map, no multicast) of 16 KiB runs of key rows into a ring of up to
+//     ten shared-memory stages, and runs ahead of the consumers across unit boundaries.  (One
+//     such warp moves 33-35 GB/s per SM whatever the ring depth -- measured with the scoring
+//     switched off -- which is what bounds the long-key form.)
+//   * The consumer warps compute the scores of a unit's range as the stages land: a warp takes
+//     32 rows, D/8 lanes per row over D/8 passes, then transposes and adds the partial dot
+//     products with D/8 - 1 shuffles, after which every lane holds one row's score.  Scores stay
+//     in shared memory; a running (maximum, sum) per thread is merged once per unit and posted
+//     into every CTA of the cluster with st.async, counted on the receiver's mbarrier -- no
+//     cluster-wide barrier per unit.  A unit is finished (weights, one add per key into the
+//     output) one unit late, behind the scores of the next, when every range's values are in.
 //   * The output is cleared by a small kernel launched just before; this kernel is a
 //     programmatic dependent of it and waits for it only before its first add, so the
 //     clear costs no time on the device.
