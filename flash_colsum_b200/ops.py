@@ -439,6 +439,21 @@ def threshold_columns(colsum: torch.Tensor, threshold: float, relative: bool = F
 _copy_streams: Dict[int, torch.cuda.Stream] = {}
 
 
+def _host_chunks(B: int, batch_chunk: Optional[int]):
+    """(first entry, entries) of the chunks a host-memory call is copied and computed in."""
+    if batch_chunk is not None:
+        if batch_chunk <= 0:
+            raise ValueError(f"batch_chunk must be positive, got {batch_chunk}")
+        return [(b0, min(batch_chunk, B - b0)) for b0 in range(0, B, batch_chunk)]
+    out, b0 = [], 0
+    while b0 < B:
+        left = B - b0
+        n = left - max(1, left // 4) if left > 2 else 1
+        out.append((b0, n))
+        b0 += n
+    return out
+
+
 def flash_colsum_host(
     query: torch.Tensor,
     key: torch.Tensor,
@@ -447,15 +462,18 @@ def flash_colsum_host(
     cls_len: Optional[int] = None,
     *,
     device: Optional[torch.device] = None,
-    batch_chunk: int = 1,
+    batch_chunk: Optional[int] = None,
 ) -> torch.Tensor:
     """``flash_colsum`` for inputs that live in host memory; returns a host tensor.
 
     Same arguments as :func:`flash_colsum`, but ``query`` and ``key`` are CPU
     tensors (pinned memory makes the copies asynchronous).  A batched call is cut
-    along the batch into chunks of ``batch_chunk`` entries whose host-to-device
-    copies run on a second stream while the previous chunk is being computed, so
-    the call costs about the copy time of the inputs plus one chunk of compute.
+    along the batch into chunks whose host-to-device copies run on a second stream
+    while the chunk before is being computed, so the call costs about the copy time
+    of the inputs plus the compute of the last chunk.  By default the chunks shrink
+    towards the end (three quarters of what is left, then single entries): few large
+    copies, and only one entry's compute behind the last copy; ``batch_chunk`` asks
+    for uniform chunks of that many entries instead.
     Causal and single-sample calls are copied in one piece.
     """
     if query.ndim != 4 or key.ndim != 4:
@@ -477,10 +495,10 @@ def flash_colsum_host(
         out = torch.empty((B, key.shape[2]), dtype=torch.float32, device=dev)
         copy_stream.wait_stream(main)
         staged = []
-        for b0 in range(0, B, batch_chunk):
+        for b0, n in _host_chunks(B, batch_chunk):
             with torch.cuda.stream(copy_stream):
-                qd = query[b0:b0 + batch_chunk].to(dev, non_blocking=True)
-                kd = key[b0:b0 + batch_chunk].to(dev, non_blocking=True)
+                qd = query[b0:b0 + n].to(dev, non_blocking=True)
+                kd = key[b0:b0 + n].to(dev, non_blocking=True)
                 ready = torch.cuda.Event()
                 ready.record(copy_stream)
             staged.append((b0, qd, kd, ready))

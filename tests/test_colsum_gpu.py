@@ -259,7 +259,7 @@ def test_host_entry_matches_device_entry(fc):
     q, k = make_inputs(w)
     want = fc.flash_colsum(q.cuda(), k.cuda()).cpu()
     for qh, kh in ((q, k), (q.pin_memory(), k.pin_memory())):
-        for chunk in (1, 2, 8):
+        for chunk in (None, 1, 2, 8):      # None: chunks that shrink towards the end
             got = fc.flash_colsum_host(qh, kh, batch_chunk=chunk)
             assert got.device.type == "cpu"
             torch.testing.assert_close(got, want, rtol=2e-5, atol=1e-9)   # summation order differs with the chunking
