@@ -293,6 +293,26 @@ def test_calls_can_be_captured_in_a_cuda_graph(fc):
         torch.cuda.synchronize()
         assert_parity(out.cpu().numpy(), want, "graph replay")
     assert fc.device_status() == 0
+    # the few-row kernel (a cluster launch that is a programmatic dependent of the clearing kernel)
+    for wf in (Workload("graph_cls", 8, 8, 400, 400, 64, "fp16", cls_len=1, seed=82),
+               Workload("graph_decode", 1, 8, 2, 9000, 128, "bf16", is_causal=True, seed=83)):
+        q, k = (t.cuda() for t in make_inputs(wf))
+        call = lambda: fc.flash_colsum(q, k, is_causal=wf.is_causal, cls_len=wf.cls_len)  # noqa: E731
+        call()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            call()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = call()
+        want = c_oracle.colsum_c(q.cpu(), k.cpu(), is_causal=wf.is_causal, cls_len=wf.cls_len)
+        for _ in range(3):
+            out.fill_(float("nan"))
+            graph.replay()
+            torch.cuda.synchronize()
+            assert_parity(out.cpu().numpy(), want, f"graph replay {wf.name}")
+    assert fc.device_status() == 0
 
 
 def test_error_handling(fc):
