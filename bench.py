@@ -521,7 +521,9 @@ def main():
                     peer = PeerAccumulator(w5.Sk, dev, dst=0)
                     reduce_kind = ("column-pass atomics into rank 0's peer-mapped (1,131072) fp32 buffer over "
                                    "NVLink; the target alternates between two buffers, rank 0 clears the next one "
-                                   "inside its kernels, one device barrier after the adds (no collective)")
+                                   "inside its kernels; the last CTA of every rank's column pass posts a flag on rank "
+                                   "0, which alone waits (release/acquire flags in peer memory: no collective, no "
+                                   "all-to-all barrier, no kernel of its own on the other ranks)")
                 except Exception as exc:   # symmetric memory not available: keep the collective
                     peer = None
                     reduce_kind += f" (peer-memory path unavailable: {type(exc).__name__})"
@@ -540,8 +542,16 @@ def main():
                                flush_buf, barrier)
             bd = {"local_kernels_ms": max_over_ranks(sum(t_loc) / len(t_loc))}
             if peer is not None:
-                t_bar = time_steps(lambda: peer.handle.barrier(channel=0), n_b, 3, flush_buf, barrier)
-                bd["barrier_alone_ms"] = max_over_ranks(sum(t_bar) / len(t_bar))
+                # the flags of a call with nothing to add, issued by one-warp kernels (rank 0 still clears
+                # the next buffer); inside a real call they ride in the column pass
+                def nothing_to_add(target, clear_next, signals):
+                    if signals is not None:
+                        return False
+                    if clear_next is not None:
+                        clear_next.zero_()
+                    return True
+                t_bar = time_steps(lambda: peer.reduce(nothing_to_add), n_b, 3, flush_buf, barrier)
+                bd["flags_alone_ms"] = max_over_ranks(sum(t_bar) / len(t_bar))
             breakdown5 = bd
         out5 = long_step()
         torch.cuda.synchronize()

@@ -18,16 +18,24 @@ EXPORTED_SYMBOLS = (
     "fcs_set_single_pass", "fcs_single_pass_info", "fcs_single_pass_applies",
     "fcs_colsum_causal_batched", "fcs_select_topk", "fcs_select_threshold",
     "fcs_statistics_rows", "fcs_colsum_statistics", "fcs_colsum_columns", "fcs_selftest_wait_expiry",
+    "fcs_peer_post", "fcs_peer_wait", "fcs_colsum_causal_accumulate_signalled",
 )
 
 ABI_VERSION = 200   # fcs_version() of the library these argument lists were written for
 FCS_OK = 0
+FCS_ERR_UNSUPPORTED = -2
 FCS_DTYPE_FP16 = 0
 FCS_DTYPE_BF16 = 1
 
 _lib: Optional[ctypes.CDLL] = None
 
 _i, _i64, _f, _p, _sz = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
+
+
+class PeerSignals(ctypes.Structure):
+    """`FcsPeerSignals` of the header."""
+    _fields_ = [("wait_flag", _p), ("wait_value", _i), ("post", _p * 15), ("post_n", _i), ("post_value", _i),
+                ("counter", _p), ("done_flag", _p), ("done_value", _i)]
 
 
 class LibraryMissing(RuntimeError):
@@ -93,6 +101,13 @@ def load() -> ctypes.CDLL:
                                        _i64, _f, _p, _sz, _p, _p]
     lib.fcs_select_topk.restype = _i
     lib.fcs_select_topk.argtypes = [_p, _i64, _i, _i, _i, _p, _p, _p]
+    lib.fcs_colsum_causal_accumulate_signalled.restype = _i
+    lib.fcs_colsum_causal_accumulate_signalled.argtypes = [_p, _p, _p, _p, _i, _i, _i, _i, _i] + [_i64] * 4 + \
+        [_f, _i, _i, _p, _sz, _p, _p, ctypes.POINTER(PeerSignals)]
+    lib.fcs_peer_post.restype = _i
+    lib.fcs_peer_post.argtypes = [ctypes.POINTER(_p), _i, _i, _p]
+    lib.fcs_peer_wait.restype = _i
+    lib.fcs_peer_wait.argtypes = [_p, _i, _i, _p, _p]
     lib.fcs_selftest_wait_expiry.restype = _i
     lib.fcs_selftest_wait_expiry.argtypes = [_p, _p, _p, _sz, _p, ctypes.c_double, _p]
     lib.fcs_select_threshold.restype = _i

@@ -154,6 +154,20 @@ __device__ __forceinline__ void colsum_tile(uint32_t taddr, const float4* nl, in
     }
 }
 
+// Release stores at system scope, kept out of line: with a system-scope fence or release store
+// in its own body the streaming kernel's adds into another GPU's memory run markedly slower
+// (measured on the long-context shape: 0.363 against 0.289 ms for the column pass of a rank that
+// adds over NVLink, whether or not the store is ever executed).
+__device__ __noinline__ void release_store_system(int* const* flags, int n, int value) {
+    __threadfence_system();
+    for (int i = 0; i < n; ++i)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags[i]), "r"(value) : "memory");
+}
+__device__ __noinline__ void release_store_system_one(int* flag, int value) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+
 // ---------------------------------------------------------------------------
 // The streaming kernel.  tm_a: resident operand (box of 128 rows), tm_b:
 // streamed operand (box of 256 rows), tm_ext: the 16 extension columns of the
@@ -226,6 +240,30 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     // results of the kernel before this one in the stream are read
     grid_dependency_wait();
     grid_launch_dependents();
+    if (MODE != MODE_STATS && (p.sig_wait || p.sig_post_n > 0)) {
+        // head shards on several GPUs adding into one buffer: nothing is added before the owner of
+        // the buffer has said that it is clear (a flag in this GPU's memory, written over NVLink;
+        // the wait is bounded), and the owner says so for the buffer of the next call once the
+        // kernels before this one (its statistics pass cleared that buffer) have completed
+        if (threadIdx.x == 0) {
+            if (p.sig_wait) {
+                const long long t0 = clock64();
+                unsigned spins = 0;
+                while (true) {
+                    int v;
+                    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.sig_wait) : "memory");
+                    if (v >= p.sig_wait_value) break;
+                    if ((++spins & 63u) == 0u && clock64() - t0 > g_wait_limit_cycles) {
+                        if (p.status) atomicCAS(p.status, 0, FCS_STATUS_WAIT_PEER);
+                        break;
+                    }
+                    __nanosleep(200);
+                }
+            }
+            if (blockIdx.x == 0 && p.sig_post_n > 0) release_store_system(p.sig_post, p.sig_post_n, p.sig_post_value);
+        }
+        __syncthreads();
+    }
 
     // The producer and MMA warps run their loops with all 32 lanes converged (so
     // that addresses, descriptors and counters stay in uniform registers) and
@@ -699,6 +737,19 @@ colsum_stream_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     // ---------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
+    if (MODE != MODE_STATS && p.sig_done && threadIdx.x == 0) {
+        // every add of this CTA was issued before the barrier above; the last CTA to get here tells
+        // the owner of the output (release, system scope) that this GPU's share of the call is in.
+        // One system-scope fence per grid, by that last CTA: a system-scope fence in every CTA cost
+        // 67 us on the long-context shape (they are served one after the other); the CTAs hand
+        // their writes on to it through device-scope fences and the counter.
+        __threadfence();
+        const int arrived = atomicAdd(p.sig_counter, 1);
+        if (arrived == (int)gridDim.x - 1) {
+            *p.sig_counter = 0;
+            release_store_system_one(p.sig_done, p.sig_done_value);
+        }
+    }
     if (warp == MMA_WARP) {
         if (*abort_flag) __nanosleep(1000000);   // let copies and MMAs in flight land
         tc_fence_after();
@@ -735,6 +786,40 @@ __global__ void merge_stats_kernel(const Problem p) {
         uint4* er = reinterpret_cast<uint4*>(p.ext) + (bh * p.lse_rows + q_abs) * 2;
         er[0] = e0;
         er[1] = e1;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Flags between the GPUs of a node (peer-mapped memory), for callers that order their
+// kernels across ranks without a collective: a release store per flag, and a bounded wait
+// until every flag has reached a value.
+// ---------------------------------------------------------------------------
+constexpr int PEER_FLAGS_MAX = 16;
+struct PeerFlagPointers { int* p[PEER_FLAGS_MAX]; };
+
+__global__ void peer_post_kernel(const PeerFlagPointers flags, int n, int value) {
+    if ((int)threadIdx.x < n) {
+        // everything the kernels before this one in the stream wrote (to any GPU) is visible to
+        // whoever reads this value with an acquire load
+        __threadfence_system();
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.p[threadIdx.x]), "r"(value) : "memory");
+    }
+}
+
+__global__ void peer_wait_kernel(const int* flags, int n, int value, int* status) {
+    if ((int)threadIdx.x < n) {
+        const long long t0 = clock64();
+        unsigned spins = 0;
+        while (true) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
+            if (v >= value) break;
+            if ((++spins & 63u) == 0u && clock64() - t0 > g_wait_limit_cycles) {
+                if (status) atomicCAS(status, 0, FCS_STATUS_WAIT_PEER);
+                break;
+            }
+            __nanosleep(100);
+        }
     }
 }
 
@@ -1099,7 +1184,8 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
                        int64_t ksh, int64_t kss, float scale, int causal, int k_past, int cls_n, int h_norm,
                        void* workspace, size_t workspace_bytes, int* status, void* stream_v,
                        bool clear_out = true, int passes = PASSES_BOTH, float* shared_lse = nullptr,
-                       long long norm_rows = 0, float* clear_extra = nullptr, long long clear_extra_n = 0) {
+                       long long norm_rows = 0, float* clear_extra = nullptr, long long clear_extra_n = 0,
+                       const FcsPeerSignals* sig = nullptr) {
     // passes: both, or one of the two for work split over devices (non-causal only) --
     // PASSES_STATS writes -(log-sum-exp + log2(h_norm * norm_rows)) of the given query rows to
     // `shared_lse`; PASSES_COLUMNS takes that vector for ALL query rows and the given keys.
@@ -1134,6 +1220,9 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+    if (sig && passes == PASSES_BOTH && smallq_fits(Sq, Sk, D, B * H, num_sms()))
+        return fail(FCS_ERR_UNSUPPORTED, "calls with at most four query rows take the few-row kernel, which does not "
+                                         "signal other GPUs; order them with a barrier");
     if (passes == PASSES_BOTH && smallq_fits(Sq, Sk, D, B * H, num_sms())) {
         // reported as a call whose statistics and merge passes take no time
         PassTimers* tms = g_profiling ? timers_for_current_device() : nullptr;
@@ -1258,6 +1347,16 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     // a query axis of at most 128 rows fills half a streamed block: the MMAs need N = 128 only
     if (Sq <= BLOCK / 2)
         p.idesc = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((BLOCK / 2) >> 3) << 17);
+    if (sig) {   // the column pass orders itself against the other GPUs of a head-sharded call
+        p.sig_wait = sig->wait_flag;
+        p.sig_wait_value = sig->wait_value;
+        p.sig_post_n = sig->post_n;
+        p.sig_post_value = sig->post_value;
+        for (int i = 0; i < sig->post_n; ++i) p.sig_post[i] = sig->post[i];
+        p.sig_counter = sig->counter;
+        p.sig_done = sig->done_flag;
+        p.sig_done_value = sig->done_value;
+    }
     const bool head_major = use_ext && p.col_interleave == COL_HEAD_MAJOR;
     if (head_major && p.col_combine && p.NQB == 2)
         e = (DK == 64) ? launch_stream<64, MODE_COLSUM_EXT_SHORT2_COMBINE>(tk_a, tq_b, text, p, grid2, stream, chained)
@@ -1488,6 +1587,33 @@ int fcs_select_topk(const float* colsum, int64_t ld, int B, int S, int k, int* i
     return FCS_OK;
 }
 
+int fcs_peer_post(int* const* flags, int n_flags, int value, void* stream) {
+    fcs::g_err[0] = 0;
+    if (!flags || n_flags <= 0 || n_flags > fcs::PEER_FLAGS_MAX)
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "1 to %d flag pointers are expected, got %d", fcs::PEER_FLAGS_MAX, n_flags);
+    fcs::PeerFlagPointers fp;
+    memset(&fp, 0, sizeof(fp));
+    for (int i = 0; i < n_flags; ++i) {
+        if (!flags[i] || reinterpret_cast<uintptr_t>(flags[i]) % 4)
+            return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "flag %d is NULL or misaligned", i);
+        fp.p[i] = flags[i];
+    }
+    fcs::peer_post_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(fp, n_flags, value);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fcs::fail(FCS_ERR_CUDA, "flag post launch failed: %s", cudaGetErrorString(e));
+    return FCS_OK;
+}
+
+int fcs_peer_wait(const int* flags, int n_flags, int value, int* status, void* stream) {
+    fcs::g_err[0] = 0;
+    if (!flags || n_flags <= 0 || n_flags > 32 || reinterpret_cast<uintptr_t>(flags) % 4)
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "1 to 32 consecutive, aligned flags are expected, got %d", n_flags);
+    fcs::peer_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flags, n_flags, value, status);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fcs::fail(FCS_ERR_CUDA, "flag wait launch failed: %s", cudaGetErrorString(e));
+    return FCS_OK;
+}
+
 int fcs_selftest_wait_expiry(const void* q, const void* k, void* workspace, size_t workspace_bytes, int* status,
                               double limit_seconds, void* stream_v) {
     fcs::g_err[0] = 0;
@@ -1591,6 +1717,23 @@ int fcs_colsum_causal_accumulate_and_clear(const void* q, const void* k, float* 
                             q_stride_s, k_stride_h * H, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm,
                             workspace, workspace_bytes, status, stream, /*clear_out=*/false, fcs::PASSES_BOTH, nullptr,
                             0, clear_buf, clear_buf ? (long long)k_len : 0);
+}
+
+int fcs_colsum_causal_accumulate_signalled(const void* q, const void* k, float* out, float* clear_buf, int H,
+                                           int q_len, int k_len, int D, int dtype, int64_t q_stride_h,
+                                           int64_t q_stride_s, int64_t k_stride_h, int64_t k_stride_s, float scale,
+                                           int k_past, int h_norm, void* workspace, size_t workspace_bytes,
+                                           int* status, void* stream, const FcsPeerSignals* signals) {
+    fcs::g_err[0] = 0;
+    if (!signals) return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "signals is NULL");
+    if (signals->post_n < 0 || signals->post_n > 15)
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "at most 15 flags can be posted, got %d", signals->post_n);
+    if (signals->done_flag && !signals->counter)
+        return fcs::fail(FCS_ERR_INVALID_ARGUMENT, "a done flag needs a counter");
+    return fcs::colsum_impl(q, k, out, k_len, 1, H, q_len, k_len, D, dtype, q_stride_h * H, q_stride_h,
+                            q_stride_s, k_stride_h * H, k_stride_h, k_stride_s, scale, 1, k_past, -1, h_norm,
+                            workspace, workspace_bytes, status, stream, /*clear_out=*/false, fcs::PASSES_BOTH, nullptr,
+                            0, clear_buf, clear_buf ? (long long)k_len : 0, signals);
 }
 
 }  // extern "C"

@@ -64,6 +64,14 @@ struct Problem {
     long long out_ld;
     int* status;
     uint32_t idesc;
+    // Ordering against other GPUs, inside the column pass of a head-sharded call (all NULL / 0 otherwise):
+    const int* sig_wait;      // this CTA's first thread waits (bounded) until *sig_wait >= sig_wait_value before anything is added
+    int sig_wait_value;
+    int* sig_post[15];        // CTA 0 stores sig_post_value to these flags (release, system scope) once the kernel before has completed
+    int sig_post_n, sig_post_value;
+    int* sig_counter;         // CTAs that have finished; the last one resets it and stores sig_done_value to *sig_done
+    int* sig_done;
+    int sig_done_value;
     int withhold_loads; // self-test only: the producer issues no copies, so that the bounded waits run out
 };
 

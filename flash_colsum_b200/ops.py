@@ -10,6 +10,7 @@ the library is missing the call raises.
 from __future__ import annotations
 
 import contextlib
+import ctypes
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -169,20 +170,23 @@ def _flash_colsum_non_batched(Q: torch.Tensor, K: torch.Tensor, scale: float, CL
 
 def _flash_colsum_causal(Q: torch.Tensor, K: torch.Tensor, scale: float, K_past: Optional[int] = None,
                          h_norm: int = 0, accumulate_into: Optional[torch.Tensor] = None,
-                         clear_next: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         clear_next: Optional[torch.Tensor] = None, signals=None) -> Optional[torch.Tensor]:
     """(1, K_len) fp32.  Counterpart of kernel_causal.py:94.
 
     With ``accumulate_into`` (fp32, contiguous, K_len elements, already cleared by
     the caller; may be a peer-mapped tensor of another GPU) the result is added
     into that tensor instead of a fresh one; ``clear_next`` (same form, local memory)
-    is zeroed by the same kernels, for a target that alternates between two buffers.
+    is zeroed by the same kernels, for a target that alternates between two buffers;
+    ``signals`` (a ``_cabi.PeerSignals``) makes the column pass order itself against the
+    other GPUs -- the call then returns None, having launched nothing, when its shape takes
+    a kernel that cannot do so (at most four query rows).
     """
     lib = _cabi.load()
     Q, K, code = _prepare(Q, K)
     _, H, Q_len, D = Q.shape
     K_len = K.shape[2]
     with _on_device(Q.device):
-        extra = ()
+        head, tail = (), ()
         if accumulate_into is None:
             out = torch.empty((1, K_len), device=Q.device, dtype=torch.float32)
             entry = lib.fcs_colsum_causal
@@ -192,16 +196,23 @@ def _flash_colsum_causal(Q: torch.Tensor, K: torch.Tensor, scale: float, K_past:
                 if t.dtype != torch.float32 or t.numel() != K_len or not t.is_contiguous():
                     raise ValueError("accumulate_into / clear_next must be contiguous fp32 tensors with K_len elements")
             entry = lib.fcs_colsum_causal_accumulate
-            if clear_next is not None:
+            if signals is not None:
+                entry = lib.fcs_colsum_causal_accumulate_signalled
+                head = (0 if clear_next is None else clear_next.data_ptr(),)
+                tail = (ctypes.byref(signals),)
+            elif clear_next is not None:
                 entry = lib.fcs_colsum_causal_accumulate_and_clear
-                extra = (clear_next.data_ptr(),)
+                head = (clear_next.data_ptr(),)
         ws = _workspace(lib, Q.device, 1, H, Q_len, K_len, D, True, -1 if K_past is None else int(K_past))
-        _check(entry(
-            Q.data_ptr(), K.data_ptr(), out.data_ptr(), *extra, H, Q_len, K_len, D, code,
+        rc = entry(
+            Q.data_ptr(), K.data_ptr(), out.data_ptr(), *head, H, Q_len, K_len, D, code,
             Q.stride(1), Q.stride(2), K.stride(1), K.stride(2),
             float(scale), -1 if K_past is None else int(K_past), int(h_norm),
             ws.data_ptr(), ws.numel(),
-            _status_word(Q.device).data_ptr(), _raw_stream(Q.device)))
+            _status_word(Q.device).data_ptr(), _raw_stream(Q.device), *tail)
+        if signals is not None and rc == _cabi.FCS_ERR_UNSUPPORTED:
+            return None
+        _check(rc)
     return out
 
 

@@ -33,45 +33,113 @@ def shard_range(n: int, world_size: int, rank: int) -> Tuple[int, int]:
 
 
 class PeerAccumulator:
-    """Two fp32 ``(1, S_k)`` buffers per rank in symmetric (peer-mapped) memory.
+    """Two fp32 ``(1, S_k)`` buffers and a few flags per rank in symmetric (peer-mapped) memory.
 
     Used to fold the reduce of the head-sharded causal call into the kernels: every
     rank's column pass adds its per-key sums straight into a buffer of rank ``dst``
-    over NVLink (plain system-scope atomic adds to a peer address, no multicast), and
-    one device-side barrier after the launches tells rank ``dst`` that all adds have
-    landed.  Calls alternate between the two buffers: while call n adds into one,
-    rank ``dst`` zeroes the other inside its own kernels (no clearing kernel, no
-    barrier before the adds) -- nobody adds into it before passing the barrier of
-    call n, which rank ``dst`` enters after those kernels.  One process per GPU; the
-    constructor is a collective over ``group``.
+    over NVLink (plain system-scope atomic adds to a peer address, no multicast); the last
+    CTA of that pass then stores a flag on rank ``dst`` (release, system scope), and rank
+    ``dst`` waits for the flags of all ranks -- a bounded wait in a one-warp kernel -- and has
+    the sum.  No collective and no all-to-all barrier: only rank ``dst`` waits for the others.
+    Calls alternate between the two buffers: while call n adds into one, rank ``dst`` zeroes
+    the other inside its statistics pass and its column pass then tells every rank so (a second
+    flag); a rank's column pass of call n + 1 adds nothing before it has seen that flag of
+    call n.  One process per GPU; the constructor is a collective over ``group``.
     """
+
+    DONE, CLEARED = 0, 32     # int32 slots of the flag array
 
     def __init__(self, k_len: int, device: torch.device, group=None, dst: int = 0):
         # peer mappings only: keep NVLink multicast objects out of it
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import ctypes
         import torch.distributed._symmetric_memory as symm_mem
+        from . import _cabi
         group = group if group is not None else dist.group.WORLD
         self.k_len = int(k_len)
         self.dst = int(dst)
         self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > 16:
+            raise ValueError("the peer-memory reduce is built for the GPUs of one node (at most 16 ranks)")
         self.local = symm_mem.empty((2, self.k_len), dtype=torch.float32, device=device)
         self.handle = symm_mem.rendezvous(self.local, group)
         both = self.handle.get_buffer(self.dst, (2, self.k_len), torch.float32)
         self.targets = (both[0], both[1])
         self.local.zero_()
+        self.flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
+        self.flag_handle = symm_mem.rendezvous(self.flags, group)
+        self.flags.zero_()
+        # the CTA counter of the column pass is local and hot: ordinary device memory (atomics on the
+        # peer-mapped allocation cost ~0.45 us each, one per CTA)
+        self._counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self._lib = _cabi.load()
+        self._cabi = _cabi
+        self._device = device
+        self._others = [r for r in range(self.world) if r != self.dst]
+        flags_on_dst = self.flag_handle.get_buffer(self.dst, (64,), torch.int32)
+        self._keep = [flags_on_dst]
+        if self.rank == self.dst:
+            peers = [self.flag_handle.get_buffer(r, (64,), torch.int32) for r in self._others]
+            self._keep += peers
+            self._cleared_ptrs = [t.data_ptr() + 4 * self.CLEARED for t in peers]
+            self._post = (ctypes.c_void_p * max(1, len(peers)))(*self._cleared_ptrs)
+        else:
+            self._done_ptr = flags_on_dst.data_ptr() + 4 * (self.DONE + self.rank)
+            self._post = (ctypes.c_void_p * 1)(self._done_ptr)
+        self.calls = 0
         self.parity = 0
         torch.cuda.synchronize(device)
-        self.handle.barrier(channel=0)     # every rank's buffers are clear before the first add
+        self.handle.barrier(channel=0)     # every rank's buffers and flags are clear before the first add
+        torch.cuda.synchronize(device)
 
-    def reduce(self, launch: Callable[[torch.Tensor, Optional[torch.Tensor]], None]) -> torch.Tensor:
-        """Run ``launch(target, clear_next)`` on every rank, then one barrier; rank ``dst``
-        gets the summed result (a view of its local buffer, valid until the call after the
-        next one), the others a stale buffer.  ``clear_next`` is the buffer of the next call
-        on rank ``dst`` (to be zeroed by the launched kernels) and None elsewhere."""
-        p = self.parity
-        clear_next = self.local[p ^ 1] if self.rank == self.dst else None
-        launch(self.targets[p], clear_next)
-        self.handle.barrier(channel=p)
+    def _signals(self, n: int):
+        sig = self._cabi.PeerSignals()
+        if self.rank == self.dst:
+            for i, ptr in enumerate(self._cleared_ptrs):
+                sig.post[i] = ptr
+            sig.post_n, sig.post_value = len(self._cleared_ptrs), n
+        else:
+            sig.wait_flag = self.flags.data_ptr() + 4 * self.CLEARED
+            sig.wait_value = n - 1
+            sig.counter = self._counter.data_ptr()
+            sig.done_flag, sig.done_value = self._done_ptr, n
+        return sig
+
+    def reduce(self, launch: Callable) -> torch.Tensor:
+        """Run ``launch(target, clear_next, signals)`` on every rank; rank ``dst`` gets the summed
+        result (a view of its local buffer, valid until the call after the next one), the others a
+        stale buffer.  ``clear_next`` is the buffer of the next call on rank ``dst`` (to be zeroed
+        by the launched kernels) and None elsewhere.  ``launch`` returns False when its kernels
+        cannot take the signals (it then ran them without, between the same flags issued by
+        one-warp kernels)."""
+        from . import ops
+        self.calls += 1
+        n, p = self.calls, self.parity
+        lib, dev = self._lib, self._device
+        is_dst = self.rank == self.dst
+        with ops._on_device(dev):
+            stream = ops._raw_stream(dev)
+            status = ops._status_word(dev).data_ptr()
+            in_kernel = launch(self.targets[p], self.local[p ^ 1] if is_dst else None, self._signals(n))
+            if not in_kernel:
+                # the same protocol by separate one-warp kernels around the launch
+                if not is_dst:
+                    ops._check(lib.fcs_peer_wait(self.flags.data_ptr() + 4 * self.CLEARED, 1, n - 1, status, stream))
+                launch(self.targets[p], self.local[p ^ 1] if is_dst else None, None)
+                if self._others or not is_dst:
+                    if is_dst and self._others:
+                        ops._check(lib.fcs_peer_post(self._post, len(self._others), n, stream))
+                    elif not is_dst:
+                        ops._check(lib.fcs_peer_post(self._post, 1, n, stream))
+            if is_dst and self._others:
+                lo, hi = min(self._others), max(self._others)
+                base = self.flags.data_ptr() + 4 * self.DONE
+                # (rank dst's own slot is never posted: wait on the slots before and after it)
+                if lo < self.dst:
+                    ops._check(lib.fcs_peer_wait(base + 4 * lo, self.dst - lo, n, status, stream))
+                if hi > self.dst:
+                    ops._check(lib.fcs_peer_wait(base + 4 * (self.dst + 1), hi - self.dst, n, status, stream))
         self.parity = p ^ 1
         return self.local[p:p + 1]
 
@@ -127,12 +195,16 @@ def flash_colsum_head_sharded(
         if peer.k_len != key_shard.shape[2]:
             raise ValueError(f"peer buffer holds {peer.k_len} keys, the call has {key_shard.shape[2]}")
 
-        def launch(target: torch.Tensor, clear_next: Optional[torch.Tensor]) -> None:
+        def launch(target: torch.Tensor, clear_next: Optional[torch.Tensor], signals) -> bool:
             if h_local > 0:
-                ops._flash_colsum_causal(query_shard, key_shard, scale, h_norm=h_total, accumulate_into=target,
-                                         clear_next=clear_next)
-            elif clear_next is not None:
+                out = ops._flash_colsum_causal(query_shard, key_shard, scale, h_norm=h_total, accumulate_into=target,
+                                               clear_next=clear_next, signals=signals)
+                return out is not None
+            if signals is not None:
+                return False          # no kernels of this rank to carry the flags
+            if clear_next is not None:
                 clear_next.zero_()
+            return True
 
         return peer.reduce(launch)
     if h_local == 0:

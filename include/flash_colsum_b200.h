@@ -52,6 +52,7 @@ extern "C" {
 #define FCS_STATUS_WAIT_PRODUCER 1
 #define FCS_STATUS_WAIT_MMA 2
 #define FCS_STATUS_WAIT_CONSUMER 3
+#define FCS_STATUS_WAIT_PEER 4
 
 /* Library version, as major * 10000 + minor * 100 + patch. */
 int fcs_version(void);
@@ -174,6 +175,56 @@ int fcs_colsum_causal_accumulate_and_clear(const void *q, const void *k, float *
                                            int64_t k_stride_h, int64_t k_stride_s,
                                            float scale, int k_past, int h_norm,
                                            void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+/*
+ * fcs_colsum_causal_accumulate_and_clear whose column pass orders itself against the other GPUs
+ * of a head-sharded call through flags in peer-mapped memory, so that the ranks need no barrier
+ * kernel around it (one process per GPU; no counterpart in the reference):
+ *   wait_flag / wait_value   (ranks that do not own `out`) local flag; nothing is added into `out`
+ *                            before it has reached wait_value -- the owner stores the number of
+ *                            the call during which it cleared the buffer this call adds into.
+ *                            The wait is bounded (FCS_STATUS_WAIT_PEER on expiry).
+ *   post / post_n / post_value  (the owner) flags on the other ranks, stored once the owner's
+ *                            statistics pass -- which clears `clear_buf`, the target of the next
+ *                            call -- has completed.
+ *   counter / done_flag / done_value  (ranks that do not own `out`) `counter`: a local int, zero
+ *                            between calls; the last CTA of the column pass stores done_value to
+ *                            done_flag (on the owner) with release semantics at system scope: the
+ *                            owner waits for it with fcs_peer_wait and then holds this rank's share.
+ * Unused parts are NULL / 0.  Calls with at most four query rows (the few-row kernel) are
+ * refused with FCS_ERR_UNSUPPORTED: order those with a barrier.
+ */
+typedef struct FcsPeerSignals {
+    const int *wait_flag;
+    int wait_value;
+    int *post[15];
+    int post_n;
+    int post_value;
+    int *counter;
+    int *done_flag;
+    int done_value;
+} FcsPeerSignals;
+int fcs_colsum_causal_accumulate_signalled(const void *q, const void *k, float *out, float *clear_buf,
+                                           int H, int q_len, int k_len, int D, int dtype,
+                                           int64_t q_stride_h, int64_t q_stride_s,
+                                           int64_t k_stride_h, int64_t k_stride_s,
+                                           float scale, int k_past, int h_norm,
+                                           void *workspace, size_t workspace_bytes, int *status, void *stream,
+                                           const FcsPeerSignals *signals);
+
+/*
+ * Flags between the GPUs of a node, for ordering the calls above across ranks without a
+ * collective (one process per GPU; the flags live in peer-mapped memory).  fcs_peer_post
+ * stores `value` to each of the n_flags (at most 16) addresses with release semantics at system
+ * scope, on `stream`: everything the kernels before it in that stream wrote -- adds into another
+ * GPU's buffer included -- is visible to a rank that has seen the value.  fcs_peer_wait holds
+ * `stream` until each of the n_flags (at most 32) consecutive ints at `flags` (local memory) is
+ * at least `value`, reading with acquire semantics; the wait is bounded (about two seconds), after
+ * which FCS_STATUS_WAIT_PEER is stored to *status and the stream moves on.  A rank that waits
+ * never runs on the same GPU as the rank it waits for.  No counterpart in the reference.
+ */
+int fcs_peer_post(int *const *flags, int n_flags, int value, void *stream);
+int fcs_peer_wait(const int *flags, int n_flags, int value, int *status, void *stream);
 
 /*
  * Batched non-causal column mean for callers that cannot give the library a

@@ -47,6 +47,21 @@ def _worker(rank, world, port, results):
         outs = [flash_colsum_head_sharded(q, k, H, is_causal=True, peer=peer).clone() for _ in range(3)]
         torch.cuda.synchronize()
         assert flash_colsum_b200.device_status() == 0
+        # the same accumulator with calls whose kernels cannot carry the flags themselves: two decode
+        # queries (the few-row kernel), and one head over two ranks (a rank with nothing to launch);
+        # in between, ordinary calls again
+        wf = Workload("f", 1, H, 2, 3000, 128, "bf16", is_causal=True, seed=18)
+        qf, kf = (t.to(dev) for t in make_inputs(wf, heads=(lo, hi)))
+        w1 = Workload("o", 1, 1, 200, 3000, 128, "bf16", is_causal=True, seed=19)
+        l1, h1 = shard_range(1, world, rank)
+        q1, k1 = (t.to(dev) for t in make_inputs(w1, heads=(l1, h1)))
+        mixed = []
+        for _ in range(2):
+            mixed.append(flash_colsum_head_sharded(qf, kf, H, is_causal=True, peer=peer).clone())
+            mixed.append(flash_colsum_head_sharded(q, k, H, is_causal=True, peer=peer).clone())
+            mixed.append(flash_colsum_head_sharded(q1, k1, 1, is_causal=True, peer=peer).clone())
+        torch.cuda.synchronize()
+        assert flash_colsum_b200.device_status() == 0
         # one single-head sample split by work: query rows for the statistics, keys for the columns
         from flash_colsum_b200.sharded import flash_colsum_work_sharded
         w2 = Workload("w", 1, 1, 3000, 3000, 64, "fp16", seed=23)
@@ -54,7 +69,8 @@ def _worker(rank, world, port, results):
         out_work = flash_colsum_work_sharded(q2, k2)
         torch.cuda.synchronize()
         assert flash_colsum_b200.device_status() == 0
-        results[rank] = (out_nccl.cpu().numpy(), [o.cpu().numpy() for o in outs], out_work.cpu().numpy())
+        results[rank] = (out_nccl.cpu().numpy(), [o.cpu().numpy() for o in outs], out_work.cpu().numpy(),
+                         [o.cpu().numpy() for o in mixed])
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -78,6 +94,14 @@ def test_two_gpus_match_unsharded():
     for o in results[0][1]:          # the peer-memory reduce lands on rank 0
         rel, mx = parity_errors(o, want)
         assert rel <= 1e-3 and mx <= 1e-3, ("peer", rel, mx)
+    wants = [c_oracle.colsum_c(*make_inputs(Workload("f", 1, 6, 2, 3000, 128, "bf16", is_causal=True, seed=18)),
+                               is_causal=True),
+             want,
+             c_oracle.colsum_c(*make_inputs(Workload("o", 1, 1, 200, 3000, 128, "bf16", is_causal=True, seed=19)),
+                               is_causal=True)]
+    for i, o in enumerate(results[0][3]):   # few rows / ordinary / a rank without heads, twice over
+        rel, mx = parity_errors(o, wants[i % 3])
+        assert rel <= 1e-3 and mx <= 1e-3, ("mixed", i, rel, mx)
     q2, k2 = make_inputs(Workload("w", 1, 1, 3000, 3000, 64, "fp16", seed=23))
     want2 = c_oracle.colsum_c(q2, k2)
     for r in (0, 1):                 # the work split leaves the whole result on every rank
