@@ -99,6 +99,25 @@ def test_argument_errors_of_the_pruning_and_self_test_entries():
     assert "limit_seconds" in _cabi.last_error()
     assert lib.fcs_colsum_causal_accumulate_and_clear(None, None, None, None, 1, 1, 1, 64, 0, 64, 64, 64, 64, 1.0, -1,
                                                       0, None, 0, None, None) < 0
+    # flags between GPUs: pointer counts and alignment are checked before any launch
+    assert lib.fcs_peer_post(None, 1, 1, None) == -1
+    ptrs = (ctypes.c_void_p * 1)(addr(idx) + 2)
+    assert lib.fcs_peer_post(ptrs, 1, 1, None) == -1 and "misaligned" in _cabi.last_error()
+    assert lib.fcs_peer_post(ptrs, 17, 1, None) == -1
+    assert lib.fcs_peer_wait(None, 1, 1, None, None) == -1
+    assert lib.fcs_peer_wait(addr(idx), 33, 1, None, None) == -1
+    sig = _cabi.PeerSignals()
+    sig.post_n = 16
+    assert lib.fcs_colsum_causal_accumulate_signalled(None, None, None, None, 1, 1, 1, 64, 0, 64, 64, 64, 64, 1.0, -1,
+                                                      0, None, 0, None, None, ctypes.byref(sig)) == -1
+    assert "15" in _cabi.last_error()
+    sig.post_n = 0
+    sig.done_flag = addr(idx)
+    assert lib.fcs_colsum_causal_accumulate_signalled(None, None, None, None, 1, 1, 1, 64, 0, 64, 64, 64, 64, 1.0, -1,
+                                                      0, None, 0, None, None, ctypes.byref(sig)) == -1
+    assert "counter" in _cabi.last_error()
+    assert lib.fcs_colsum_causal_accumulate_signalled(None, None, None, None, 1, 1, 1, 64, 0, 64, 64, 64, 64, 1.0, -1,
+                                                      0, None, 0, None, None, None) == -1
     pkg = os.path.join(ROOT, "flash_colsum_b200")
     for dirpath, _, files in os.walk(pkg):
         for fn in files:
