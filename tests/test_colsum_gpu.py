@@ -729,3 +729,40 @@ def test_agrees_with_the_reference_kernels_where_they_are_exact(fc):
         torch.cuda.synchronize()
         rel = float(((ours - theirs).norm() / ours.norm()).item())
         assert theirs.shape == ours.shape and rel <= 3e-3, (B, H, Sq, Sk, causal, rel)
+
+
+def test_signalled_accumulate_entry_posts_its_flags(fc):
+    """The accumulate entry whose column pass carries the flags of a head-sharded call, on one GPU
+    with every flag in local memory: the wait is already satisfied (nothing on this GPU waits for
+    another kernel), the owner's "clear" flags and the "share is in" flag are stored, the counter
+    returns to zero, the sum is right -- and a few-row call is refused so that its caller falls
+    back to flags around the call."""
+    from flash_colsum_b200 import _cabi, ops
+    w = Workload("sig", 1, 4, 300, 2500, 128, "bf16", is_causal=True, seed=55)
+    q, k = make_inputs(w)
+    qd, kd = q.cuda(), k.cuda()
+    want = c_oracle.colsum_c(q, k, is_causal=True)
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    target = torch.zeros(w.Sk, device="cuda")
+    nxt = torch.full((w.Sk,), 3.0, device="cuda")
+    base = flags.data_ptr()
+    # first two heads as "the owner" (posts two clear flags, clears the next buffer) ...
+    sig = _cabi.PeerSignals()
+    sig.post[0], sig.post[1] = base + 4, base + 8
+    sig.post_n, sig.post_value = 2, 7
+    assert ops._flash_colsum_causal(qd[:, :2], kd[:, :2], 1.0 / 128 ** 0.5, h_norm=4, accumulate_into=target,
+                                    clear_next=nxt, signals=sig) is not None
+    # ... the other two as "another rank" (waits for a flag that is already there, reports completion)
+    sig = _cabi.PeerSignals()
+    flags[0] = 5
+    sig.wait_flag, sig.wait_value = base, 5
+    sig.counter, sig.done_flag, sig.done_value = base + 16, base + 12, 9
+    assert ops._flash_colsum_causal(qd[:, 2:], kd[:, 2:], 1.0 / 128 ** 0.5, h_norm=4, accumulate_into=target,
+                                    signals=sig) is not None
+    torch.cuda.synchronize()
+    assert fc.device_status() == 0
+    assert flags.tolist()[:5] == [5, 7, 7, 9, 0]
+    assert float(nxt.abs().max().item()) == 0.0
+    assert_parity(target.cpu().numpy()[None, :], want, "signalled accumulate")
+    # two decode queries: the few-row kernel cannot carry the flags
+    assert ops._flash_colsum_causal(qd[:, :, :2], kd, 1.0 / 128 ** 0.5, accumulate_into=target, signals=sig) is None
