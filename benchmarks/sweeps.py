@@ -8,8 +8,8 @@ Shapes and dtype follow the reference's ``sweep_all_unified``
 (benchmarks/benchmark_colsum.py:289-424 and 757-801): fp16;
 batched non-causal H=16 S=1024 D=64 over the batch size; single-sample non-causal
 H=16 D=64 over the sequence length; causal H=32 Q=128 D=128 over the key length.
-Latency is reported two ways: per call by CUDA events over back-to-back calls
-(device time), and the reference's way -- host clock around call + synchronize
+Latency is reported two ways: per call by CUDA events over back-to-back calls (device time; the median of five
+groups of calls), and the reference's way -- host clock around call + synchronize
 (benchmark_colsum.py:42-56).  Peak memory is ``torch.cuda.max_memory_allocated``
 around one call (benchmark_colsum.py:59-71), inputs included.  One CSV row per point.
 
@@ -72,16 +72,23 @@ def load_reference():
 
 
 def time_device(call, warmup, iters):
+    """Device time of one call: back-to-back calls in up to five groups, each group bracketed by CUDA
+    events, the median of the groups' means (one mean over all calls would carry any one-off stall of
+    the launching thread that lets the queue run dry)."""
     for _ in range(warmup):
         call()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        out = call()
-    e1.record()
+    groups = min(5, iters)
+    per = max(1, iters // groups)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(groups + 1)]
+    marks[0].record()
+    for g in range(groups):
+        for _ in range(per):
+            out = call()
+        marks[g + 1].record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters, out
+    means = sorted(marks[g].elapsed_time(marks[g + 1]) / per for g in range(groups))
+    return means[groups // 2], out
 
 
 def naive_in_pieces(ref_naive, q, k, causal, cls_len):
