@@ -406,6 +406,41 @@ def test_headline_workloads_full_size(fc, name, chunk):
         torch.backends.cuda.matmul.allow_tf32 = prev
 
 
+def test_operands_of_more_than_two_to_the_31_elements(fc):
+    """Batch sizes whose operands pass 2^31 elements (4.8 GB each): every call form agrees with
+    the same call on 256 batch entries at a time, and the last entries -- past the 32-bit mark
+    -- with the fp32 materialising evaluation."""
+    if torch.cuda.mem_get_info()[0] < (14 << 30):
+        pytest.skip("needs 14 GB of free device memory")
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        B, H, S, D = 2304, 16, 1024, 64
+        g = torch.Generator(device="cuda").manual_seed(5)
+        q = torch.randn(B, H, S, D, generator=g, device="cuda", dtype=torch.float16)
+        k = torch.randn(B, H, S, D, generator=g, device="cuda", dtype=torch.float16)
+        assert q.numel() > 2 ** 31
+        forms = {
+            "all rows": lambda a, b: fc.flash_colsum(a, b),
+            "cls prefix": lambda a, b: fc.flash_colsum(a, b, cls_len=1),
+            "causal suffix": lambda a, b: fc.flash_colsum_causal(a[:, :, -128:], b),
+        }
+        for name, call in forms.items():
+            full = call(q, k)
+            parts = torch.cat([call(q[b:b + 256], k[b:b + 256]) for b in range(0, B, 256)], dim=0)
+            assert fc.device_status() == 0
+            rel = float((full - parts).norm() / parts.norm())
+            assert rel <= 1e-4, (name, rel)
+        tail = slice(B - 2, B)
+        for name, causal, cls_len, rows in (("all rows", False, None, slice(None)), ("cls prefix", False, 1, slice(None)),
+                                            ("causal suffix", True, None, slice(S - 128, S))):
+            got = forms[name](q, k)[tail].cpu().numpy()
+            want = _torch_fp32_reference(q[tail, :, rows], k[tail], causal, cls_len, 4)
+            assert_parity(got, want, name)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
 def test_long_inputs_take_the_interleaved_column_schedule(fc):
     """More than 300 000 query rows: the column pass deals (b, h, key tile) chunks round-robin.
     Non-causal with ragged sizes, and causal with more than one batch entry."""
