@@ -16,12 +16,13 @@ EXPORTED_SYMBOLS = (
     "fcs_set_profiling", "fcs_last_pass_ms", "fcs_plan_info",
     "fcs_colsum_batched_static_scratch", "fcs_colsum_causal_accumulate", "fcs_colsum_causal_accumulate_and_clear",
     "fcs_set_single_pass", "fcs_single_pass_info", "fcs_single_pass_applies",
+    "fcs_set_short_fused", "fcs_short_fused_applies",
     "fcs_colsum_causal_batched", "fcs_select_topk", "fcs_select_threshold",
     "fcs_statistics_rows", "fcs_colsum_statistics", "fcs_colsum_columns", "fcs_selftest_wait_expiry",
     "fcs_peer_post", "fcs_peer_wait", "fcs_colsum_causal_accumulate_signalled",
 )
 
-ABI_VERSION = 200   # fcs_version() of the library these argument lists were written for
+ABI_VERSION = 201   # fcs_version() of the library these argument lists were written for
 FCS_OK = 0
 FCS_ERR_UNSUPPORTED = -2
 FCS_DTYPE_FP16 = 0
@@ -128,6 +129,10 @@ def load() -> ctypes.CDLL:
     lib.fcs_single_pass_applies.argtypes = [_i, _i, _i, _i, _i, _i]
     lib.fcs_single_pass_info.restype = _i
     lib.fcs_single_pass_info.argtypes = [_i, ctypes.POINTER(_i), ctypes.POINTER(_i)]
+    lib.fcs_set_short_fused.restype = _i
+    lib.fcs_set_short_fused.argtypes = [_i]
+    lib.fcs_short_fused_applies.restype = _i
+    lib.fcs_short_fused_applies.argtypes = [_i, _i, _i, _i, _i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]
     lib.fcs_last_pass_ms.restype = _i
     lib.fcs_last_pass_ms.argtypes = [_p, _p, _p]
     lib.fcs_plan_info.restype = _i
@@ -167,6 +172,28 @@ def set_single_pass(mode: int) -> None:
     if load().fcs_set_single_pass(int(mode)) != FCS_OK:
         raise ValueError(f"single-pass mode must be 0, 1 or 2, got {mode}")
     _call_workspace.clear()   # the scratch a call uses follows the kernel it takes
+
+
+SHORT_FUSED_AUTO, SHORT_FUSED_NEVER, SHORT_FUSED_ALWAYS = 0, 1, 2
+
+
+def set_short_fused(mode: int) -> None:
+    """Kernel choice for short query axes over short key axes (`fcs_set_short_fused`)."""
+    if load().fcs_set_short_fused(int(mode)) != FCS_OK:
+        raise ValueError(f"short-fused mode must be 0, 1 or 2, got {mode}")
+    _call_workspace.clear()   # the scratch a call uses follows the kernel it takes
+
+
+def short_fused_applies(B: int, H: int, sq_rows: int, sk: int, is_causal: bool = True, k_past: int = -1,
+                        D: int = 128):
+    """(cluster size, key blocks per CTA) when a call with these sizes takes the one-kernel form for
+    short query axes under the current mode, else None.  Calls with at most four query rows, and calls
+    that the single-pass kernel takes, are decided before this."""
+    cl, bpc = _i(0), _i(0)
+    if not load().fcs_short_fused_applies(B, H, sq_rows, sk, D, int(is_causal), int(k_past), ctypes.byref(cl),
+                                          ctypes.byref(bpc)):
+        return None
+    return cl.value, bpc.value
 
 
 _call_workspace: dict = {}   # (sizes, k_past) -> fcs_call_workspace_bytes; host arithmetic, cached per shape

@@ -22,6 +22,7 @@ SOURCES = [os.path.join(CSRC, "flash_colsum_sm100.cu")]
 HEADERS = [os.path.join(CSRC, "sm100_ptx.cuh"), os.path.join(CSRC, "schedule.h"),
            os.path.join(CSRC, "colsum_small_q.cuh"), os.path.join(CSRC, "colsum_math.cuh"),
            os.path.join(CSRC, "colsum_single_pass.cuh"), os.path.join(CSRC, "select_topk.cuh"),
+           os.path.join(CSRC, "colsum_fused_short.cuh"),
            os.path.join(os.path.dirname(PKG), "include", "flash_colsum_b200.h")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

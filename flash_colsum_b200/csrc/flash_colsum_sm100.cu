@@ -27,8 +27,9 @@
 // buffers of 256 tensor-memory columns.  Calls with at most four query rows
 // take the matrix-vector kernel of colsum_small_q.cuh instead; short non-causal
 // key axes at head dimension 64 take the single-pass cluster kernel of
-// colsum_single_pass.cuh; select_topk.cuh holds the pruning step that callers
-// run on the result.
+// colsum_single_pass.cuh; a query axis of at most 128 rows over a few thousand keys
+// takes the one-kernel cluster form of colsum_fused_short.cuh; select_topk.cuh holds
+// the pruning step that callers run on the result.
 #include "sm100_ptx.cuh"
 #include "schedule.h"
 #include "colsum_small_q.cuh"
@@ -794,6 +795,12 @@ __global__ void merge_stats_kernel(const Problem p) {
 // kernels across ranks without a collective: a release store per flag, and a bounded wait
 // until every flag has reached a value.
 // ---------------------------------------------------------------------------
+}  // namespace fcs
+
+#include "colsum_fused_short.cuh"
+
+namespace fcs {
+
 constexpr int PEER_FLAGS_MAX = 16;
 struct PeerFlagPointers { int* p[PEER_FLAGS_MAX]; };
 
@@ -1163,6 +1170,129 @@ static int launch_single_pass(const CUtensorMap& tq, const CUtensorMap& tk, floa
     return FCS_OK;
 }
 
+// Short query axis over a short key axis: the one-kernel cluster form.
+// g_short_fused: 0 = where fused_short_plan says so, 1 = never, 2 = whenever the query
+// rows fit one tile.
+static int g_short_fused = 0;
+
+// Clusters of 1..8 CTAs of the one-kernel form that the current device runs at once
+// (table[c]; fewer than SMs / c: a cluster stays inside one GPC).  Without a device to ask,
+// seven eighths of SMs / c, which is what a B200 answers for clusters of four and of eight.
+template <int D>
+static const int* fused_short_max_clusters() {
+    static int cached[64][fused::MAX_CL + 1] = {{0}};
+    static int fallback[fused::MAX_CL + 1];
+    int dev = 0;
+    const bool have_dev = cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64;
+    if (!have_dev) cudaGetLastError();
+    const int sms = num_sms();
+    int* table = have_dev ? cached[dev] : fallback;
+    if (have_dev && table[1] != 0) return table;
+    auto kern = fused::colsum_fused_short_kernel<D>;
+    bool ask = have_dev && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                fused::FLayout<D>::DYN_BYTES) == cudaSuccess;
+    for (int cl = 1; cl <= fused::MAX_CL; ++cl) {
+        int n = 0;
+        if (ask) {
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim = dim3((unsigned)(cl * 64));
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = fused::FLayout<D>::DYN_BYTES;
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = (unsigned)cl;
+            attr.val.clusterDim.y = 1;
+            attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+                cudaGetLastError();
+                n = 0;
+            }
+        }
+        if (n <= 0) n = cl == 1 ? sms : (sms / cl) * 7 / 8;
+        table[cl] = n > 0 ? n : 1;
+    }
+    return table;
+}
+
+static bool short_fused_applies(int B, int H, int Sq, int Sk, int D, int causal, int k_past, int* cl_out,
+                                int* nkb_out, int* bpc_out) {
+    if (g_short_fused == 1) return false;
+    if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
+    const int* table = D <= 64 ? fused_short_max_clusters<64>() : fused_short_max_clusters<128>();
+    return fused_short_plan(B, H, Sq, Sk, causal, causal ? k_past : 0, num_sms(), table, g_short_fused == 2, cl_out,
+                            nkb_out, bpc_out);
+}
+
+template <int D>
+static cudaError_t launch_fused_short_d(const CUtensorMap& tq, const CUtensorMap& tk, const fused::Params& fp,
+                                        cudaStream_t stream, bool after_clear) {
+    using LayoutT = fused::FLayout<D>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kern = fused::colsum_fused_short_kernel<D>;
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LayoutT::DYN_BYTES);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)((long long)fp.p.B * fp.p.H * fp.CL));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = LayoutT::DYN_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = (unsigned)fp.CL;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    // behind the clearing kernel: start at once, wait for it only before the adds
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = after_clear ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, tq, tk, fp);
+}
+
+// `p` carries the sizes, the mask rule, the scale and the output; tq: boxes of 128 query rows,
+// tk: boxes of 256 key rows.
+static int launch_fused_short(const CUtensorMap& tq, const CUtensorMap& tk, const Problem& p, int DK, float scale,
+                              bool use_ext, int cl, int nkb, int bpc, bool clear_out, float* clear_extra,
+                              long long clear_extra_n, cudaStream_t stream) {
+    if (clear_extra && clear_extra_n > 0) {
+        long long blocks = (clear_extra_n + 1023) / 1024;
+        if (blocks > sms_for_clear()) blocks = sms_for_clear();
+        clear_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(clear_extra, clear_extra_n, 1, (int)clear_extra_n);
+    }
+    if (clear_out) {
+        long long blocks = ((long long)p.B * p.Sk + 1023) / 1024;
+        if (blocks > num_sms()) blocks = num_sms();
+        clear_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.out, p.out_ld, p.B, p.Sk);
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "clearing the output failed: %s", cudaGetErrorString(e));
+    }
+    fused::Params fp;
+    memset(&fp, 0, sizeof(fp));
+    fp.p = p;
+    fp.CL = cl;
+    fp.nkb = nkb;
+    fp.blocks_per_cta = bpc;
+    fp.use_ext = use_ext ? 1 : 0;
+    const uint32_t fmt = p.ext_bf16 ? 1u : 0u;
+    const uint32_t common = (1u << 4) | (fmt << 7) | (fmt << 10) | ((scale < 0.f ? 1u : 0u) << 13) |
+                            ((uint32_t)(TILE >> 4) << 24);
+    fp.idesc_scores = common | ((uint32_t)(BLOCK >> 3) << 17);
+    fp.idesc_cols = common | ((uint32_t)((BLOCK / 2) >> 3) << 17);
+    const cudaError_t e = (DK == 64) ? launch_fused_short_d<64>(tq, tk, fp, stream, clear_out)
+                                     : launch_fused_short_d<128>(tq, tk, fp, stream, clear_out);
+    if (e != cudaSuccess) return fail(FCS_ERR_CUDA, "one-kernel short form launch failed: %s", cudaGetErrorString(e));
+    return FCS_OK;
+}
+
 enum : int { PASSES_BOTH = 0, PASSES_STATS = 1, PASSES_COLUMNS = 2 };
 
 // -(log-sum-exp) per query row -> the 16 extension columns the column pass contracts with.
@@ -1282,6 +1412,21 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
             }
             rc = launch_single_pass(tq_a, tk_b, out, out_ld, B, H, Sq, Sk, scale, h_norm, dtype, clear_out,
                                     max_clusters, status, stream);
+            if (rc == FCS_OK && tms) { cudaEventRecord(tms->ev[3], stream); tms->recorded = true; }
+            return rc;
+        }
+    }
+    {
+        int fcl = 0, fnkb = 0, fbpc = 0;
+        if (passes == PASSES_BOTH && !sig && short_fused_applies(B, H, Sq, Sk, D, causal, k_past, &fcl, &fnkb, &fbpc)) {
+            // reported as a call whose statistics and merge passes take no time
+            PassTimers* tms = g_profiling ? timers_for_current_device() : nullptr;
+            if (tms) {
+                tms->recorded = false;
+                for (int i = 0; i < 3; ++i) cudaEventRecord(tms->ev[i], stream);
+            }
+            rc = launch_fused_short(tq_a, tk_b, p, DK, scale, use_ext, fcl, fnkb, fbpc, clear_out, clear_extra,
+                                    clear_extra_n, stream);
             if (rc == FCS_OK && tms) { cudaEventRecord(tms->ev[3], stream); tms->recorded = true; }
             return rc;
         }
@@ -1413,7 +1558,7 @@ static int static_scratch_address(void** out_ptr) {
 // ---------------------------------------------------------------------------
 extern "C" {
 
-int fcs_version(void) { return 200; }
+int fcs_version(void) { return 201; }
 
 const char* fcs_last_error(void) { return fcs::g_err; }
 
@@ -1426,6 +1571,22 @@ int fcs_set_single_pass(int mode) {
     if (mode < 0 || mode > 2) return FCS_ERR_INVALID_ARGUMENT;
     fcs::g_single_pass = mode;
     return FCS_OK;
+}
+
+int fcs_set_short_fused(int mode) {
+    if (mode < 0 || mode > 2) return FCS_ERR_INVALID_ARGUMENT;
+    fcs::g_short_fused = mode;
+    return FCS_OK;
+}
+
+int fcs_short_fused_applies(int B, int H, int sq_rows, int Sk, int D, int is_causal, int k_past, int* cluster_size,
+                            int* blocks_per_cta) {
+    if (B <= 0 || H <= 0 || sq_rows <= 0 || Sk <= 0 || !fcs::head_dim_ok(D)) return 0;
+    int cl = 0, nkb = 0, bpc = 0;
+    if (!fcs::short_fused_applies(B, H, sq_rows, Sk, D, is_causal ? 1 : 0, k_past, &cl, &nkb, &bpc)) return 0;
+    if (cluster_size) *cluster_size = cl;
+    if (blocks_per_cta) *blocks_per_cta = bpc;
+    return 1;
 }
 
 int fcs_single_pass_applies(int B, int H, int sq_rows, int Sk, int D, int is_causal) {
@@ -1501,6 +1662,8 @@ int fcs_call_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_ca
         fcs::single_pass_max_clusters(fcs::single_pass_cluster_size(Sk)) > 0)
         return FCS_OK;   // single-pass kernel: no scratch
     if (causal && k_past < 0) k_past = Sk > sq_rows ? Sk - sq_rows : 0;
+    if (fcs::short_fused_applies(B, H, sq_rows, Sk, D, causal, k_past, nullptr, nullptr, nullptr))
+        return FCS_OK;   // one-kernel short form: no scratch
     fcs::Problem p;
     memset(&p, 0, sizeof(p));
     fcs::plan(p, B, H, sq_rows, Sk, causal, causal ? k_past : 0, fcs::num_sms());

@@ -484,6 +484,58 @@ struct TileRange {
     }
 };
 
+// ---------------------------------------------------------------------------
+// The one-kernel form for a short query axis over a short key axis: a cluster of `cl` CTAs
+// per (batch, head), CTA r walking the r-th run of `bpc` 256-key blocks twice (statistics,
+// then columns).  `max_clusters[c]` is how many clusters of c CTAs the device runs at once
+// (c = 1..8); `k_past` is the resolved value (>= 0) of a causal call.
+//
+// The cluster size is the largest with which all (batch, head) pairs run in one wave; with
+// more pairs than SMs, one CTA each in several waves.  The form is taken when the query
+// rows fit one 128-row tile and
+//   * the call is small (at most 16 key blocks per SM in all): it is bound by its launches,
+//     and this form has one kernel where the streaming passes have three; or
+//   * it is up to four times that, one wave of clusters covers four fifths of the SMs and
+//     no CTA walks more than 64 blocks: both forms then run at the memory rate, and this
+//     one still saves the launches (measured on 32 heads x 128 queries: 27 against 41 us at
+//     4096 keys, 64 against 79 at 16384, 191 against 211 at 65536, a tie from 131072 on);
+//   * never with more than four waves of CTAs (768 pairs of 197 keys: 60 against 50 us --
+//     the ramp of a CTA is paid once per wave).
+// `force`: only the shape limits apply (at most 128 rows).
+// ---------------------------------------------------------------------------
+constexpr int FUSED_SHORT_MAX_CLUSTER = 8;
+constexpr int FUSED_SHORT_MAX_BLOCKS = 64;      // per CTA
+constexpr int FUSED_SHORT_SMALL_WORK = 16;      // 256-key blocks in the whole call, per SM
+constexpr int FUSED_SHORT_LARGE_WORK = 64;
+constexpr int FUSED_SHORT_MAX_WAVES = 4;
+FCS_HD inline bool fused_short_plan(int B, int H, int Sq, int Sk, int causal, int k_past, int sms,
+                                    const int* max_clusters, bool force, int* cl_out, int* nkb_out, int* bpc_out) {
+    if (Sq > TILE) return false;
+    long long keys = Sk;
+    if (causal && (long long)k_past + Sq < keys) keys = (long long)k_past + Sq;   // keys some row sees
+    const long long nkb = (keys + BLOCK - 1) / BLOCK;
+    const long long units = (long long)B * H;
+    int cl = 1;
+    for (int c = nkb < FUSED_SHORT_MAX_CLUSTER ? (int)nkb : FUSED_SHORT_MAX_CLUSTER; c > 1; --c)
+        if (units <= max_clusters[c]) { cl = c; break; }
+    const long long bpc = (nkb + cl - 1) / cl;
+    cl = (int)((nkb + bpc - 1) / bpc);                 // no CTA without a block
+    if (bpc > (1 << 20)) return false;
+    if (!force) {
+        if (bpc > FUSED_SHORT_MAX_BLOCKS) return false;
+        if (units * cl > (long long)FUSED_SHORT_MAX_WAVES * sms) return false;
+        const long long work = units * nkb;
+        if (work > (long long)FUSED_SHORT_SMALL_WORK * sms) {
+            if (work > (long long)FUSED_SHORT_LARGE_WORK * sms) return false;
+            if (units > max_clusters[cl] || units * cl * 5 < (long long)sms * 4) return false;
+        }
+    }
+    if (cl_out) *cl_out = cl;
+    if (nkb_out) *nkb_out = (int)nkb;
+    if (bpc_out) *bpc_out = (int)bpc;
+    return true;
+}
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // Scratch layout: [neg_lse | ext | part]; returns the total and the offsets.

@@ -72,12 +72,13 @@ size_t fcs_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_caus
 
 /*
  * Scratch bytes the call with exactly these arguments will use, written to
- * *bytes: 0 when it takes the few-row kernel (at most four query rows) or the
- * single-pass kernel (see fcs_set_single_pass), which use none -- such a call
+ * *bytes: 0 when it takes the few-row kernel (at most four query rows), the
+ * single-pass kernel (see fcs_set_single_pass) or the one-kernel form for short
+ * query axes (see fcs_set_short_fused), which use none -- such a call
  * may pass workspace = NULL -- otherwise the layout of the two streaming passes
  * for this k_past (k_past < 0: the inferred max(0, Sk - sq_rows); ignored when
  * not causal).  The answer follows the kernel choice in force when it is asked:
- * ask again after fcs_set_single_pass.  Never more than fcs_workspace_bytes().
+ * ask again after fcs_set_single_pass or fcs_set_short_fused.  Never more than fcs_workspace_bytes().
  * Returns FCS_OK or an FCS_ERR_* code for sizes no call accepts.
  */
 int fcs_call_workspace_bytes(int B, int H, int sq_rows, int Sk, int D, int is_causal, int k_past,
@@ -347,6 +348,32 @@ int fcs_single_pass_applies(int B, int H, int sq_rows, int Sk, int D, int is_cau
 /* CTAs per cluster the single pass uses for `Sk` keys (one per 256 keys) and how many
  * such clusters the current device runs at once. */
 int fcs_single_pass_info(int Sk, int *cluster_size, int *max_clusters);
+
+/*
+ * Kernel choice for a query axis of at most 128 rows (the causal query suffix of a
+ * prompt, a CLS prefix of more than four rows) over a short key axis.  Such calls take
+ * tens of microseconds and are bound by their launches; the one-kernel form runs a
+ * thread-block cluster per (batch, head): every CTA finds the row statistics of its
+ * run of 256-key blocks, the CTAs exchange them through distributed shared memory, and
+ * every CTA then sums its keys' columns -- one kernel behind a small clearing kernel
+ * instead of three, and no scratch.  No counterpart in the reference, whose causal
+ * launcher (flash_colsum/kernel_causal_batched.py:106-136) is one Triton kernel per
+ * call with atomics over key blocks.
+ * mode 0 (default): the cluster size is the largest with which all (batch, head) pairs
+ * run at once (32 heads on 148 SMs: clusters of four); the form is taken for small calls
+ * (at most 16 key blocks of 256 per SM in all), for calls up to four times that when the
+ * clusters cover four fifths of the SMs and no CTA walks more than 64 blocks, and never
+ * with more than four waves of CTAs; 1: never; 2: whenever the query rows fit one tile.
+ * Process-wide; not thread-safe.  The call reports its whole duration as the column
+ * pass in fcs_last_pass_ms(); fcs_call_workspace_bytes() follows the mode in force.
+ */
+int fcs_set_short_fused(int mode);
+/* 1 if a call with these sizes takes the one-kernel form under the current mode (host
+ * arithmetic only; k_past < 0: the inferred value; calls the few-row or the single-pass
+ * kernel takes are decided before this one).  Writes the CTAs per cluster and the key
+ * blocks each walks when the pointers are not NULL. */
+int fcs_short_fused_applies(int B, int H, int sq_rows, int Sk, int D, int is_causal, int k_past, int *cluster_size,
+                            int *blocks_per_cta);
 
 /*
  * Self-test of the device status path.  Every wait inside the kernels (on an mbarrier that a

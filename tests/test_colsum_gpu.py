@@ -575,6 +575,94 @@ def test_batched_causal_and_explicit_k_past(fc):
         fc.flash_colsum_causal(q.cuda(), k.cuda(), k_past=-2)
 
 
+SHORT_AXES = [
+    # B, H, Sq, Sk, D, dtype, causal, scale, k_past
+    (1, 32, 128, 4096, 128, "fp16", True, None, None),      # the reference's causal test shape: clusters of four
+    (1, 8, 128, 4096, 128, "bf16", True, None, None),       # clusters of eight
+    (1, 2, 7, 7, 128, "bf16", False, None, None),           # one block, one CTA per head
+    (1, 3, 100, 1000, 64, "fp16", True, None, None),
+    (2, 4, 64, 300, 64, "fp16", True, None, None),          # batched causal
+    (1, 5, 128, 100, 64, "fp16", True, None, None),         # fewer keys than queries
+    (1, 6, 33, 2049, 128, "fp16", True, None, None),        # one key in the last block
+    (1, 32, 64, 2048, 80, "fp16", True, None, None),        # head dimension padded to 128 columns
+    (1, 4, 128, 3000, 64, "bf16", True, -0.2, None),        # negative scale: the MMA negates
+    (1, 4, 90, 1500, 128, "fp16", True, 1e-5, None),        # scale too small for the extra columns
+    (1, 4, 100, 2000, 128, "fp16", True, None, 0),          # explicit K_past: only the first keys are seen
+    (1, 4, 100, 2000, 128, "fp16", True, None, 700),
+    (1, 4, 100, 2000, 128, "bf16", True, None, 5000),       # beyond the key axis: no mask left
+    (3, 70, 20, 600, 64, "fp16", True, None, None),         # more (batch, head) pairs than SMs: several waves
+    (1, 16, 128, 40000, 128, "bf16", True, None, None),     # 20 blocks per CTA
+]
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk,D,dtype,causal,scale,k_past", SHORT_AXES)
+def test_short_query_axes_in_one_kernel(fc, B, H, Sq, Sk, D, dtype, causal, scale, k_past):
+    """At most 128 query rows: the one-kernel cluster form (statistics, exchange through
+    distributed shared memory, columns) against the float64 evaluation, and against the two
+    streaming passes on the same inputs."""
+    from flash_colsum_b200 import _cabi
+    from oracle.naive_colsum import naive_colsum_f64
+    w = Workload("short", B, H, Sq, Sk, D, dtype, is_causal=causal, seed=B + H + Sq + Sk)
+    q, k = make_inputs(w)
+    qc, kc = q.cuda(), k.cuda()
+
+    def call():
+        if causal:
+            return fc.flash_colsum_causal(qc, kc, scale=scale, k_past=k_past)
+        return fc.flash_colsum(qc, kc, scale=scale)
+    want = naive_colsum_f64(q, k, scale=scale, is_causal=causal, k_past=k_past)
+    try:
+        _cabi.set_short_fused(_cabi.SHORT_FUSED_ALWAYS)
+        assert _cabi.short_fused_applies(B, H, Sq, Sk, causal, -1 if k_past is None else k_past, D) is not None
+        assert _cabi.call_workspace_bytes(B, H, Sq, Sk, D, causal, -1 if k_past is None else k_past) == 0
+        got = call()
+        torch.cuda.synchronize()
+        assert fc.device_status() == 0
+        again = call()                      # a second call in a row: nothing is left over from the first
+        _cabi.set_short_fused(_cabi.SHORT_FUSED_NEVER)
+        two_pass = call()
+        torch.cuda.synchronize()
+        assert fc.device_status() == 0
+    finally:
+        _cabi.set_short_fused(_cabi.SHORT_FUSED_AUTO)
+    assert_parity(got.cpu().numpy(), want, f"one kernel {B}x{H}x{Sq}x{Sk}x{D}")
+    assert_parity(two_pass.cpu().numpy(), want, f"two passes {B}x{H}x{Sq}x{Sk}x{D}")
+    torch.testing.assert_close(got, again, rtol=1e-5, atol=1e-9)
+    np.testing.assert_allclose(got.sum(dim=1).cpu().numpy(), 1.0, rtol=1e-4)
+
+
+def test_short_query_axes_accumulate_and_graph_capture(fc):
+    """The accumulate entry adds into what the buffer holds (no clearing kernel in front), and a
+    call of the one-kernel form replays from a CUDA graph."""
+    from flash_colsum_b200 import _cabi
+    w = Workload("short_acc", 1, 8, 128, 3000, 128, "fp16", is_causal=True, seed=77)
+    q, k = make_inputs(w)
+    qc, kc = q.cuda(), k.cuda()
+    assert _cabi.short_fused_applies(1, 4, 128, 3000) is not None
+    want = c_oracle.colsum_c(q, k, is_causal=True)
+    from flash_colsum_b200 import ops
+    total = torch.zeros(3000, device="cuda", dtype=torch.float32)
+    for h0 in (0, 4):      # two shards of four heads each, normalised by all eight
+        ops._flash_colsum_causal(qc[:, h0:h0 + 4], kc[:, h0:h0 + 4], 1.0 / 128 ** 0.5, h_norm=8, accumulate_into=total)
+    torch.cuda.synchronize()
+    assert fc.device_status() == 0
+    assert_parity(total.cpu().numpy()[None, :], want, "two head shards into one buffer")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fc.flash_colsum(qc, kc, is_causal=True)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = fc.flash_colsum(qc, kc, is_causal=True)
+    for _ in range(3):
+        out.fill_(-1.0)
+        graph.replay()
+    torch.cuda.synchronize()
+    assert fc.device_status() == 0
+    assert_parity(out.cpu().numpy(), want, "graph replay")
+
+
 def test_topk_columns_matches_a_plain_sort(fc):
     """The pruning step: exact top-k positions per row, ascending, ties to the lower position."""
     from oracle.naive_colsum import topk_positions

@@ -173,6 +173,14 @@ def test_scratch_queries_cover_every_k_past(emu):
     lib = _cabi.load()
     sms = _cabi.plan_info(1, 1, 128, 128, False)["sms"]
     need = ctypes.c_size_t(0)
+    _cabi.set_short_fused(_cabi.SHORT_FUSED_NEVER)   # (at most 128 rows would take the one-kernel form)
+    try:
+        _walk_scratch(emu, lib, sms, need)
+    finally:
+        _cabi.set_short_fused(_cabi.SHORT_FUSED_AUTO)
+
+
+def _walk_scratch(emu, lib, sms, need):
     walked = shortfalls = grew = 0
     for B in (1, 2, 5):
         for H in (1, 3, 8, 32):
@@ -209,8 +217,22 @@ def test_calls_that_take_a_kernel_without_scratch_ask_for_none():
     assert lib.fcs_call_workspace_bytes(32, 16, 1, 577, 64, 0, 0, ctypes.byref(need)) == 0 and need.value == 0
     # four decode queries over a long key axis, causal
     assert lib.fcs_call_workspace_bytes(1, 32, 4, 8192, 128, 1, -1, ctypes.byref(need)) == 0 and need.value == 0
-    # five rows: the streaming passes
-    assert lib.fcs_call_workspace_bytes(1, 32, 5, 8192, 128, 1, -1, ctypes.byref(need)) == 0 and need.value > 0
+    # five rows over the same keys, and the causal suffix of 128 queries over 4096 keys: the one-kernel form
+    assert lib.fcs_call_workspace_bytes(1, 32, 5, 8192, 128, 1, -1, ctypes.byref(need)) == 0 and need.value == 0
+    assert lib.fcs_call_workspace_bytes(1, 32, 128, 4096, 128, 1, -1, ctypes.byref(need)) == 0 and need.value == 0
+    assert _cabi.short_fused_applies(1, 32, 128, 4096) == (4, 4)
+    # ... unless it is switched off, or the call is large: the streaming passes
+    _cabi.set_short_fused(_cabi.SHORT_FUSED_NEVER)
+    try:
+        assert lib.fcs_call_workspace_bytes(1, 32, 128, 4096, 128, 1, -1, ctypes.byref(need)) == 0 and need.value > 0
+        assert _cabi.short_fused_applies(1, 32, 128, 4096) is None
+    finally:
+        _cabi.set_short_fused(_cabi.SHORT_FUSED_AUTO)
+    assert _cabi.short_fused_applies(1, 32, 128, 65536) == (4, 64)       # still one wave over most SMs
+    assert lib.fcs_call_workspace_bytes(1, 32, 128, 131072, 128, 1, -1, ctypes.byref(need)) == 0 and need.value > 0
+    assert _cabi.short_fused_applies(1, 16, 128, 65536) is None           # too few CTAs for a call this long
+    assert _cabi.short_fused_applies(64, 12, 16, 197, is_causal=False, D=64) is None   # more than four waves
+    assert lib.fcs_call_workspace_bytes(1, 32, 300, 8192, 128, 1, -1, ctypes.byref(need)) == 0 and need.value > 0
     # sizes no call accepts
     assert lib.fcs_call_workspace_bytes(1, 1, 1, 1, 100, 0, 0, ctypes.byref(need)) == -2
     assert lib.fcs_call_workspace_bytes(0, 1, 1, 1, 64, 0, 0, ctypes.byref(need)) == -1
