@@ -14,7 +14,8 @@ batched sweep shape (B=128 H=16 S=1024 per GPU), which takes the single-pass clu
 next to the two-pass kernels on the same inputs under "short_key_axis", and a point of the
 reference's causal sweep (H=32 Q=128 K=65536 D=128), which is bound by HBM, under "causal_suffix",
 the CLIP-style CLS call (B=32 H=16 S=577, cls_len=1; bound by HBM) under "cls_prefix" and the
-decode-suffix call (H=32 Q=128 K=4096 D=128; bound by launches) under "causal_short".  The
+decode-suffix call (H=32 Q=128 K=4096 D=128; bound by latency: the one-kernel cluster form, with the
+three-kernel form timed beside it) under "causal_short".  The
 long-context leg carries a "parity" object: its result against a materialising fp32 evaluation
 of all heads (every rank evaluates its own heads, the sums meet in one NCCL all-reduce).
 
@@ -606,7 +607,7 @@ def main():
                   "ms_per_call": ms_q, "value": wq.flop * world / (ms_q * 1e-3) / 1e12, "unit": UNIT,
                   "roofline": {"bound": "hbm", "achieved": key_bytes / (ms_q * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                                "unit": "GB/s", "frac": key_bytes / (ms_q * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                               "bytes": "keys once per pass, two passes; the whole call incl. the merge kernel"}}
+                               "bytes": "the keys twice (once per phase of the one-kernel form, or once per streaming pass); the whole call"}}
         del qq, kq
     assert fc.device_status() == 0
 
@@ -633,15 +634,28 @@ def main():
         w4 = WORKLOADS["c4"]
         q4, k4 = (t.to(dev) for t in make_inputs(Workload(w4.name, w4.B, w4.H, w4.Sq, w4.Sk, w4.D, w4.dtype,
                                                           is_causal=True, seed=w4.seed + rank)))
-        ms4, b2b4, st4, mg4, col4 = small_call_leg(fc, _cabi, w4, q4, k4, n_small, flush_buf, barrier, max_over_ranks, peaks)
+        ms4, b2b4, _, _, kern4 = small_call_leg(fc, _cabi, w4, q4, k4, n_small, flush_buf, barrier, max_over_ranks, peaks)
+        form4 = _cabi.short_fused_applies(w4.B, w4.H, w4.Sq, w4.Sk, True, -1, w4.D)
+        # the same call through the statistics, merge and column kernels, for comparison
+        _cabi.set_short_fused(_cabi.SHORT_FUSED_NEVER)
+        try:
+            ms4_three, _, st4, mg4, col4 = small_call_leg(fc, _cabi, w4, q4, k4, n_small, flush_buf, barrier,
+                                                          max_over_ranks, peaks)
+        finally:
+            _cabi.set_short_fused(_cabi.SHORT_FUSED_AUTO)
         causal_short = {"workload": "c4: causal H=32 Q=128 K=4096 D=128 fp16 per GPU",
-                        "ms_per_call": ms4, "ms_per_call_back_to_back": b2b4,
-                        "pass_ms": {"statistics": st4, "merge": mg4, "columns": col4},
+                        "kernel": ("colsum_fused_short_kernel (a cluster of %d CTAs per head, %d key blocks each: statistics, "
+                                   "exchange through distributed shared memory, columns) behind clear_rows_kernel" % form4
+                                   if form4 else "statistics, merge and column kernels"),
+                        "ms_per_call": ms4, "ms_per_call_back_to_back": b2b4, "kernel_ms": kern4,
+                        "three_kernels": {"ms_per_call": ms4_three,
+                                          "pass_ms": {"statistics": st4, "merge": mg4, "columns": col4}},
                         "value": w4.flop / (ms4 * 1e-3) / 1e12, "unit": UNIT,
                         "roofline": {"bound": "tensor", "achieved": w4.flop / (ms4 * 1e-3) / 1e12, "peak": peaks["tflops"],
                                      "unit": UNIT, "frac": w4.flop / (ms4 * 1e-3) / 1e12 / peaks["tflops"],
-                                     "note": ("launch-bound: three kernels of a few microseconds each, chained by programmatic "
-                                              "dependent launch; 8.6 GFLOP would take 5 us at the peak")}}
+                                     "note": ("bound by latency, not by a unit: 8.6 GFLOP would take 5 us at the tensor peak, "
+                                              "the 33.5 MB of keys 5 us at the HBM rate, the 67 M exps 9 us on 128 SMs; the "
+                                              "rest is the launch, the ramp of a CTA and the exchange between the phases")}}
         del q4, k4
     assert fc.device_status() == 0
 

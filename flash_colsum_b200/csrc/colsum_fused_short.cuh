@@ -1,8 +1,9 @@
 // Attention column mean of a short query axis (at most 128 rows: the causal query
-// suffix of a prompt, a long CLS prefix) over a key axis of a few thousand keys, in
-// one kernel instead of the statistics kernel, the merge kernel and the column kernel.
-// Such calls take tens of microseconds and were bound by their three launches, each
-// with its own ramp (barriers, tensor memory, first tiles) and drain.
+// suffix of a prompt, a long CLS prefix) in one kernel instead of the statistics
+// kernel, the merge kernel and the column kernel.  Over a few thousand keys such a
+// call takes tens of microseconds and was bound by its three launches, each with its
+// own ramp (barriers, tensor memory, first tiles) and drain; which calls take this
+// form is decided by fused_short_plan (schedule.h).
 //
 // One thread-block cluster per (batch, head); CTA r of the cluster owns the r-th run
 // of 256-key blocks.  The head's query block is loaded once and serves both phases:
@@ -20,8 +21,8 @@
 //                              tensor-memory lane = key: exp2 summed down the query axis
 //                              in the thread, one add per key and consumer group
 //
-// The key blocks are fetched again for phase 2 (they are in L2: the same CTA read them
-// microseconds before); the copy warp runs ahead across the exchange.  The output is
+// The key blocks are fetched again for phase 2 (from L2 when the call's keys fit it: the
+// same CTA read them microseconds before); the copy warp runs ahead across the exchange.  The output is
 // cleared by a small kernel in front, of which this kernel is a programmatic dependent:
 // it waits for it only before its first add.
 //
@@ -33,7 +34,6 @@ namespace fcs {
 namespace fused {
 
 constexpr int MAX_CL = 8;               // CTAs per cluster (portable limit)
-constexpr int MAX_BLOCKS_PER_CTA = 16;  // 256-key blocks one CTA walks in each phase
 
 struct Params {
     Problem p;              // sizes, mask rule, scale, output (the scratch fields stay unused)
@@ -149,7 +149,6 @@ colsum_fused_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 
     if (warp == PRODUCER_WARP) {
         // -------------------------------------------- copies: the query block, then the key blocks twice
-        smallq_cluster_wait();
         if (elect_one_sync()) {
             mbar_arrive_expect_tx(q_full, L::Q_BYTES);
 #pragma unroll
@@ -171,9 +170,9 @@ colsum_fused_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             }
             __syncwarp();
         }
+        smallq_cluster_wait();      // (pairs with the arrive above; this warp stores nothing into other CTAs)
     } else if (warp == MMA_WARP) {
         // -------------------------------------------- MMA issuer
-        smallq_cluster_wait();
         bool ok = wait_all(q_full, 0, FCS_STATUS_WAIT_MMA);
         const uint64_t dq = umma_desc_k_sw128(q_smem);
         int n = 0;
@@ -196,6 +195,7 @@ colsum_fused_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             }
             __syncwarp();
         }
+        smallq_cluster_wait();      // (pairs with the arrive above)
         // the extra columns of the query block are in shared memory (and every score of phase 1 has been read)
         if (ok) ok = wait_all(ext_ready, 0, FCS_STATUS_WAIT_MMA);
         for (; ok && n < 2 * nblk; ++n) {      // phase 2: two tiles of 128 keys x 128 queries per block

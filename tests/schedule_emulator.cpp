@@ -307,3 +307,60 @@ extern "C" long long scratch_need(int B, int H, int Sq, int Sk, int causal, int 
     if (nsplit_out) *nsplit_out = p.nsplit;
     return (long long)workspace_layout(p, nullptr);
 }
+
+// The one-kernel form for short query axes: plan a call, then walk every CTA's run of key blocks the
+// way the kernel does and check, element by element, that the mask rules of its two phases (row
+// statistics with lane = query, column sums with lane = key) both see exactly the (query, key) pairs
+// of the definition, each once.  Returns 0 when the plan declines the call, cl * 1000 + bpc when it
+// takes it and the walk is clean, a negative code otherwise.
+extern "C" int check_fused_short(int B, int H, int Sq, int Sk, int causal, int k_past, int sms,
+                                 const int* max_clusters, int force) {
+    if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
+    if (!causal) k_past = 0;
+    int cl = 0, nkb = 0, bpc = 0;
+    if (!fused_short_plan(B, H, Sq, Sk, causal, k_past, sms, max_clusters, force != 0, &cl, &nkb, &bpc)) return 0;
+    if (cl < 1 || cl > FUSED_SHORT_MAX_CLUSTER || bpc < 1) return -1;
+    if ((long long)cl * bpc < nkb || (long long)(cl - 1) * bpc >= nkb) return -2;   // a CTA without a block
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.causal = causal; p.k_past = k_past;
+    std::vector<int> seen_stats((size_t)Sq * Sk, 0), seen_cols((size_t)Sq * Sk, 0);
+    int f_lo, f_hi;
+    stats_full_range(p, 0, f_lo, f_hi);
+    for (int r = 0; r < cl; ++r) {
+        int kb0 = r * bpc, kb1 = kb0 + bpc;
+        if (kb1 > nkb) kb1 = nkb;
+        for (int kb = kb0; kb < kb1; ++kb) {
+            // phase 1: rows are queries, columns the 256 keys of the block
+            for (int row = 0; row < TILE; ++row) {
+                const int lim = (kb >= f_lo && kb < f_hi) ? BLOCK - 1 : stats_last_visible(p, 0, kb, row);
+                for (int col = 0; col <= lim && col < BLOCK; ++col) {
+                    const long long key = (long long)kb * BLOCK + col;
+                    if (row >= Sq) continue;              // padding rows: their statistics are dropped
+                    if (key >= Sk) return -3;
+                    ++seen_stats[(size_t)row * Sk + key];
+                }
+            }
+            // phase 2: rows are the keys of a 128-key tile, columns the queries
+            for (int t = 0; t < 2; ++t) {
+                const int ktg = kb * 2 + t;
+                const int end = colsum_end_visible(p, 0);
+                for (int row = 0; row < TILE; ++row) {
+                    const long long key = (long long)ktg * TILE + row;
+                    const int first = colsum_first_visible(p, ktg, 0, row);
+                    for (int qc = first; qc < end; ++qc) {
+                        if (key >= Sk) continue;          // lanes past the key axis are not added
+                        ++seen_cols[(size_t)qc * Sk + key];
+                    }
+                }
+            }
+        }
+    }
+    for (int qi = 0; qi < Sq; ++qi)
+        for (int key = 0; key < Sk; ++key) {
+            const int want = (!causal || key <= (long long)k_past + qi) ? 1 : 0;
+            if (seen_stats[(size_t)qi * Sk + key] != want) return -4;
+            if (seen_cols[(size_t)qi * Sk + key] != want) return -5;
+        }
+    return cl * 1000 + bpc;
+}

@@ -30,6 +30,8 @@ def emu():
     lib.emulate_colsum.restype = ctypes.c_int
     lib.emulate_colsum.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 5 + [ctypes.c_float] + \
         [ctypes.c_int] * 5 + [ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
+    lib.check_fused_short.restype = ctypes.c_int
+    lib.check_fused_short.argtypes = [ctypes.c_int] * 7 + [ctypes.c_void_p, ctypes.c_int]
     lib.scratch_need.restype = ctypes.c_longlong
     lib.scratch_need.argtypes = [ctypes.c_int] * 7 + [ctypes.c_void_p]
     return lib
@@ -237,3 +239,43 @@ def test_calls_that_take_a_kernel_without_scratch_ask_for_none():
     assert lib.fcs_call_workspace_bytes(1, 1, 1, 1, 100, 0, 0, ctypes.byref(need)) == -2
     assert lib.fcs_call_workspace_bytes(0, 1, 1, 1, 64, 0, 0, ctypes.byref(need)) == -1
     assert lib.fcs_call_workspace_bytes(1, 1, 1, 1, 64, 0, 0, None) == -1
+
+
+# clusters of 1..8 CTAs that run at once, as a B200 answers for the one-kernel form (index = size)
+B200_CLUSTERS = (ctypes.c_int * 9)(0, 148, 74, 48, 32, 28, 24, 16, 15)
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk,causal,k_past,expect", [
+    (1, 32, 128, 4096, 1, -1, 4004),       # the reference's causal test shape: 32 clusters of four, four blocks each
+    (1, 8, 128, 4096, 1, -1, 8002),
+    (1, 16, 128, 4096, 1, -1, 6003),       # sixteen clusters of eight do not run at once: seven would, six are enough
+    (1, 2, 7, 7, 0, 0, 1001),
+    (2, 4, 64, 300, 1, -1, 2001),
+    (1, 5, 128, 100, 1, -1, 1001),         # fewer keys than queries
+    (1, 6, 33, 2049, 1, -1, 5002),         # nine blocks over five CTAs
+    (1, 4, 100, 2000, 1, 0, 1001),         # K_past 0: the first 100 keys are all that is seen
+    (1, 4, 100, 2000, 1, 700, 4001),
+    (1, 4, 100, 2000, 1, 5000, 8001),
+    (3, 70, 20, 600, 1, -1, 1003),         # more pairs than SMs: one CTA each
+    (1, 32, 128, 65536, 1, -1, 4064),
+    (1, 32, 128, 131072, 1, -1, 0),        # too long
+    (1, 16, 128, 65536, 1, -1, 0),         # long and too few CTAs
+    (64, 12, 16, 197, 0, 0, 0),            # more than four waves
+    (1, 4, 129, 1000, 1, -1, 0),           # two query tiles
+])
+def test_one_kernel_form_plan_and_masks(emu, B, H, Sq, Sk, causal, k_past, expect):
+    assert emu.check_fused_short(B, H, Sq, Sk, causal, k_past, 148, B200_CLUSTERS, 0) == expect
+
+
+def test_one_kernel_form_masks_on_a_walk_of_sizes(emu):
+    """Forced onto every size of a walk (ragged rows and keys, every K_past regime): both phases see
+    each visible (query, key) pair exactly once."""
+    walked = 0
+    for Sq in (1, 5, 31, 64, 100, 127, 128):
+        for Sk in (1, 40, 255, 256, 257, 600, 1024, 1500):
+            for k_past in (-1, 0, 3, 200, 255, 256, 700, Sk - 1, Sk, 3 * Sk):
+                rc = emu.check_fused_short(1, 3, Sq, Sk, 1, k_past, 148, B200_CLUSTERS, 1)
+                assert rc > 0, (Sq, Sk, k_past, rc)
+                walked += 1
+            assert emu.check_fused_short(2, 2, Sq, Sk, 0, 0, 148, B200_CLUSTERS, 1) > 0
+    assert walked == 7 * 8 * 10
