@@ -21,8 +21,9 @@
 //                              tensor-memory lane = key: exp2 summed down the query axis
 //                              in the thread, one add per key and consumer group
 //
-// The key blocks are fetched again for phase 2 (from L2 when the call's keys fit it: the
-// same CTA read them microseconds before); the copy warp runs ahead across the exchange.  The output is
+// The key blocks are fetched again for phase 2, last block first: what phase 1 read last is
+// what L2 still holds when the call's keys do not all fit it.  The copy warp runs ahead
+// across the exchange.  The output is
 // cleared by a small kernel in front, of which this kernel is a programmatic dependent:
 // it waits for it only before its first add.
 //
@@ -159,7 +160,7 @@ colsum_fused_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         bool ok = true;
         for (int n = 0; ok && n < 2 * nblk; ++n) {
             const int stage = n % L::NS;
-            const int kb = kb0 + (n < nblk ? n : n - nblk);
+            const int kb = n < nblk ? kb0 + n : kb1 - 1 - (n - nblk);   // phase 2 walks back: the last blocks are the ones still in L2
             if (n >= L::NS && !wait_all(k_empty(stage), ((n / L::NS) & 1) ^ 1, FCS_STATUS_WAIT_PRODUCER)) break;
             if (elect_one_sync()) {
                 mbar_arrive_expect_tx(k_full(stage), L::K_BYTES);
@@ -314,7 +315,7 @@ colsum_fused_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         float* dst = p.out + (long long)b * p.out_ld;
         bool out_clear = false;
         for (int i = 0; i < nblk; ++i, ++n) {
-            const int kb = kb0 + i, buf = n & (NUM_TBUF - 1);
+            const int kb = kb1 - 1 - i, buf = n & (NUM_TBUF - 1);
             ok = ok && mbar_wait(t_full(buf), (n >> 1) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
