@@ -28,6 +28,10 @@
  *   - All calls are asynchronous on `stream`, never synchronise and never
  *     allocate.  Return value: FCS_OK or a negative FCS_ERR_* code;
  *     fcs_last_error() gives the message for the calling thread.
+ *   - The first call that takes a given kernel on a device sets that kernel's
+ *     shared-memory limit (and, for the cluster kernels, asks the device how many
+ *     clusters it runs at once): make the first call of each shape outside any
+ *     stream capture; the calls after it can be captured in a CUDA graph.
  */
 #ifndef FLASH_COLSUM_B200_H_
 #define FLASH_COLSUM_B200_H_
