@@ -31,7 +31,10 @@
  *   - The first call that takes a given kernel on a device sets that kernel's
  *     shared-memory limit (and, for the cluster kernels, asks the device how many
  *     clusters it runs at once): make the first call of each shape outside any
- *     stream capture; the calls after it can be captured in a CUDA graph.
+ *     stream capture.  Later calls of the entries that take a caller's workspace
+ *     have been captured in CUDA graphs and replayed (few-row, short-axis and
+ *     streaming shapes); fcs_colsum_batched_static_scratch makes no statement on
+ *     capture.
  */
 #ifndef FLASH_COLSUM_B200_H_
 #define FLASH_COLSUM_B200_H_
@@ -247,8 +250,8 @@ int fcs_peer_wait(const int *flags, int n_flags, int value, int *status, void *s
  * Same arguments and result as fcs_colsum_batched, minus the workspace.
  *   - Limit: the call must need no more than FCS_STATIC_SCRATCH_BYTES of
  *     scratch (fcs_call_workspace_bytes(B, H, rows, S, D, 0, 0, &n): calls
- *     that take the few-row or the single-pass kernel need none and are never
- *     refused); larger problems are rejected with FCS_ERR_WORKSPACE and a
+ *     that take the few-row kernel, the single-pass kernel or the one-kernel
+ *     form for short query axes need none and are never refused); larger problems are rejected with FCS_ERR_WORKSPACE and a
  *     message, nothing is launched.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current) and caches it.  Make
