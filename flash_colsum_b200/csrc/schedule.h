@@ -492,22 +492,24 @@ struct TileRange {
 //
 // The cluster size is the largest with which all (batch, head) pairs run in one wave; with
 // more pairs than SMs, one CTA each in several waves.  The form is taken when the query
-// rows fit one 128-row tile and
-//   * the call is small (at most 16 key blocks per SM in all): it is bound by its launches,
-//     and this form has one kernel where the streaming passes have three; or
-//   * it is up to four times that, one wave of clusters covers four fifths of the SMs and
-//     no CTA walks more than 64 blocks: both forms then run at the memory rate, and this
-//     one still saves the launches (measured on 32 heads x 128 queries: 27 against 41 us at
-//     4096 keys, 64 against 79 at 16384, 191 against 211 at 65536, a tie from 131072 on);
-//   * never with more than four waves of CTAs (768 pairs of 197 keys: 60 against 50 us --
-//     the ramp of a CTA is paid once per wave).
-// `force`: only the shape limits apply (at most 128 rows).
+// rows fit one 128-row tile and a model of the two forms says so.  In units of one key
+// block through one phase on one SM (~1.35 us at D = 128): a CTA of this form costs a ramp
+// of ~3 and then its blocks, once per wave of CTAs; the three kernels of the streaming form
+// cost ~10 in launches, ramps and drains and then the call's blocks spread over all SMs:
+//       waves * (3 + bpc)  <=  10 + B * H * nkb / SMs
+// (measured per call, 32 heads x 128 queries: 28 against 41 us at 4096 keys, 64 against 79
+// at 16384, 107 against 128 at 32768; 8 heads x 32768 keys -- 64 CTAs -- tie at 55 and stay
+// with the streaming form; 768 pairs of 197 keys, six waves of one-block CTAs, lose 60 to 50).
+// Calls that are bound by memory in either form are also taken while one wave of clusters
+// covers four fifths of the SMs, no CTA walks more than 64 blocks and the call holds at
+// most 64 blocks per SM (32 heads x 65536 keys: 191 against 211 us; a tie from 131072 on).
+// `force`: only the shape limit applies (at most 128 rows).
 // ---------------------------------------------------------------------------
 constexpr int FUSED_SHORT_MAX_CLUSTER = 8;
 constexpr int FUSED_SHORT_MAX_BLOCKS = 64;      // per CTA
-constexpr int FUSED_SHORT_SMALL_WORK = 16;      // 256-key blocks in the whole call, per SM
-constexpr int FUSED_SHORT_LARGE_WORK = 64;
-constexpr int FUSED_SHORT_MAX_WAVES = 4;
+constexpr int FUSED_SHORT_RAMP = 3;             // blocks: what a CTA costs before its first block
+constexpr int FUSED_SHORT_LAUNCHES = 10;        // blocks: what the three-kernel form costs before its first block
+constexpr int FUSED_SHORT_LARGE_WORK = 64;      // blocks per SM in the whole call
 FCS_HD inline bool fused_short_plan(int B, int H, int Sq, int Sk, int causal, int k_past, int sms,
                                     const int* max_clusters, bool force, int* cl_out, int* nkb_out, int* bpc_out) {
     if (Sq > TILE) return false;
@@ -523,12 +525,13 @@ FCS_HD inline bool fused_short_plan(int B, int H, int Sq, int Sk, int causal, in
     if (bpc > (1 << 20)) return false;
     if (!force) {
         if (bpc > FUSED_SHORT_MAX_BLOCKS) return false;
-        if (units * cl > (long long)FUSED_SHORT_MAX_WAVES * sms) return false;
+        const long long at_once = cl > 1 ? max_clusters[cl] : sms;
+        const long long waves = (units + at_once - 1) / at_once;
         const long long work = units * nkb;
-        if (work > (long long)FUSED_SHORT_SMALL_WORK * sms) {
-            if (work > (long long)FUSED_SHORT_LARGE_WORK * sms) return false;
-            if (units > max_clusters[cl] || units * cl * 5 < (long long)sms * 4) return false;
-        }
+        const bool model = waves * (FUSED_SHORT_RAMP + bpc) * sms <= (long long)FUSED_SHORT_LAUNCHES * sms + work;
+        const bool memory_bound = waves == 1 && units * cl * 5 >= (long long)sms * 4 &&
+                                  work <= (long long)FUSED_SHORT_LARGE_WORK * sms;
+        if (!model && !memory_bound) return false;
     }
     if (cl_out) *cl_out = cl;
     if (nkb_out) *nkb_out = (int)nkb;

@@ -367,10 +367,11 @@ int fcs_single_pass_info(int Sk, int *cluster_size, int *max_clusters);
  * launcher (flash_colsum/kernel_causal_batched.py:106-136) is one Triton kernel per
  * call with atomics over key blocks.
  * mode 0 (default): the cluster size is the largest with which all (batch, head) pairs
- * run at once (32 heads on 148 SMs: clusters of four); the form is taken for small calls
- * (at most 16 key blocks of 256 per SM in all), for calls up to four times that when the
- * clusters cover four fifths of the SMs and no CTA walks more than 64 blocks, and never
- * with more than four waves of CTAs; 1: never; 2: whenever the query rows fit one tile.
+ * run at once (32 heads on 148 SMs: clusters of four); the form is taken when a cost
+ * model says it is the faster one -- per wave of CTAs a ramp and the blocks one CTA
+ * walks, against the three launches of the streaming form and the call's blocks spread
+ * over all SMs -- and for calls bound by memory (up to 64 blocks per SM) while the
+ * clusters cover four fifths of the SMs; 1: never; 2: whenever the query rows fit one tile.
  * Process-wide; not thread-safe.  The call reports its whole duration as the column
  * pass in fcs_last_pass_ms(); fcs_call_workspace_bytes() follows the mode in force.
  */

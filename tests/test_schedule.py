@@ -233,7 +233,7 @@ def test_calls_that_take_a_kernel_without_scratch_ask_for_none():
     assert _cabi.short_fused_applies(1, 32, 128, 65536) == (4, 64)       # still one wave over most SMs
     assert lib.fcs_call_workspace_bytes(1, 32, 128, 131072, 128, 1, -1, ctypes.byref(need)) == 0 and need.value > 0
     assert _cabi.short_fused_applies(1, 16, 128, 65536) is None           # too few CTAs for a call this long
-    assert _cabi.short_fused_applies(64, 12, 16, 197, is_causal=False, D=64) is None   # more than four waves
+    assert _cabi.short_fused_applies(64, 12, 16, 197, is_causal=False, D=64) is None   # six waves of tiny CTAs
     assert lib.fcs_call_workspace_bytes(1, 32, 300, 8192, 128, 1, -1, ctypes.byref(need)) == 0 and need.value > 0
     # sizes no call accepts
     assert lib.fcs_call_workspace_bytes(1, 1, 1, 1, 100, 0, 0, ctypes.byref(need)) == -2
@@ -260,7 +260,11 @@ B200_CLUSTERS = (ctypes.c_int * 9)(0, 148, 74, 48, 32, 28, 24, 16, 15)
     (1, 32, 128, 65536, 1, -1, 4064),
     (1, 32, 128, 131072, 1, -1, 0),        # too long
     (1, 16, 128, 65536, 1, -1, 0),         # long and too few CTAs
-    (64, 12, 16, 197, 0, 0, 0),            # more than four waves
+    (64, 12, 16, 197, 0, 0, 0),            # six waves of one-block CTAs: the ramp is paid six times
+    (1, 8, 128, 32768, 1, -1, 0),          # 64 CTAs of 16 blocks: the idle SMs cost more than the launches
+    (1, 4, 128, 131072, 1, -1, 0),         # four heads of a head-sharded long context: 32 CTAs
+    (1, 50, 128, 4096, 1, -1, 2008),
+    (16, 16, 128, 1024, 1, -1, 1004),      # 256 pairs in two waves
     (1, 4, 129, 1000, 1, -1, 0),           # two query tiles
 ])
 def test_one_kernel_form_plan_and_masks(emu, B, H, Sq, Sk, causal, k_past, expect):
