@@ -34,7 +34,7 @@
 namespace fcs {
 namespace fused {
 
-constexpr int MAX_CL = 8;               // CTAs per cluster (portable limit)
+constexpr int MAX_CL = FUSED_SHORT_MAX_CLUSTER;   // CTAs per cluster (the portable limit of eight)
 
 struct Params {
     Problem p;              // sizes, mask rule, scale, output (the scratch fields stay unused)
