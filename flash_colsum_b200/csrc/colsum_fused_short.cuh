@@ -197,29 +197,61 @@ colsum_fused_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             __syncwarp();
         }
         smallq_cluster_wait();      // (pairs with the arrive above)
-        // the extra columns of the query block are in shared memory (and every score of phase 1 has been read)
+        // phase 2: two tiles of 128 keys x 128 queries per block.  The score MMAs of the first two
+        // blocks do not need the statistics: they are issued while the exchange is under way, and only
+        // the MMAs of the extra columns (and the hand-over to the consumers) wait for it.
+        auto score_mmas = [&](int stage, int buf) {
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                // rows 128 t .. 128 t + 127 of the block: 16 KiB into each 32 KiB slab
+                const uint64_t dk = umma_desc_k_sw128(k_smem + stage * L::K_BYTES + t * (TILE * 128));
+                const uint32_t d_tmem = tmem_base + buf * BLOCK + t * (BLOCK / 2);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint64_t oq = (uint64_t)(((ks >> 2) * L::Q_SLAB_BYTES + (ks & 3) * 32) >> 4);
+                    const uint64_t ok_ = (uint64_t)(((ks >> 2) * L::K_SLAB_BYTES + (ks & 3) * 32) >> 4);
+                    umma_f16(d_tmem, dk + ok_, dq + oq, fp.idesc_cols, ks > 0 ? 1u : 0u);
+                }
+            }
+        };
+        auto extra_mmas = [&](int buf) {
+            if (!fp.use_ext) return;
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+                umma_f16(tmem_base + buf * BLOCK + t * (BLOCK / 2), umma_desc_k_sw32(smem_base + L::EXTA_OFF),
+                         umma_desc_k_sw32(smem_base + L::EXTB_OFF), fp.idesc_cols, 1u);
+        };
+        const int early = nblk < NUM_TBUF ? nblk : NUM_TBUF;
+        for (int e = 0; ok && e < early; ++e) {
+            const int m = n + e, stage = m % L::NS, buf = m & (NUM_TBUF - 1);
+            if (!wait_all(k_full(stage), (m / L::NS) & 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+            if (m >= NUM_TBUF && !wait_all(t_empty(buf), ((m >> 1) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
+            tc_fence_after();
+            if (elect_one_sync()) {
+                score_mmas(stage, buf);
+                umma_commit(k_empty(stage));
+            }
+            __syncwarp();
+        }
+        // the extra columns of the query block are in shared memory
         if (ok) ok = wait_all(ext_ready, 0, FCS_STATUS_WAIT_MMA);
-        for (; ok && n < 2 * nblk; ++n) {      // phase 2: two tiles of 128 keys x 128 queries per block
+        tc_fence_after();
+        for (int e = 0; ok && e < early; ++e, ++n) {
+            const int buf = n & (NUM_TBUF - 1);
+            if (elect_one_sync()) {
+                extra_mmas(buf);
+                umma_commit(t_full(buf));
+            }
+            __syncwarp();
+        }
+        for (; ok && n < 2 * nblk; ++n) {
             const int stage = n % L::NS, buf = n & (NUM_TBUF - 1);
             if (!wait_all(k_full(stage), (n / L::NS) & 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
             if (n >= NUM_TBUF && !wait_all(t_empty(buf), ((n >> 1) & 1) ^ 1, FCS_STATUS_WAIT_MMA)) { ok = false; break; }
             tc_fence_after();
             if (elect_one_sync()) {
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    // rows 128 t .. 128 t + 127 of the block: 16 KiB into each 32 KiB slab
-                    const uint64_t dk = umma_desc_k_sw128(k_smem + stage * L::K_BYTES + t * (TILE * 128));
-                    const uint32_t d_tmem = tmem_base + buf * BLOCK + t * (BLOCK / 2);
-#pragma unroll
-                    for (int ks = 0; ks < D / 16; ++ks) {
-                        const uint64_t oq = (uint64_t)(((ks >> 2) * L::Q_SLAB_BYTES + (ks & 3) * 32) >> 4);
-                        const uint64_t ok_ = (uint64_t)(((ks >> 2) * L::K_SLAB_BYTES + (ks & 3) * 32) >> 4);
-                        umma_f16(d_tmem, dk + ok_, dq + oq, fp.idesc_cols, ks > 0 ? 1u : 0u);
-                    }
-                    if (fp.use_ext)
-                        umma_f16(d_tmem, umma_desc_k_sw32(smem_base + L::EXTA_OFF),
-                                 umma_desc_k_sw32(smem_base + L::EXTB_OFF), fp.idesc_cols, 1u);
-                }
+                score_mmas(stage, buf);
+                extra_mmas(buf);
                 umma_commit(k_empty(stage));
                 umma_commit(t_full(buf));
             }
