@@ -187,8 +187,8 @@ def set_short_fused(mode: int) -> None:
 def short_fused_applies(B: int, H: int, sq_rows: int, sk: int, is_causal: bool = True, k_past: int = -1,
                         D: int = 128):
     """(cluster size, key blocks per CTA) when a call with these sizes takes the one-kernel form for
-    short query axes under the current mode, else None.  Calls with at most four query rows, and calls
-    that the single-pass kernel takes, are decided before this."""
+    short query axes under the current mode, else None.  Calls with at most four query rows are decided
+    before this; so are calls that the single-pass kernel takes, unless this form runs them in one wave."""
     cl, bpc = _i(0), _i(0)
     if not load().fcs_short_fused_applies(B, H, sq_rows, sk, D, int(is_causal), int(k_past), ctypes.byref(cl),
                                           ctypes.byref(bpc)):

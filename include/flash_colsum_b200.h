@@ -350,7 +350,8 @@ int fcs_last_pass_ms(float *stats_ms, float *merge_ms, float *colsum_ms);
 int fcs_set_single_pass(int mode);
 /* 1 if a call with these sizes (sq_rows = query rows that enter the mean) takes the
  * single pass under the current mode (host arithmetic only; calls with at most four query rows take the few-row kernel
- * before this choice is made). */
+ * before this choice is made, and so do calls of at most 128 query rows that the one-kernel form of
+ * fcs_set_short_fused runs in one wave of clusters). */
 int fcs_single_pass_applies(int B, int H, int sq_rows, int Sk, int D, int is_causal);
 /* CTAs per cluster the single pass uses for `Sk` keys (one per 256 keys) and how many
  * such clusters the current device runs at once. */
@@ -377,8 +378,9 @@ int fcs_single_pass_info(int Sk, int *cluster_size, int *max_clusters);
  */
 int fcs_set_short_fused(int mode);
 /* 1 if a call with these sizes takes the one-kernel form under the current mode (host
- * arithmetic only; k_past < 0: the inferred value; calls the few-row or the single-pass
- * kernel takes are decided before this one).  Writes the CTAs per cluster and the key
+ * arithmetic only; k_past < 0: the inferred value).  Calls the few-row kernel takes are
+ * decided before this one; so are calls the single-pass kernel takes, unless this form
+ * runs all their (batch, head) pairs in one wave of clusters.  Writes the CTAs per cluster and the key
  * blocks each walks when the pointers are not NULL. */
 int fcs_short_fused_applies(int B, int H, int sq_rows, int Sk, int D, int is_causal, int k_past, int *cluster_size,
                             int *blocks_per_cta);
