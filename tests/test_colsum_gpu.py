@@ -663,6 +663,51 @@ def test_short_query_axes_accumulate_and_graph_capture(fc):
     assert_parity(out.cpu().numpy(), want, "graph replay")
 
 
+def test_random_shapes_through_every_kernel_choice(fc):
+    """Sixty seeded random shapes (ragged sizes, both dtypes, head dimensions from 8 to 128, causal
+    with and without an explicit K_past, CLS prefixes) against the C checker: whichever kernel the
+    library picks for a shape -- few-row, single-pass, one-kernel cluster form, streaming passes --
+    the result is the same function of the inputs."""
+    from flash_colsum_b200 import _cabi
+    from oracle.naive_colsum import naive_colsum_f64
+    rng = np.random.default_rng(20240607)
+    took = {"few_rows": 0, "one_kernel": 0, "single_pass": 0, "streaming": 0}
+    for case in range(60):
+        causal = bool(rng.integers(0, 2))
+        D = int(rng.choice([8, 32, 64, 64, 80, 128, 128]))
+        dtype = "fp16" if rng.integers(0, 2) else "bf16"
+        B = int(rng.integers(1, 4))
+        H = int(rng.integers(1, 7))
+        Sk = int(rng.choice([1, 17, 128, 255, 256, 257, 600, 1000, 1537, 2200, 3100]))
+        if causal:
+            Sq = int(rng.choice([1, 2, 4, 5, 64, 100, 128, 129, 300, 520]))
+            k_past = None if rng.integers(0, 2) else int(rng.integers(0, Sk + 50))
+            cls_len = None
+        else:
+            Sq, k_past = Sk, None
+            cls_len = None if rng.integers(0, 2) else int(rng.choice([1, 3, 4, 5, 40, 128, 129, 300]))
+        w = Workload(f"fuzz{case}", B, H, Sq, Sk, D, dtype, is_causal=causal, cls_len=cls_len, seed=1000 + case)
+        q, k = make_inputs(w)
+        if causal:
+            got = fc.flash_colsum_causal(q.cuda(), k.cuda(), k_past=k_past)
+        else:
+            got = fc.flash_colsum(q.cuda(), k.cuda(), cls_len=cls_len)
+        torch.cuda.synchronize()
+        assert fc.device_status() == 0, w
+        want = naive_colsum_f64(q, k, is_causal=causal, cls_len=cls_len, k_past=k_past)
+        assert_parity(got.cpu().numpy(), want, f"{w} k_past={k_past}")
+        rows = Sq if cls_len is None else min(cls_len, Sq)
+        if rows <= 4 and D in (64, 128):
+            took["few_rows"] += 1
+        elif _cabi.short_fused_applies(B, H, rows, Sk, causal, -1 if k_past is None else k_past, D) is not None:
+            took["one_kernel"] += 1     # (a few of these go to the single-pass kernel: more than one wave)
+        elif _cabi.single_pass_applies(B, H, Sk, D, causal, rows):
+            took["single_pass"] += 1
+        else:
+            took["streaming"] += 1
+    assert min(took.values()) >= 3, took
+
+
 def test_topk_columns_matches_a_plain_sort(fc):
     """The pruning step: exact top-k positions per row, ascending, ties to the lower position."""
     from oracle.naive_colsum import topk_positions
