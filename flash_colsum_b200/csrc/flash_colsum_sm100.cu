@@ -998,6 +998,8 @@ static cudaError_t launch_small_q_w(const SmallQParams& sp, int grid, size_t sme
     cfg.blockDim = dim3(32 * (W + 1));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
+    // The cluster attribute is given for clusters of one as well: the kernel's cluster instructions
+    // (barrier.cluster, mapa, st.async) are illegal in a launch without it.
     cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeClusterDimension;
     attrs[0].val.clusterDim.x = (unsigned)sp.CL;
@@ -1254,6 +1256,7 @@ static cudaError_t launch_fused_short_d(const CUtensorMap& tq, const CUtensorMap
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = LayoutT::DYN_BYTES;
     cfg.stream = stream;
+    // (the cluster attribute also for clusters of one: the kernel uses cluster instructions)
     cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeClusterDimension;
     attrs[0].val.clusterDim.x = (unsigned)fp.CL;
