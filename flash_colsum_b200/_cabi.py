@@ -19,10 +19,11 @@ EXPORTED_SYMBOLS = (
     "fcs_set_short_fused", "fcs_short_fused_applies",
     "fcs_colsum_causal_batched", "fcs_select_topk", "fcs_select_threshold",
     "fcs_statistics_rows", "fcs_colsum_statistics", "fcs_colsum_columns", "fcs_selftest_wait_expiry",
+    "fcs_selftest_wait_expiry_cluster",
     "fcs_peer_post", "fcs_peer_wait", "fcs_colsum_causal_accumulate_signalled",
 )
 
-ABI_VERSION = 201   # fcs_version() of the library these argument lists were written for
+ABI_VERSION = 202   # fcs_version() of the library these argument lists were written for
 FCS_OK = 0
 FCS_ERR_UNSUPPORTED = -2
 FCS_DTYPE_FP16 = 0
@@ -111,6 +112,8 @@ def load() -> ctypes.CDLL:
     lib.fcs_peer_wait.argtypes = [_p, _i, _i, _p, _p]
     lib.fcs_selftest_wait_expiry.restype = _i
     lib.fcs_selftest_wait_expiry.argtypes = [_p, _p, _p, _sz, _p, ctypes.c_double, _p]
+    lib.fcs_selftest_wait_expiry_cluster.restype = _i
+    lib.fcs_selftest_wait_expiry_cluster.argtypes = [_p, _p, _p, _p, ctypes.c_double, _p]
     lib.fcs_select_threshold.restype = _i
     lib.fcs_select_threshold.argtypes = [_p, _i64, _i, _i, _f, _i, _p, _p, _p]
     lib.fcs_colsum_causal_accumulate.restype = _i

@@ -150,14 +150,14 @@ colsum_fused_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 
     if (warp == PRODUCER_WARP) {
         // -------------------------------------------- copies: the query block, then the key blocks twice
-        if (elect_one_sync()) {
+        bool ok = p.withhold_loads == 0;   // (self-test: nothing is loaded, every wait for data runs out)
+        if (ok && elect_one_sync()) {
             mbar_arrive_expect_tx(q_full, L::Q_BYTES);
 #pragma unroll
             for (int sl = 0; sl < L::SLABS; ++sl)
                 tma_load_4d(q_smem + sl * L::Q_SLAB_BYTES, &tm_q, q_full, sl * 64, 0, h, b);
         }
         __syncwarp();
-        bool ok = true;
         for (int n = 0; ok && n < 2 * nblk; ++n) {
             const int stage = n % L::NS;
             const int kb = n < nblk ? kb0 + n : kb1 - 1 - (n - nblk);   // phase 2 walks back: the last blocks are the ones still in L2
@@ -385,9 +385,12 @@ colsum_fused_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    // nobody leaves while a peer may still store into its shared memory
+    // nobody leaves while a peer may still store into its shared memory: a CTA whose flow was
+    // intact has waited for every such store on its exchange barrier; one that gave up a wait
+    // has not, and lingers until stores issued before the peers' arrival have landed
     smallq_cluster_arrive();
     smallq_cluster_wait();
+    if (*abort_flag) __nanosleep(100000);
 }
 
 }  // namespace fused

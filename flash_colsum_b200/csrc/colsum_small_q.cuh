@@ -442,9 +442,11 @@ colsum_small_q_kernel(const SmallQParams p) {
         if (prev_unit >= 0) finish(prev_unit, ucount - 1);
         if (!peers_up) smallq_cluster_wait();
     }
-    // nobody leaves while a peer may still store into its shared memory
+    // nobody leaves while a peer may still store into its shared memory (a CTA that gave up a wait
+    // has not waited for those stores on its exchange barriers: it lingers until they have landed)
     smallq_cluster_arrive();
     smallq_cluster_wait();
+    if (*abort_flag) __nanosleep(100000);
 }
 
 }  // namespace fcs

@@ -1572,7 +1572,7 @@ static int static_scratch_address(void** out_ptr) {
 // ---------------------------------------------------------------------------
 extern "C" {
 
-int fcs_version(void) { return 201; }
+int fcs_version(void) { return 202; }
 
 const char* fcs_last_error(void) { return fcs::g_err; }
 
@@ -1833,6 +1833,46 @@ int fcs_selftest_wait_expiry(const void* q, const void* k, void* workspace, size
         return fail(FCS_ERR_CUDA, "wait-expiry self-test failed to launch: %s",
                     cudaGetErrorString(e != cudaSuccess ? e : e2));
     return FCS_OK;
+}
+
+int fcs_selftest_wait_expiry_cluster(const void* q, const void* k, float* out, int* status, double limit_seconds,
+                                     void* stream_v) {
+    fcs::g_err[0] = 0;
+    using namespace fcs;
+    if (!q || !k || !out || !status)
+        return fail(FCS_ERR_INVALID_ARGUMENT, "q, k, out and status must not be NULL");
+    if (!(limit_seconds > 0.0) || limit_seconds > 2.0)
+        return fail(FCS_ERR_INVALID_ARGUMENT, "limit_seconds must be in (0, 2]");
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+    // the one-kernel form on one head: 128 queries, two blocks of 256 keys, a cluster of two CTAs
+    const int B = 1, H = 1, Sq = TILE, Sk = 2 * BLOCK, D = 64;
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk;
+    p.out = out;
+    p.out_ld = Sk;
+    p.status = status;
+    p.c = 0.125f * 1.4426950408889634f;
+    p.inv_c = 1.0f / p.c;
+    p.log2_norm = log2f((float)Sq);
+    p.withhold_loads = 1;
+    CUtensorMap tq, tk;
+    int rc;
+    if ((rc = make_tensor_map(&tq, q, FCS_DTYPE_FP16, B, H, Sq, D, (int64_t)Sq * D, (int64_t)Sq * D, D, TILE)) != FCS_OK) return rc;
+    if ((rc = make_tensor_map(&tk, k, FCS_DTYPE_FP16, B, H, Sk, D, (int64_t)Sk * D, (int64_t)Sk * D, D, BLOCK)) != FCS_OK) return rc;
+    static long long short_limit, full_limit = kWaitLimitCycles;
+    short_limit = (long long)(limit_seconds * 1.9e9);
+    cudaError_t e = cudaMemcpyToSymbolAsync(g_wait_limit_cycles, &short_limit, sizeof(long long), 0,
+                                            cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess)
+        rc = launch_fused_short(tq, tk, p, 64, 0.125f, true, /*cl=*/2, /*nkb=*/2, /*bpc=*/1, /*clear_out=*/true, nullptr, 0,
+                                stream);
+    const cudaError_t e2 = cudaMemcpyToSymbolAsync(g_wait_limit_cycles, &full_limit, sizeof(long long), 0,
+                                                   cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess || e2 != cudaSuccess)
+        return fail(FCS_ERR_CUDA, "wait-expiry self-test failed to launch: %s",
+                    cudaGetErrorString(e != cudaSuccess ? e : e2));
+    return rc;
 }
 
 int fcs_select_threshold(const float* colsum, int64_t ld, int B, int S, float threshold, int relative, int* indices,

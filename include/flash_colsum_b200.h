@@ -399,6 +399,15 @@ int fcs_short_fused_applies(int B, int H, int sq_rows, int Sk, int D, int is_cau
  */
 int fcs_selftest_wait_expiry(const void *q, const void *k, void *workspace, size_t workspace_bytes,
                              int *status, double limit_seconds, void *stream);
+/*
+ * The same for the kernels that run on thread-block clusters: one launch of the one-kernel form
+ * for short query axes (one head, 128 queries, 512 keys: a cluster of two CTAs; q: 128 x 64 fp16,
+ * k: 512 x 64 fp16, out: 512 floats, cleared) whose copy warp issues nothing.  Every CTA's waits
+ * run out, the CTAs still meet at their barriers, exchange what they have and leave together;
+ * *status is FCS_STATUS_WAIT_MMA or FCS_STATUS_WAIT_CONSUMER afterwards and `out` holds zeros.
+ */
+int fcs_selftest_wait_expiry_cluster(const void *q, const void *k, float *out, int *status, double limit_seconds,
+                                     void *stream);
 
 /*
  * How a call with these sizes is decomposed on the current device: key ranges

@@ -97,6 +97,8 @@ def test_argument_errors_of_the_pruning_and_self_test_entries():
     assert lib.fcs_selftest_wait_expiry(None, None, None, 0, None, 0.05, None) == -1
     assert lib.fcs_selftest_wait_expiry(addr(buf), addr(buf), addr(buf), 0, addr(idx), 3.0, None) == -1
     assert "limit_seconds" in _cabi.last_error()
+    assert lib.fcs_selftest_wait_expiry_cluster(None, None, None, None, 0.05, None) == -1
+    assert lib.fcs_selftest_wait_expiry_cluster(addr(buf), addr(buf), addr(buf), addr(idx), 0.0, None) == -1
     assert lib.fcs_colsum_causal_accumulate_and_clear(None, None, None, None, 1, 1, 1, 64, 0, 64, 64, 64, 64, 1.0, -1,
                                                       0, None, 0, None, None) < 0
     # flags between GPUs: pointer counts and alignment are checked before any launch

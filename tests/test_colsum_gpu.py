@@ -871,6 +871,30 @@ def test_a_wait_that_runs_out_reports_a_status_and_leaves_the_context_usable(fc)
     assert_parity(got, c_oracle.colsum_c(qq, kk), "call after an expired wait")
 
 
+def test_a_wait_that_runs_out_in_a_cluster_kernel(fc):
+    """The same for a kernel on thread-block clusters (the one-kernel form for short query axes, a
+    cluster of two CTAs): with nothing copied every CTA's waits run out after 50 ms, the CTAs still
+    meet at their barriers and leave together, the status word is set, nothing was added to the
+    output -- and the same kernel then computes a real call correctly."""
+    from flash_colsum_b200 import _cabi
+    lib = _cabi.load()
+    q = torch.randn(128, 64, device="cuda").half()
+    k = torch.randn(512, 64, device="cuda").half()
+    out = torch.full((512,), 7.0, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.fcs_selftest_wait_expiry_cluster(q.data_ptr(), k.data_ptr(), out.data_ptr(), status.data_ptr(),
+                                                0.05, stream) == 0, _cabi.last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) in (2, 3)       # FCS_STATUS_WAIT_MMA or FCS_STATUS_WAIT_CONSUMER
+    assert float(out.abs().max().item()) == 0.0
+    w = Workload("after_cluster", 1, 6, 128, 900, 64, "fp16", is_causal=True, seed=98)
+    qq, kk = make_inputs(w)
+    assert _cabi.short_fused_applies(1, 6, 128, 900, True, -1, 64) is not None
+    got = run_gpu(fc, w, qq, kk)
+    assert_parity(got, c_oracle.colsum_c(qq, kk, is_causal=True), "call after an expired wait in a cluster")
+
+
 def test_agrees_with_the_reference_kernels_where_they_are_exact(fc):
     """Against the reference's own Triton kernels (an unmodified install of the reference in
     baseline/_ref; skipped when there is none) on shapes where those kernels follow
