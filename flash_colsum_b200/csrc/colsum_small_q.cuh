@@ -306,10 +306,26 @@ colsum_small_q_kernel(const SmallQParams p) {
         // next one: by then every range's (maximum, sum) has long arrived
         auto finish = [&](int unit, int uc) {
             const int xb = uc & 1;
+            float M[SMALLQ_MAX_ROWS], w[SMALLQ_MAX_ROWS];
+            if (p.CL == 1) {
+                // the whole key axis is this CTA's: the warps' values are in shared memory since the
+                // barrier that ended the unit, no exchange to wait for
+                const float* rbp = red + (size_t)xb * SMALLQ_CONSUMER_WARPS * SMALLQ_MAX_ROWS * 2;
+#pragma unroll
+                for (int r = 0; r < SMALLQ_MAX_ROWS; ++r) {
+                    M[r] = 0.f; w[r] = 0.f;
+                    if (r < RMAX && r < p.R) {
+                        float mm = -INFINITY, ll = 0.f;
+                        for (int wi = 0; wi < W; ++wi)
+                            smallq_merge(mm, ll, rbp[(wi * SMALLQ_MAX_ROWS + r) * 2], rbp[(wi * SMALLQ_MAX_ROWS + r) * 2 + 1]);
+                        M[r] = mm;
+                        w[r] = ok ? p.inv_norm / ll : 0.f;
+                    }
+                }
+            } else {
             ok = ok && mbar_wait(xch_bar(xb), (uc >> 1) & 1, abort_flag, p.status, FCS_STATUS_WAIT_CONSUMER);
             ok = __all_sync(0xffffffffu, ok);
             const float* xv = xch + (size_t)xb * SMALLQ_MAX_CLUSTER * SMALLQ_MAX_ROWS * 2;
-            float M[SMALLQ_MAX_ROWS], w[SMALLQ_MAX_ROWS];
 #pragma unroll
             for (int r = 0; r < SMALLQ_MAX_ROWS; ++r) {
                 M[r] = 0.f; w[r] = 0.f;
@@ -320,6 +336,7 @@ colsum_small_q_kernel(const SmallQParams p) {
                     M[r] = mm;
                     w[r] = ok ? p.inv_norm / ll : 0.f;
                 }
+            }
             }
             if (!out_clear) { grid_dependency_wait(); out_clear = true; }   // the output has been cleared
             const float* sc = sc_base + (size_t)(p.bufs == 2 ? xb : 0) * sc_buf;
@@ -347,7 +364,7 @@ colsum_small_q_kernel(const SmallQParams p) {
             }
             if (unit + p.clusters < p.units) load_q(unit + p.clusters, qnext);   // lands during this unit
             const int xb = ucount & 1;
-            if (threadIdx.x == 0) mbar_arrive_expect_tx(xch_bar(xb), (uint32_t)p.CL * SMALLQ_MAX_ROWS * 8);
+            if (threadIdx.x == 0 && p.CL > 1) mbar_arrive_expect_tx(xch_bar(xb), (uint32_t)p.CL * SMALLQ_MAX_ROWS * 8);
             float* sc = sc_base + (size_t)(p.bufs == 2 ? xb : 0) * sc_buf;
 
             // scores (log2 domain) of this range, with a running (maximum, sum) per thread
@@ -428,7 +445,7 @@ colsum_small_q_kernel(const SmallQParams p) {
             }
             smallq_consumer_sync<W>();   // also orders this unit's score stores, and the finish above before the next unit's
             if (!peers_up) { smallq_cluster_wait(); peers_up = true; }
-            if (threadIdx.x < p.CL * SMALLQ_MAX_ROWS) {
+            if (p.CL > 1 && threadIdx.x < p.CL * SMALLQ_MAX_ROWS) {
                 const int dst = threadIdx.x / SMALLQ_MAX_ROWS, r = threadIdx.x % SMALLQ_MAX_ROWS;
                 float mm = -INFINITY, ll = 0.f;
                 if (r < RMAX && r < p.R)
