@@ -441,6 +441,29 @@ def test_operands_of_more_than_two_to_the_31_elements(fc):
         torch.backends.cuda.matmul.allow_tf32 = prev
 
 
+def test_key_axes_of_millions_of_keys(fc):
+    """Key axes of two and three million keys (ragged, one and 128 suffix queries): all heads in one
+    call agree with the heads taken one by one, every column mean sums to one over the keys, and
+    the last keys -- seen only by the last queries -- match a direct evaluation of those queries."""
+    if torch.cuda.mem_get_info()[0] < (8 << 30):
+        pytest.skip("needs 8 GB of free device memory")
+    g = torch.Generator(device="cuda").manual_seed(12)
+    for (H, Sq, Sk, D) in [(2, 128, 3000001, 128), (8, 1, 1 << 21, 128)]:
+        q = torch.randn(1, H, Sq, D, generator=g, device="cuda", dtype=torch.bfloat16)
+        k = torch.randn(1, H, Sk, D, generator=g, device="cuda", dtype=torch.bfloat16)
+        full = fc.flash_colsum(q, k, is_causal=True)
+        parts = torch.stack([fc.flash_colsum(q[:, h:h + 1], k[:, h:h + 1], is_causal=True) for h in range(H)]).mean(0)
+        torch.cuda.synchronize()
+        assert fc.device_status() == 0
+        assert float((full - parts).norm() / parts.norm()) <= 1e-5
+        assert abs(float(full.sum()) - 1.0) <= 1e-4 and bool((full >= 0).all())
+        # the last query alone: softmax over all keys, its weight on the last key is that key's whole column sum
+        s = (q[0, :, -1:].float() @ k[0].float().transpose(-1, -2)) / D ** 0.5          # (H, 1, Sk)
+        p_last = torch.softmax(s, dim=-1)[:, 0, -1].sum() / (H * Sq)
+        assert abs(float(full[0, -1]) - float(p_last)) <= 1e-3 * float(p_last) + 1e-12
+        del q, k, s
+
+
 def test_long_inputs_take_the_interleaved_column_schedule(fc):
     """More than 300 000 query rows: the column pass deals (b, h, key tile) chunks round-robin.
     Non-causal with ragged sizes, and causal with more than one batch entry."""
