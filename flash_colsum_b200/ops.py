@@ -216,6 +216,19 @@ def _flash_colsum_causal(Q: torch.Tensor, K: torch.Tensor, scale: float, K_past:
     return out
 
 
+def _without_work(query: torch.Tensor, key: torch.Tensor) -> Optional[torch.Tensor]:
+    """The result for inputs with an empty axis, which launch nothing: what ``naive_colsum`` of the
+    reference returns for them (baselines.py:35-78) -- an empty (B, S_k) tensor when there is no
+    batch entry or no key, and NaN (a mean over no rows) when there are keys but no query rows or heads."""
+    B, H, S_q, _ = query.shape
+    S_k = key.shape[2]
+    if B == 0 or S_k == 0:
+        return torch.empty((B, S_k), device=query.device, dtype=torch.float32)
+    if S_q == 0 or H == 0:
+        return torch.full((B, S_k), float("nan"), device=query.device, dtype=torch.float32)
+    return None
+
+
 def flash_colsum(
     query: torch.Tensor,
     key: torch.Tensor,
@@ -273,14 +286,19 @@ def flash_colsum(
             raise ValueError(
                 f"Query and key must have same heads and head_dim, got "
                 f"H_q={H_q}, H_k={H_k}, D_q={D_q}, D_k={D_k}")
-        out = _flash_colsum_causal(query, key, scale)
+        out = _without_work(query, key)
+        if out is None:
+            out = _flash_colsum_causal(query, key, scale)
     else:
         if B_q != B_k or H_q != H_k or S_q != S_k or D_q != D_k:
             raise ValueError(
                 f"For non-causal attention, query and key must have same shape, got "
                 f"query: {query.shape}, key: {key.shape}")
         cls_n = -1 if cls_len is None else int(cls_len)
-        if B_q == 1:
+        out = _without_work(query, key)
+        if out is not None:
+            pass
+        elif B_q == 1:
             out = _flash_colsum_non_batched(query, key, scale, CLS_N=cls_n)
         else:
             out = _flash_colsum_batched(query, key, scale, CLS_N=cls_n)
@@ -325,6 +343,9 @@ def flash_colsum_causal(
         raise ValueError(f"k_past must be non-negative, got {k_past}")
     if scale is None:
         scale = 1.0 / (D ** 0.5)
+    out = _without_work(query, key)
+    if out is not None:
+        return out if out_dtype is None else out.to(out_dtype)
     lib = _cabi.load()
     Q, K, code = _prepare(query, key)
     K_len = K.shape[2]

@@ -228,6 +228,23 @@ def test_zero_queries_give_closed_form(fc):
     np.testing.assert_allclose(flat, 1.0 / Sq, rtol=2e-5)
 
 
+def test_inputs_with_an_empty_axis(fc):
+    """No batch entry, no key, no query row: what the reference's naive_colsum returns for such
+    inputs (an empty result, or NaN for a mean over no rows), and nothing is launched."""
+    dev = "cuda"
+    h = lambda *shape: torch.empty(*shape, device=dev, dtype=torch.float16)   # noqa: E731
+    out = fc.flash_colsum(h(0, 2, 4, 64), h(0, 2, 4, 64))
+    assert out.shape == (0, 4) and out.dtype == torch.float32
+    assert fc.flash_colsum(h(1, 2, 0, 64), h(1, 2, 0, 64)).shape == (1, 0)
+    assert fc.flash_colsum(h(3, 2, 0, 64), h(3, 2, 0, 64), cls_len=1).shape == (3, 0)
+    out = fc.flash_colsum(h(1, 2, 0, 64), torch.randn(1, 2, 5, 64, device=dev).half(), is_causal=True)
+    assert out.shape == (1, 5) and bool(torch.isnan(out).all())
+    assert fc.flash_colsum_causal(torch.randn(2, 2, 3, 64, device=dev).half(), h(2, 2, 0, 64)).shape == (2, 0)
+    assert fc.flash_colsum_causal(h(0, 2, 3, 64), h(0, 2, 7, 64), out_dtype=torch.float16).dtype == torch.float16
+    torch.cuda.synchronize()
+    assert fc.device_status() == 0
+
+
 def test_non_contiguous_views_and_out_dtype(fc):
     g = torch.Generator().manual_seed(41)
     big_q = torch.randn(2, 3, 200, 128, generator=g).half().cuda()
