@@ -1,13 +1,14 @@
 #!/usr/bin/env python
 """The reference's three published sweeps, on this library.
 
-    python benchmarks/sweeps.py [--sweep batched|single|causal|configs|all] [--csv out.csv] [--quick]
+    python benchmarks/sweeps.py [--sweep batched|single|causal|causal_short|configs|all] [--csv out.csv] [--quick]
                                 [--with-reference] [--label TEXT]
 
 Shapes and dtype follow the reference's ``sweep_all_unified``
 (benchmarks/benchmark_colsum.py:289-424 and 757-801): fp16;
 batched non-causal H=16 S=1024 D=64 over the batch size; single-sample non-causal
-H=16 D=64 over the sequence length; causal H=32 Q=128 D=128 over the key length.
+H=16 D=64 over the sequence length; causal H=32 Q=128 D=128 over the key length (and,
+as `causal_short`, the same shape from 1024 to 8192 keys, below the reference's axis).
 Latency is reported two ways: per call by CUDA events over back-to-back calls (device time; the median of five
 groups of calls), and the reference's way -- host clock around call + synchronize
 (benchmark_colsum.py:42-56).  Peak memory is ``torch.cuda.max_memory_allocated``
@@ -49,6 +50,8 @@ SWEEPS = {
                for s in (4096, 8192, 16384, 32768, 65536, 131072, 262144)],
     "causal": [dict(B=1, H=32, Sq=128, Sk=k, D=128, causal=True)
                for k in (16384, 32768, 65536, 131072, 262144)],
+    # the same causal shape below the reference's axis: decode-time calls, bound by launch and ramp
+    "causal_short": [dict(B=1, H=32, Sq=128, Sk=k, D=128, causal=True) for k in (1024, 2048, 4096, 8192)],
     # the configurations the headline numbers are quoted on (fp16 here; the long-context one is
     # bf16 with outlier keys in the benchmark proper)
     "configs": [dict(B=8, H=16, Sq=2048, Sk=2048, D=64, causal=False),
@@ -188,7 +191,7 @@ def main():
     reference = load_reference() if args.with_reference else None
     rows = []
     for name in (sorted(SWEEPS) if args.sweep == "all" else [args.sweep]):
-        pts = SWEEPS[name][:-2] if args.quick and name != "configs" else SWEEPS[name]
+        pts = SWEEPS[name][:-2] if args.quick and name not in ("configs", "causal_short") else SWEEPS[name]
         for pt in pts:
             big = pt["B"] * pt["H"] * pt["Sq"] * pt["Sk"] > 3e10
             r = run_point(pt, warmup=2 if big else 10, iters=3 if big else 50, reference=reference)

@@ -24,6 +24,7 @@ def test_sweep_points_are_the_reference_benchmarks_axes():
     assert [p["Sk"] for p in sweeps.SWEEPS["causal"]] == [16384 << i for i in range(5)]
     assert all((p["H"], p["Sq"], p["D"], p["causal"]) == (32, 128, 128, True) for p in sweeps.SWEEPS["causal"])
     assert len(sweeps.SWEEPS["configs"]) == 4
+    assert [p["Sk"] for p in sweeps.SWEEPS["causal_short"]] == [1024, 2048, 4096, 8192]
 
 
 @pytest.mark.parametrize("B,H,S,budget,chunked", [
