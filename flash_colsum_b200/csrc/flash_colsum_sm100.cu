@@ -1408,10 +1408,11 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
 
     // each tensor is the resident operand (128-row boxes) of one pass and the
     // streamed operand (256-row boxes) of the other
+    // (the two cluster kernels take queries in 128-row and keys in 256-row boxes only: the other two
+    // maps are encoded once it is known that the streaming passes run -- an encode is a microsecond
+    // of host time, and the calls the cluster kernels take are bound by the host when issued back to back)
     CUtensorMap tq_a, tq_b, tk_a, tk_b;
     if ((rc = make_tensor_map(&tq_a, q, dtype, B, H, Sq, D, qsb, qsh, qss, TILE)) != FCS_OK) return rc;
-    if ((rc = make_tensor_map(&tq_b, q, dtype, B, H, Sq, D, qsb, qsh, qss, BLOCK)) != FCS_OK) return rc;
-    if ((rc = make_tensor_map(&tk_a, k, dtype, B, H, Sk, D, ksb, ksh, kss, TILE)) != FCS_OK) return rc;
     if ((rc = make_tensor_map(&tk_b, k, dtype, B, H, Sk, D, ksb, ksh, kss, BLOCK)) != FCS_OK) return rc;
     int fcl = 0, fnkb = 0, fbpc = 0;
     const bool fused_ok = passes == PASSES_BOTH && !sig && short_fused_applies(B, H, Sq, Sk, D, causal, k_past, &fcl, &fnkb, &fbpc);
@@ -1445,6 +1446,8 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
             return rc;
         }
     }
+    if ((rc = make_tensor_map(&tq_b, q, dtype, B, H, Sq, D, qsb, qsh, qss, BLOCK)) != FCS_OK) return rc;
+    if ((rc = make_tensor_map(&tk_a, k, dtype, B, H, Sk, D, ksb, ksh, kss, TILE)) != FCS_OK) return rc;
     // the two streaming passes are the only kernels that use scratch memory
     size_t part_off = 0, ext_off = 0;
     const size_t need = workspace_layout(p, &part_off, &ext_off);
