@@ -1462,6 +1462,7 @@ static int colsum_impl(const void* q, const void* k, float* out, int64_t out_ld,
     if (use_ext && (rc = make_ext_tensor_map(&text, p.ext, dtype, (long long)B * H, p.lse_rows)) != FCS_OK) return rc;
 
     const int grid1 = (int)(p.stats_items < sms ? p.stats_items : sms);
+    stats_set_grid(p, grid1);
     long long col_items = p.steps_total;
     if (p.col_interleave == COL_HEAD_MAJOR) col_items = (long long)B * H * ceil_div(p.NKC, p.col_pack);
     const int grid2 = (int)(col_items < sms ? col_items : sms);

@@ -50,6 +50,9 @@ struct Problem {
     int col_pack;       // head-major order: key tiles per item (2 when the queries fill half an accumulator, else 1)
     int col_combine;    // head-major order: the kernels that combine the consumer groups' sums before one add per key are used
     long long stats_items;
+    // the statistics pass's CTA count, as the steps an item index advances by in (key range, query tile,
+    // head, batch entry) digits: lets a CTA go from one of its items to the next without a division
+    int stats_grid, stats_d_sp, stats_d_qt, stats_d_h, stats_d_b;
     long long steps_per_batch;  // column pass: steps of one batch entry
     long long steps_total;
     long long lse_rows;         // rows of neg_lse per (b, h): NQB * 256
@@ -159,17 +162,42 @@ struct StatsItems {
     int b, h, qt, sp, s0, s1, grid;   // steps = key blocks s0..s1-1
     long long item;
 
+    // Decoding an item index is on the critical path of every role at every item boundary (the MMA
+    // warp cannot issue the next item's first MMA before it): 32-bit arithmetic wherever the counts
+    // allow it -- a 64-bit division is a subroutine of a hundred instructions, and eight of them
+    // left the consumers waiting 1 500-2 600 cycles for the first tile of every item.
     FCS_HD void load(const Problem& p) {
         if (item >= p.stats_items) { done = true; return; }
-        sp = (int)(item % p.nsplit);
-        const long long t = item / p.nsplit;
-        qt = (int)(t % p.NQ);
-        const long long bh = t / p.NQ;
-        h = (int)(bh % p.H);
-        b = (int)(bh / p.H);
+        if (p.stats_items <= 0x7fffffffLL) {
+            const unsigned it = (unsigned)item, ns = (unsigned)p.nsplit, nq = (unsigned)p.NQ, nh = (unsigned)p.H;
+            const unsigned t = it / ns;
+            sp = (int)(it - t * ns);
+            const unsigned bh = t / nq;
+            qt = (int)(t - bh * nq);
+            const unsigned bb = bh / nh;
+            h = (int)(bh - bb * nh);
+            b = (int)bb;
+        } else {
+            sp = (int)(item % p.nsplit);
+            const long long t = item / p.nsplit;
+            qt = (int)(t % p.NQ);
+            const long long bh = t / p.NQ;
+            h = (int)(bh % p.H);
+            b = (int)(bh / p.H);
+        }
+        ranges(p);
+    }
+    // key blocks of the item's key range
+    FCS_HD void ranges(const Problem& p) {
         const int nk = stats_key_blocks(p, qt);
-        s0 = (int)((long long)sp * nk / p.nsplit);
-        s1 = (int)((long long)(sp + 1) * nk / p.nsplit);
+        if (p.nsplit == 1) {
+            s0 = 0;
+            s1 = nk;
+        } else {
+            // sp < 64 and nk < 2^23 (a key axis of 2^31 keys): the products fit 32 bits
+            s0 = (int)((unsigned)sp * (unsigned)nk / (unsigned)p.nsplit);
+            s1 = (int)((unsigned)(sp + 1) * (unsigned)nk / (unsigned)p.nsplit);
+        }
     }
     FCS_HD void init(const Problem& p, int cta, int grid_) {
         done = false;
@@ -179,12 +207,37 @@ struct StatsItems {
     }
     FCS_HD void next(const Problem& p) {
         item += grid;
-        load(p);
+        if (grid != p.stats_grid) { load(p); return; }    // (no digits for this grid: decode afresh)
+        if (item >= p.stats_items) { done = true; return; }
+        // add the grid's digits, with carries
+        sp += p.stats_d_sp;
+        int carry = sp >= p.nsplit ? 1 : 0;
+        sp -= carry ? p.nsplit : 0;
+        qt += p.stats_d_qt + carry;
+        carry = qt >= p.NQ ? 1 : 0;
+        qt -= carry ? p.NQ : 0;
+        h += p.stats_d_h + carry;
+        carry = h >= p.H ? 1 : 0;
+        h -= carry ? p.H : 0;
+        b += p.stats_d_b + carry;
+        ranges(p);
     }
     FCS_HD int a_row() const { return qt * TILE; }        // resident = query tile
     FCS_HD int b_row(int s) const { return s * BLOCK; }   // streamed = key block
     FCS_HD bool flush() const { return false; }
 };
+
+// The digits of `grid` (the statistics pass's CTA count) for StatsItems::next; call before launching it.
+inline void stats_set_grid(Problem& p, int grid) {
+    p.stats_grid = grid;
+    long long g = grid;
+    p.stats_d_sp = (int)(g % p.nsplit);
+    g /= p.nsplit;
+    p.stats_d_qt = (int)(g % p.NQ);
+    g /= p.NQ;
+    p.stats_d_h = (int)(g % p.H);
+    p.stats_d_b = (int)(g / p.H);
+}
 
 // Column pass, two ways of dealing out the steps.
 // Contiguous (short inputs): steps ordered (b, key tile, h, query block); a CTA takes
@@ -209,17 +262,35 @@ struct ColsumItems {
 
     FCS_HD void load_chunk(const Problem& p) {
         const long long total = (long long)p.B * p.H * p.NKC * p.col_parts;
+        const bool small = total <= 0x7fffffffLL;     // 32-bit arithmetic (see StatsItems::load)
         for (; chunk < total; chunk += stride) {
-            const int part = (int)(chunk % p.col_parts);
-            long long item = chunk / p.col_parts;
-            kt = (int)(item % p.NKC);
-            item /= p.NKC;
-            h = (int)(item % p.H);
-            b = (int)(item / p.H);
+            int part;
+            if (small) {
+                const unsigned c = (unsigned)chunk, cp = (unsigned)p.col_parts, nk = (unsigned)p.NKC, nh = (unsigned)p.H;
+                const unsigned i0 = c / cp;
+                part = (int)(c - i0 * cp);
+                const unsigned i1 = i0 / nk;
+                kt = (int)(i0 - i1 * nk);
+                const unsigned i2 = i1 / nh;
+                h = (int)(i1 - i2 * nh);
+                b = (int)i2;
+            } else {
+                part = (int)(chunk % p.col_parts);
+                long long item = chunk / p.col_parts;
+                kt = (int)(item % p.NKC);
+                item /= p.NKC;
+                h = (int)(item % p.H);
+                b = (int)(item / p.H);
+            }
             qlo = colsum_first_q_block(p, kt);
-            const long long n = p.NQB - qlo;
-            s0 = qlo + (int)(n * part / p.col_parts);
-            s1 = qlo + (int)(n * (part + 1) / p.col_parts);
+            const unsigned n = (unsigned)(p.NQB - qlo), cp = (unsigned)p.col_parts;
+            if (n <= 0xffffffffu / cp) {      // the products fit 32 bits
+                s0 = qlo + (int)(n * (unsigned)part / cp);
+                s1 = qlo + (int)(n * (unsigned)(part + 1) / cp);
+            } else {
+                s0 = qlo + (int)((long long)n * part / p.col_parts);
+                s1 = qlo + (int)((long long)n * (part + 1) / p.col_parts);
+            }
             if (s1 > s0) { flush_ = true; return; }   // (a part of a short item may be empty)
         }
         done = true;

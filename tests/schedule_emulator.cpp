@@ -364,3 +364,32 @@ extern "C" int check_fused_short(int B, int H, int Sq, int Sk, int causal, int k
         }
     return cl * 1000 + bpc;
 }
+
+// StatsItems::next with the grid's digits against a fresh decode of every item index: walks every
+// CTA's items of a planned call.  Returns the number of items walked, or a negative code.
+extern "C" long long check_stats_digits(int B, int H, int Sq, int Sk, int causal, int k_past, int sms) {
+    if (causal && k_past < 0) k_past = Sk > Sq ? Sk - Sq : 0;
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    plan(p, B, H, Sq, Sk, causal, k_past, sms);
+    const int grid = (int)(p.stats_items < sms ? p.stats_items : sms);
+    stats_set_grid(p, grid);
+    long long walked = 0;
+    for (int cta = 0; cta < grid; ++cta) {
+        StatsItems it;
+        it.init(p, cta, grid);
+        for (; !it.done; it.next(p)) {
+            StatsItems ref;
+            ref.done = false;
+            ref.grid = grid;
+            ref.item = it.item;
+            ref.load(p);
+            if (ref.done) return -1;
+            if (ref.b != it.b || ref.h != it.h || ref.qt != it.qt || ref.sp != it.sp || ref.s0 != it.s0 || ref.s1 != it.s1)
+                return -2;
+            ++walked;
+        }
+        if (it.item < p.stats_items) return -3;
+    }
+    return walked == p.stats_items ? walked : -4;
+}

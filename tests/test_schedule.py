@@ -32,6 +32,8 @@ def emu():
         [ctypes.c_int] * 5 + [ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
     lib.check_fused_short.restype = ctypes.c_int
     lib.check_fused_short.argtypes = [ctypes.c_int] * 7 + [ctypes.c_void_p, ctypes.c_int]
+    lib.check_stats_digits.restype = ctypes.c_longlong
+    lib.check_stats_digits.argtypes = [ctypes.c_int] * 7
     lib.scratch_need.restype = ctypes.c_longlong
     lib.scratch_need.argtypes = [ctypes.c_int] * 7 + [ctypes.c_void_p]
     return lib
@@ -283,3 +285,18 @@ def test_one_kernel_form_masks_on_a_walk_of_sizes(emu):
                 walked += 1
             assert emu.check_fused_short(2, 2, Sq, Sk, 0, 0, 148, B200_CLUSTERS, 1) > 0
     assert walked == 7 * 8 * 10
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk,causal,k_past,sms", [
+    (8, 16, 2048, 2048, 0, 0, 148),        # the headline shape: 2048 items, no key split
+    (1, 32, 512, 131072, 1, -1, 148),      # long context: key ranges split
+    (3, 5, 383, 383, 0, 0, 148),
+    (1, 2, 700, 5000, 1, 100, 148),
+    (2, 7, 130, 900, 1, -1, 7),            # a grid that is no multiple of anything
+    (5, 3, 1000, 1000, 0, 0, 100),
+    (1, 1, 1, 1, 0, 0, 148),
+])
+def test_statistics_items_advance_by_digits(emu, B, H, Sq, Sk, causal, k_past, sms):
+    """Going from one item of a CTA to its next by adding the grid's digits gives the same items as
+    decoding every index afresh, for every CTA, and covers every item once."""
+    assert emu.check_stats_digits(B, H, Sq, Sk, causal, k_past, sms) > 0
