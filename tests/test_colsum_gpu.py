@@ -970,7 +970,15 @@ def test_signalled_accumulate_entry_posts_its_flags(fc):
     returns to zero, the sum is right -- and a few-row call is refused so that its caller falls
     back to flags around the call."""
     from flash_colsum_b200 import _cabi, ops
-    w = Workload("sig", 1, 4, 300, 2500, 128, "bf16", is_causal=True, seed=55)
+    # two query blocks over many key tiles (the short-query column mode), then a longer query axis
+    # (the generic column mode, which takes the flag pointers from its shared-memory copy of the call)
+    for w in (Workload("sig", 1, 4, 300, 2500, 128, "bf16", is_causal=True, seed=55),
+              Workload("sig_generic", 1, 4, 1100, 1500, 64, "fp16", is_causal=True, seed=56)):
+        _signalled_accumulate_case(fc, w)
+
+
+def _signalled_accumulate_case(fc, w):
+    from flash_colsum_b200 import _cabi, ops
     q, k = make_inputs(w)
     qd, kd = q.cuda(), k.cuda()
     want = c_oracle.colsum_c(q, k, is_causal=True)
@@ -982,14 +990,15 @@ def test_signalled_accumulate_entry_posts_its_flags(fc):
     sig = _cabi.PeerSignals()
     sig.post[0], sig.post[1] = base + 4, base + 8
     sig.post_n, sig.post_value = 2, 7
-    assert ops._flash_colsum_causal(qd[:, :2], kd[:, :2], 1.0 / 128 ** 0.5, h_norm=4, accumulate_into=target,
+    scale = 1.0 / w.D ** 0.5
+    assert ops._flash_colsum_causal(qd[:, :2], kd[:, :2], scale, h_norm=4, accumulate_into=target,
                                     clear_next=nxt, signals=sig) is not None
     # ... the other two as "another rank" (waits for a flag that is already there, reports completion)
     sig = _cabi.PeerSignals()
     flags[0] = 5
     sig.wait_flag, sig.wait_value = base, 5
     sig.counter, sig.done_flag, sig.done_value = base + 16, base + 12, 9
-    assert ops._flash_colsum_causal(qd[:, 2:], kd[:, 2:], 1.0 / 128 ** 0.5, h_norm=4, accumulate_into=target,
+    assert ops._flash_colsum_causal(qd[:, 2:], kd[:, 2:], scale, h_norm=4, accumulate_into=target,
                                     signals=sig) is not None
     torch.cuda.synchronize()
     assert fc.device_status() == 0
@@ -997,4 +1006,4 @@ def test_signalled_accumulate_entry_posts_its_flags(fc):
     assert float(nxt.abs().max().item()) == 0.0
     assert_parity(target.cpu().numpy()[None, :], want, "signalled accumulate")
     # two decode queries: the few-row kernel cannot carry the flags
-    assert ops._flash_colsum_causal(qd[:, :, :2], kd, 1.0 / 128 ** 0.5, accumulate_into=target, signals=sig) is None
+    assert ops._flash_colsum_causal(qd[:, :, :2], kd, scale, accumulate_into=target, signals=sig) is None
