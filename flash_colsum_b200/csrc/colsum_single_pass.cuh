@@ -362,9 +362,11 @@ colsum_single_pass_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         // ------------------------------------------------ statistics exchange and weights
         const int xw = warp - XCHG_WARP;
         const int total = range.tiles();
-        for (int i = 0; i < total; ++i) {
+        // (the query tile of the share's i-th tile, kept by counting: decoding it is a 64-bit
+        // modulo, a hundred instructions in the warp every tile's exchange waits for)
+        int t = total > 0 ? range.tile_of(0) : 0;
+        for (int i = 0; i < total; ++i, t = (t + 1 == p.NQ) ? 0 : t + 1) {
             const int slot = i & 1;
-            const int t = range.tile_of(i);
             // (1) the four groups' (max, sum) of this CTA -> one pair per row, posted to every CTA
             if (!wait_all(stats_bar(slot), (i >> 1) & 1, FCS_STATUS_WAIT_CONSUMER)) break;
             float mg[XCHG_ROWS_PER_LANE][CONSUMER_GROUPS];
