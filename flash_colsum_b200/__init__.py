@@ -6,4 +6,4 @@ from .ops import (flash_colsum, flash_colsum_causal, flash_colsum_host, topk_col
 __all__ = ["flash_colsum", "flash_colsum_causal", "flash_colsum_host", "topk_columns", "threshold_columns",
            "device_status"]
 
-__version__ = "0.2.0"
+__version__ = "0.2.2"
