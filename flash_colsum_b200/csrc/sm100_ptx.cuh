@@ -87,8 +87,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // the CTA gives up first, so that every other role stops waiting promptly.  The
 // limit is counted on the SM's cycle counter, which is cheap to read; it is only
 // consulted every 16 polls.
+// One poll that never parks the thread.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
+    if (mbar_test_wait(bar, parity)) return true;    // (most waits find their phase complete)
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     unsigned spins = 0;
